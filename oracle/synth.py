@@ -1,0 +1,84 @@
+"""Seeded synthetic inputs with the shapes of the benchmark configurations.
+
+Test infrastructure only.  No dataset or checkpoint is read: weights are drawn
+from N(0, sigma) by seed, rounded to BF16 (or kept FP32), and laid out as
+safetensors files, which is the container the reference's planner parses
+(lmz/planner.py:196-237).
+"""
+from __future__ import annotations
+
+import json
+
+import numpy as np
+
+
+def bf16_bytes(x: np.ndarray) -> np.ndarray:
+    """float32 -> bfloat16 bytes, round-to-nearest-even (what torch's .to(bfloat16) does)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = ((u >> 16) & 1) + np.uint32(0x7FFF)
+    return ((u + r) >> 16).astype(np.uint16).view(np.uint8)
+
+
+def normal_bf16(shape, seed: int, sigma: float = 0.02) -> np.ndarray:
+    rng = np.random.default_rng(seed)
+    n = int(np.prod(shape))
+    return bf16_bytes(rng.standard_normal(n, dtype=np.float32) * np.float32(sigma))
+
+
+def safetensors_bytes(tensors) -> np.ndarray:
+    """Serialise [(name, dtype string, shape, uint8 data)] as one safetensors file."""
+    meta, pos = {}, 0
+    for name, dt, shape, data in tensors:
+        meta[name] = {"dtype": dt, "shape": list(shape), "data_offsets": [pos, pos + data.size]}
+        pos += data.size
+    head = json.dumps(meta, separators=(",", ":")).encode()
+    head += b" " * (-(8 + len(head)) % 8)
+    out = np.empty(8 + len(head) + pos, dtype=np.uint8)
+    out[:8] = np.frombuffer(len(head).to_bytes(8, "little"), dtype=np.uint8)
+    out[8:8 + len(head)] = np.frombuffer(head, dtype=np.uint8)
+    p = 8 + len(head)
+    for _n, _d, _s, data in tensors:
+        out[p:p + data.size] = data
+        p += data.size
+    return out
+
+
+def llama_layer_shapes(hidden=4096, ffn=14336, kv=1024):
+    return [("self_attn.q_proj.weight", (hidden, hidden)), ("self_attn.k_proj.weight", (kv, hidden)),
+            ("self_attn.v_proj.weight", (kv, hidden)), ("self_attn.o_proj.weight", (hidden, hidden)),
+            ("mlp.gate_proj.weight", (ffn, hidden)), ("mlp.up_proj.weight", (ffn, hidden)),
+            ("mlp.down_proj.weight", (hidden, ffn)),
+            ("input_layernorm.weight", (hidden,)), ("post_attention_layernorm.weight", (hidden,))]
+
+
+def llama_shard(layers, seed: int, hidden=4096, ffn=14336, kv=1024, vocab=0,
+                embed=False, head=False, scale: float = 1.0) -> np.ndarray:
+    """One safetensors shard of a Llama-architecture model: the given layer
+    indices, optionally the embedding and the output head.  `scale` < 1 shrinks
+    every matrix dimension for CPU-sized test cases."""
+    h, f, k, v = (max(8, int(d * scale)) for d in (hidden, ffn, kv, max(vocab, 8)))
+    tensors, s = [], seed * 1000003
+    if embed:
+        tensors.append(("model.embed_tokens.weight", "BF16", (v, h), normal_bf16((v, h), s)))
+        s += 1
+    for li in layers:
+        for name, shape in llama_layer_shapes(h, f, k):
+            s += 1
+            if len(shape) == 1:
+                data = bf16_bytes(np.ones(shape, dtype=np.float32))
+            else:
+                data = normal_bf16(shape, s)
+            tensors.append((f"model.layers.{li}.{name}", "BF16", shape, data))
+    if head:
+        tensors.append(("model.norm.weight", "BF16", (h,), bf16_bytes(np.ones(h, np.float32))))
+        tensors.append(("lm_head.weight", "BF16", (v, h), normal_bf16((v, h), s + 7)))
+    return safetensors_bytes(tensors)
+
+
+def perturbed_bf16(prev: np.ndarray, seed: int, frac: float = 0.3, sigma: float = 1e-4):
+    """prev (bf16 bytes) plus N(0, sigma) noise on a random `frac` of elements."""
+    rng = np.random.default_rng(seed)
+    w = (prev.view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+    mask = rng.random(w.size) < frac
+    w = w + mask * rng.standard_normal(w.size, dtype=np.float32) * np.float32(sigma)
+    return bf16_bytes(w)
