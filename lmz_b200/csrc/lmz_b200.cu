@@ -1,0 +1,240 @@
+// C-ABI shared library: sm_100a decode of lmz rANS byte-plane streams.
+//
+// The first nine exports are the boundary the reference's Python binds
+// (lmz/gpu/lmzgpu.cu:341-527, ctypes signatures at lmz/gpu/__init__.py:130-148)
+// with the same names, argument meaning, return codes and error behaviour; the
+// rest are additive entry points for whole-archive decode.  Declarations and
+// the per-function contract live in include/lmz_b200.h.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/lmz_b200.h"
+#include "rans_kernel.cuh"
+#include "chunk_kernels.cuh"
+
+using namespace lmz;
+
+#define API extern "C" __attribute__((visibility("default")))
+
+static thread_local char g_err[256];
+
+static int fail_msg(int rc, const char *what)
+{
+    snprintf(g_err, sizeof g_err, "%s", what);
+    return rc;
+}
+
+static int fail_cuda(const char *what, cudaError_t e)
+{
+    snprintf(g_err, sizeof g_err, "%s: %s", what, cudaGetErrorString(e));
+    return LMZ_GPU_ECUDA;
+}
+
+#define CK(what, x)                                        \
+    do {                                                   \
+        cudaError_t e_ = (x);                              \
+        if (e_ != cudaSuccess) return fail_cuda(what, e_); \
+    } while (0)
+
+static int device_ready()
+{
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        return fail_msg(LMZ_GPU_ENODEV, "no CUDA device");
+    }
+    return LMZ_GPU_OK;
+}
+
+// Kernels ask for more dynamic shared memory than the default 48 KiB; the
+// opt-in is per device and is made once.
+template <class K>
+static int opt_in_smem(K kernel, uint32_t bytes, bool *done /* [64] by device */)
+{
+    int dev = 0;
+    CK("cudaGetDevice", cudaGetDevice(&dev));
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && done[dev]) return LMZ_GPU_OK;
+    CK("cudaFuncSetAttribute",
+       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (dev >= 0 && dev < 64) done[dev] = true;
+    return LMZ_GPU_OK;
+}
+
+constexpr int WARPS_NARROW = 4;
+constexpr int WARPS_WIDE = 8;
+
+static int launch_rans(const RansArgs &a, cudaStream_t cs)
+{
+    if (a.njobs == 0) return LMZ_GPU_OK;
+    if (a.shared_hdr) {
+        static bool done[64];
+        constexpr uint32_t shm = rans_smem_bytes<true>(WARPS_WIDE);
+        int rc = opt_in_smem(k_rans<true, WARPS_WIDE>, shm, done);
+        if (rc) return rc;
+        unsigned blocks = (a.njobs + WARPS_WIDE * 4 - 1) / (WARPS_WIDE * 4);
+        k_rans<true, WARPS_WIDE><<<blocks, WARPS_WIDE * 32, shm, cs>>>(a);
+    } else {
+        static bool done[64];
+        constexpr uint32_t shm = rans_smem_bytes<false>(WARPS_NARROW);
+        int rc = opt_in_smem(k_rans<false, WARPS_NARROW>, shm, done);
+        if (rc) return rc;
+        unsigned blocks = (a.njobs + WARPS_NARROW * 4 - 1) / (WARPS_NARROW * 4);
+        k_rans<false, WARPS_NARROW><<<blocks, WARPS_NARROW * 32, shm, cs>>>(a);
+    }
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch", le);
+    return LMZ_GPU_OK;
+}
+
+// ------------------------------------------------------- the reference's nine
+
+API int lmz_gpu_abi_version(void) { return 1; }
+API const char *lmz_gpu_last_error(void) { return g_err; }
+API int lmz_gpu_grain(void) { return 1; }
+API int lmz_gpu_header_bytes(void) { return (int)HDR_BYTES; }
+API int lmz_gpu_pad_bytes(void) { return (int)PAD_BYTES; }
+
+API int lmz_gpu_device_name(char *buf, int cap)
+{
+    int rc = device_ready();
+    if (rc) return rc;
+    int dev = 0;
+    CK("cudaGetDevice", cudaGetDevice(&dev));
+    cudaDeviceProp prop;
+    CK("cudaGetDeviceProperties", cudaGetDeviceProperties(&prop, dev));
+    snprintf(buf, (size_t)cap, "%s sm_%d%d %d SMs", prop.name, prop.major, prop.minor,
+             prop.multiProcessorCount);
+    return LMZ_GPU_OK;
+}
+
+API int lmz_gpu_validate(const void *streams_v, const void *off_v, unsigned nstr)
+{
+    const uint8_t *streams = (const uint8_t *)streams_v;
+    const uint64_t *off = (const uint64_t *)off_v;
+    for (unsigned i = 0; i < nstr; i++) {
+        if (off[2 * i + 1] < HDR_BYTES + STATE_BYTES)
+            return fail_msg(LMZ_GPU_EBADSTREAM, "a stream is shorter than its own header");
+        const uint8_t *p = streams + off[2 * i];
+        if (p[0] != 'R' || p[1] != '1')
+            return fail_msg(LMZ_GPU_EBADSTREAM, "a stream does not start with the rANS magic");
+        uint32_t sum = 0;
+        for (int s = 0; s < 256; s++) sum += (uint32_t)p[4 + 2 * s] | ((uint32_t)p[5 + 2 * s] << 8);
+        if (sum != PROB_SCALE)
+            return fail_msg(LMZ_GPU_EBADSTREAM, "a stream's frequencies do not sum to 4096");
+    }
+    return LMZ_GPU_OK;
+}
+
+API int lmz_gpu_decode_batch_dev(const void *d_hdr, const void *d_streams, const void *d_off,
+                                 unsigned nstr, unsigned plane, void *d_out, void *cuda_stream,
+                                 unsigned tpb)
+{
+    (void)tpb;  // block shape is fixed by the shared-memory layout
+    if (nstr == 0) return LMZ_GPU_OK;
+    if (plane == 0) return fail_msg(LMZ_GPU_EUNSUPPORTED, "plane is zero");
+    int rc = device_ready();
+    if (rc) return rc;
+    RansArgs a{};
+    a.src = (const uint8_t *)d_streams;
+    a.offs = (const uint64_t *)d_off;
+    a.plane = plane;
+    a.njobs = nstr;
+    a.dst = (uint8_t *)d_out;
+    a.shared_hdr = (const uint8_t *)d_hdr;
+    return launch_rans(a, (cudaStream_t)cuda_stream);
+}
+
+API int lmz_gpu_decode_batch(const void *hdr, const void *streams, size_t nbytes, const void *off,
+                             unsigned nstr, unsigned plane, void *out)
+{
+    if (nstr == 0) return LMZ_GPU_OK;
+    if (plane == 0) return fail_msg(LMZ_GPU_EUNSUPPORTED, "plane is zero");
+    int rc = device_ready();
+    if (rc) return rc;
+    const uint64_t *o = (const uint64_t *)off;
+    for (unsigned i = 0; i < nstr; i++)
+        if (o[2 * i] > nbytes || o[2 * i + 1] > nbytes - o[2 * i])
+            return fail_msg(LMZ_GPU_EBADSTREAM, "a stream lies outside the buffer");
+    if (hdr == NULL) {
+        rc = lmz_gpu_validate(streams, off, nstr);
+        if (rc) return rc;
+    }
+    size_t obytes = (size_t)nstr * plane;
+    uint8_t *d_streams = NULL, *d_out = NULL, *d_hdr = NULL;
+    uint64_t *d_off = NULL;
+    uint32_t *d_flag = NULL;
+    uint32_t flag = 0;
+    rc = LMZ_GPU_ECUDA;
+#define TRY(what, call)                                            \
+    do {                                                           \
+        cudaError_t e_ = (call);                                   \
+        if (e_ != cudaSuccess) { rc = fail_cuda(what, e_); goto done; } \
+    } while (0)
+    TRY("cudaMalloc(streams)", cudaMalloc(&d_streams, nbytes + PAD_BYTES));
+    TRY("cudaMalloc(offsets)", cudaMalloc(&d_off, (size_t)nstr * 16));
+    TRY("cudaMalloc(out)", cudaMalloc(&d_out, obytes));
+    TRY("cudaMalloc(flag)", cudaMalloc(&d_flag, 4));
+    if (hdr) TRY("cudaMalloc(table)", cudaMalloc(&d_hdr, HDR_BYTES));
+    TRY("H2D streams", cudaMemcpy(d_streams, streams, nbytes, cudaMemcpyHostToDevice));
+    TRY("memset pad", cudaMemset(d_streams + nbytes, 0, PAD_BYTES));
+    TRY("memset flag", cudaMemset(d_flag, 0, 4));
+    TRY("H2D offsets", cudaMemcpy(d_off, off, (size_t)nstr * 16, cudaMemcpyHostToDevice));
+    if (hdr) TRY("H2D table", cudaMemcpy(d_hdr, hdr, HDR_BYTES, cudaMemcpyHostToDevice));
+    {
+        RansArgs a{};
+        a.src = d_streams; a.offs = d_off; a.plane = plane; a.njobs = nstr;
+        a.dst = d_out; a.shared_hdr = d_hdr; a.any_bad = d_flag;
+        rc = launch_rans(a, 0);
+        if (rc) goto done;
+    }
+    rc = LMZ_GPU_ECUDA;
+    TRY("cudaDeviceSynchronize", cudaDeviceSynchronize());
+    TRY("D2H flag", cudaMemcpy(&flag, d_flag, 4, cudaMemcpyDeviceToHost));
+    if (flag) {
+        rc = fail_msg(LMZ_GPU_EBADSTREAM, "a stream is malformed or truncated");
+        goto done;
+    }
+    TRY("D2H out", cudaMemcpy(out, d_out, obytes, cudaMemcpyDeviceToHost));
+    rc = LMZ_GPU_OK;
+#undef TRY
+done:
+    if (d_streams) cudaFree(d_streams);
+    if (d_off) cudaFree(d_off);
+    if (d_out) cudaFree(d_out);
+    if (d_flag) cudaFree(d_flag);
+    if (d_hdr) cudaFree(d_hdr);
+    return rc;
+}
+
+// ------------------------------------------------------------------- additive
+
+API int lmz_gpu_set_device(int device)
+{
+    int rc = device_ready();
+    if (rc) return rc;
+    CK("cudaSetDevice", cudaSetDevice(device));
+    return LMZ_GPU_OK;
+}
+
+API int lmz_gpu_decode_streams_dev(const void *d_jobs, unsigned njobs, const void *d_src,
+                                   void *d_dst, const void *d_shared_hdr, void *d_status,
+                                   void *d_any_bad, void *cuda_stream)
+{
+    if (njobs == 0) return LMZ_GPU_OK;
+    int rc = device_ready();
+    if (rc) return rc;
+    RansArgs a{};
+    a.src = (const uint8_t *)d_src;
+    a.jobs = (const StreamJob *)d_jobs;
+    a.njobs = njobs;
+    a.dst = (uint8_t *)d_dst;
+    a.shared_hdr = (const uint8_t *)d_shared_hdr;
+    a.status = (uint32_t *)d_status;
+    a.any_bad = (uint32_t *)d_any_bad;
+    return launch_rans(a, (cudaStream_t)cuda_stream);
+}
+
+#include "chunk_abi.inl"
