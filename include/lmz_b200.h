@@ -98,6 +98,59 @@ int lmz_gpu_decode_streams_dev(const void *d_jobs, unsigned njobs, const void *d
                                void *d_dst, const void *d_shared_hdr, void *d_status,
                                void *d_any_bad, void *cuda_stream);
 
+/* ---- whole-archive decode ---------------------------------------------------
+ * The reference has no GPU counterpart for anything below: its chunk framing,
+ * plane merge, exponent conditioning, delta undo and checksum run on the CPU
+ * (lmz/codec.py:1075-1230, lmz/api.py:832-886).  These entry points run that
+ * work on the device from descriptors the host planner builds out of the
+ * archive's 32-byte chunk records (lmz/format.py:53-56). */
+
+/* sizeof of {stream job, chunk job, cond job, cond state}, so a host planner can
+ * check its mirrored layouts. */
+int lmz_gpu_struct_sizes(unsigned *out4);
+
+/* Output bytes one thread block finishes at a time (65536); chunks are cut into
+ * pieces of this size and checksummed piecewise. */
+int lmz_gpu_piece_bytes(void);
+
+/* Fill host_dst with the CRC-32 tables the finish kernel reads (upload them once
+ * per device).  Returns the size in bytes; if cap is too small nothing is written. */
+int lmz_gpu_crc_tables(void *host_dst, size_t cap);
+
+/* Everything lmz_gpu_decode_chunks_dev needs.  All pointers are device pointers.
+ * Layouts of the job arrays are those of csrc/common.cuh and csrc/chunk_kernels.cuh;
+ * lmz_b200/plan.py builds them. */
+typedef struct lmz_decode_plan {
+    const void *d_payload;      /* archive payload bytes, 16-byte aligned, pad_bytes() of slack */
+    void *d_scratch;            /* decoded planes and segments */
+    void *d_out;                /* the concatenated output space, 64 bytes of slack */
+    const void *d_stream_jobs;  /* rANS streams whose decoded size the host knows */
+    void *d_seg_jobs;           /* 8 per conditioned chunk, sized on the device */
+    void *d_stream_status;      /* uint32 per stream job */
+    void *d_seg_status;         /* uint32 per segment job */
+    const void *d_chunks;       /* chunk jobs, ordered: pass 1 cond, pass 1 plain, pass 2 cond, pass 2 plain */
+    const void *d_piece_chunk;  /* uint32 per piece: its chunk */
+    const void *d_cond_jobs;
+    void *d_cond_state;
+    const void *d_cond_pieces;  /* uint32 piece ids of conditioned chunks */
+    void *d_hist;               /* n_cond x 256 uint32 */
+    void *d_piece_cnt;          /* n_pieces x 8 uint32 */
+    void *d_piece_crc;          /* n_pieces uint32, or NULL to skip checksums */
+    const void *d_crc_tables;
+    void *d_chunk_status;       /* uint32 per chunk: 0 ok, 4 bad shape, 5 bad crc */
+    void *d_chunk_crc;          /* computed crc32 per chunk, or NULL */
+    void *d_any_bad;            /* uint32: bit 0 a stream failed, bit 1 a chunk failed */
+    uint32_t n_stream_jobs, n_seg_jobs, n_chunks, n_pieces, n_cond, n_cond_pieces;
+    uint32_t piece_split[5];    /* piece-id boundaries of the four chunk groups */
+    uint32_t reserved;
+} lmz_decode_plan;
+
+/* Decode every chunk of the plan into d_out: rANS streams, conditioned-chunk
+ * bookkeeping, then the fused merge / delta-XOR / CRC pass that writes the
+ * plaintext once.  Asynchronous on cuda_stream; the caller reads d_any_bad and
+ * the status arrays after synchronising. */
+int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *plan, void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

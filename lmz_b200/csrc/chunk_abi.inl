@@ -1,1 +1,150 @@
-// chunk ABI
+// Additive C-ABI entry points for whole-archive decode (included by lmz_b200.cu).
+
+#include "cond_kernels.cuh"
+
+static_assert(sizeof(lmz_stream_job) == sizeof(StreamJob), "public and device StreamJob differ");
+
+API int lmz_gpu_struct_sizes(unsigned *out4)
+{
+    out4[0] = (unsigned)sizeof(StreamJob);
+    out4[1] = (unsigned)sizeof(ChunkJob);
+    out4[2] = (unsigned)sizeof(CondJob);
+    out4[3] = (unsigned)sizeof(CondState);
+    return LMZ_GPU_OK;
+}
+
+API int lmz_gpu_piece_bytes(void) { return (int)PIECE_BYTES; }
+
+API int lmz_gpu_crc_tables(void *host_dst, size_t cap)
+{
+    if (cap < sizeof(CrcTables)) return (int)sizeof(CrcTables);
+    static CrcTables tabs;
+    static std::once_flag once;
+    std::call_once(once, [] { crc_build_tables(tabs); });
+    memcpy(host_dst, &tabs, sizeof tabs);
+    return (int)sizeof(CrcTables);
+}
+
+template <bool COND>
+static int launch_finish(const FinishArgs &fa, int sms, cudaStream_t cs)
+{
+    if (fa.piece_begin >= fa.piece_end) return LMZ_GPU_OK;
+    static bool done[64];
+    constexpr uint32_t shm = finish_smem(COND);
+    int rc = opt_in_smem(k_finish<COND>, shm, done);
+    if (rc) return rc;
+    unsigned per_sm = COND ? 2 : 8;
+    unsigned n = fa.piece_end - fa.piece_begin;
+    unsigned grid = n < (unsigned)sms * per_sm ? n : (unsigned)sms * per_sm;
+    k_finish<COND><<<grid, FINISH_THREADS, shm, cs>>>(fa);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch k_finish", le);
+    return LMZ_GPU_OK;
+}
+
+static int sm_count(int *out)
+{
+    static int cached[64];
+    int dev = 0;
+    CK("cudaGetDevice", cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && cached[dev]) { *out = cached[dev]; return LMZ_GPU_OK; }
+    int n = 0;
+    CK("cudaDeviceGetAttribute", cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    if (dev >= 0 && dev < 64) cached[dev] = n;
+    *out = n;
+    return LMZ_GPU_OK;
+}
+
+API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
+{
+    if (!p) return fail_msg(LMZ_GPU_EUNSUPPORTED, "no plan");
+    int rc = device_ready();
+    if (rc) return rc;
+    cudaStream_t cs = (cudaStream_t)cuda_stream;
+    int sms = 0;
+    rc = sm_count(&sms);
+    if (rc) return rc;
+
+    if (p->d_any_bad) CK("memset any_bad", cudaMemsetAsync(p->d_any_bad, 0, 4, cs));
+
+    // 1. every rANS stream whose length is known up front, into scratch
+    if (p->n_stream_jobs) {
+        RansArgs a{};
+        a.src = (const uint8_t *)p->d_payload;
+        a.jobs = (const StreamJob *)p->d_stream_jobs;
+        a.njobs = p->n_stream_jobs;
+        a.dst = (uint8_t *)p->d_scratch;
+        a.status = (uint32_t *)p->d_stream_status;
+        a.any_bad = (uint32_t *)p->d_any_bad;
+        rc = launch_rans(a, cs);
+        if (rc) return rc;
+    }
+
+    // 2. exponent-conditioned chunks: histogram -> bucket map -> segment decodes -> ranks
+    if (p->n_cond) {
+        CondArgs c{};
+        c.chunks = (const ChunkJob *)p->d_chunks;
+        c.piece_chunk = (const uint32_t *)p->d_piece_chunk;
+        c.cond_pieces = (const uint32_t *)p->d_cond_pieces;
+        c.ncond_pieces = p->n_cond_pieces;
+        c.cond_jobs = (const CondJob *)p->d_cond_jobs;
+        c.cond_state = (CondState *)p->d_cond_state;
+        c.ncond = p->n_cond;
+        c.hist = (uint32_t *)p->d_hist;
+        c.piece_cnt = (uint32_t *)p->d_piece_cnt;
+        c.seg_jobs = (StreamJob *)p->d_seg_jobs;
+        c.payload = (const uint8_t *)p->d_payload;
+        c.scratch = (const uint8_t *)p->d_scratch;
+        CK("memset hist", cudaMemsetAsync(p->d_hist, 0, (size_t)p->n_cond * 1024, cs));
+        k_cond_hist<<<p->n_cond_pieces, 256, 0, cs>>>(c);
+        k_cond_plan<<<(p->n_cond + 63) / 64, 64, 0, cs>>>(c);
+        RansArgs a{};
+        a.src = (const uint8_t *)p->d_payload;
+        a.jobs = (const StreamJob *)p->d_seg_jobs;
+        a.njobs = p->n_seg_jobs;
+        a.dst = (uint8_t *)p->d_scratch;
+        a.status = (uint32_t *)p->d_seg_status;
+        a.any_bad = (uint32_t *)p->d_any_bad;
+        rc = launch_rans(a, cs);
+        if (rc) return rc;
+        k_cond_count<<<p->n_cond_pieces, 256, 0, cs>>>(c);
+        cudaError_t le = cudaGetLastError();
+        if (le != cudaSuccess) return fail_cuda("launch cond kernels", le);
+    }
+
+    // 3. finish: pass 1 (plain chunks), then pass 2 (refs and deltas, which read pass 1's output)
+    FinishArgs f{};
+    f.chunks = (const ChunkJob *)p->d_chunks;
+    f.piece_chunk = (const uint32_t *)p->d_piece_chunk;
+    f.payload = (const uint8_t *)p->d_payload;
+    f.scratch = (const uint8_t *)p->d_scratch;
+    f.out = (uint8_t *)p->d_out;
+    f.piece_crc = (uint32_t *)p->d_piece_crc;
+    f.tabs = (const CrcTables *)p->d_crc_tables;
+    f.cond_jobs = (const CondJob *)p->d_cond_jobs;
+    f.cond_state = (const CondState *)p->d_cond_state;
+    f.piece_cnt = (const uint32_t *)p->d_piece_cnt;
+    for (int part = 0; part < 4; part++) {
+        f.piece_begin = p->piece_split[part];
+        f.piece_end = p->piece_split[part + 1];
+        rc = (part & 1) ? launch_finish<false>(f, sms, cs) : launch_finish<true>(f, sms, cs);
+        if (rc) return rc;
+    }
+
+    // 4. verdicts
+    if (p->n_chunks) {
+        CheckArgs k{};
+        k.chunks = (const ChunkJob *)p->d_chunks;
+        k.nchunks = p->n_chunks;
+        k.piece_crc = (const uint32_t *)p->d_piece_crc;
+        k.tabs = (const CrcTables *)p->d_crc_tables;
+        k.cond_state = (const CondState *)p->d_cond_state;
+        k.chunk_status = (uint32_t *)p->d_chunk_status;
+        k.chunk_crc = (uint32_t *)p->d_chunk_crc;
+        k.any_bad = (uint32_t *)p->d_any_bad;
+        k_crc_check<<<(p->n_chunks + 127) / 128, 128, 0, cs>>>(k);
+        cudaError_t le = cudaGetLastError();
+        if (le != cudaSuccess) return fail_cuda("launch k_crc_check", le);
+    }
+    return LMZ_GPU_OK;
+}

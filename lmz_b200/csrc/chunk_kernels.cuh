@@ -1,1 +1,349 @@
-// chunk kernels (filled in below)
+// Whole-chunk kernels: everything between "planes are decoded" and "the chunk's
+// plaintext sits at its destination, checksummed".
+//
+//   k_finish      merge planes (BF16 field merge, byte-plane interleave, copy),
+//                 exponent-conditioned un-partition, XOR with a delta base,
+//                 CRC-32 of the result; output written once, 16 bytes a thread
+//   k_cond_hist   256-bin histogram of a decoded exponent plane
+//   k_cond_plan   bucket map + bucket sizes from that histogram; sizes the
+//                 sign/mantissa segment decodes
+//   k_cond_count  per-piece bucket populations (ranks for the un-partition)
+//   k_crc_check   combine piece checksums per chunk and compare with the record
+//
+// Reference behaviour: lmz/codec.py:1149-1230 (decode_chunk), :1075-1146
+// (_decode_bf16c), :1045-1057 (decode_delta); lmz/native/lmzcore.c:439-447
+// (BF16 merge), :289-347 (plane interleave), :525-543 (bucket map), :614-641
+// (un-partition), :233-245 (xor).
+#pragma once
+#include "common.cuh"
+#include "crc.cuh"
+
+namespace lmz {
+
+constexpr uint64_t NONE64 = ~0ull;
+constexpr uint32_t PIECE_ELEMS = PIECE_BYTES / 2;   // BF16 elements per piece
+constexpr uint32_t COND_BUCKETS = 8;
+
+enum : uint8_t { K_COPY = 0, K_BF16 = 1, K_SPLIT = 2, K_COND = 3 };
+
+struct ChunkJob {
+    uint64_t dst_off;        // chunk start in the output
+    uint64_t base_off;       // delta source in the output, or NONE64
+    uint64_t plane_off[8];   // plane k: payload offset, or scratch offset when bit k of scratch_mask
+    uint32_t rlen;
+    uint32_t crc;            // expected crc32, 0 = not recorded
+    uint32_t piece0;         // first piece id of this chunk
+    uint32_t aux;            // K_COND: index of its CondJob
+    uint8_t kind, esize, scratch_mask, src_is_out;   // src_is_out: K_COPY reads the output (a ref)
+    uint32_t record;         // archive record this chunk came from
+};
+static_assert(sizeof(ChunkJob) == 104, "ChunkJob layout is shared with the host");
+
+struct CondJob {
+    uint64_t exp_off;        // exponent plane: scratch offset, or payload offset when stored
+    uint64_t seg_src[8];     // coded segment b in the payload
+    uint64_t seg_scratch;    // where decoded rANS segments go (scratch)
+    uint32_t seg_len[8];
+    uint32_t nelem;
+    uint32_t seg_job0;       // first of the chunk's 8 StreamJob slots
+    uint32_t piece0;
+    uint32_t chunk;
+    uint8_t seg_method[8];
+    uint8_t exp_in_scratch;
+    uint8_t pad_[7];
+};
+static_assert(sizeof(CondJob) == 144, "CondJob layout is shared with the host");
+
+struct CondState {           // written on the device
+    uint64_t seg_ptr[8];     // plain bytes of segment b (payload or scratch offset)
+    uint32_t counts[8];
+    uint8_t lut[256];
+    uint32_t seg_in_scratch;
+    uint32_t status;
+};
+static_assert(sizeof(CondState) == 360, "CondState layout");
+
+// ---- unaligned loads ---------------------------------------------------------
+// N little-endian words starting at any byte address, from aligned 32-bit loads.
+// Reads up to 3 bytes before and 4 after the range; buffers carry that slack.
+template <int N>
+__device__ __forceinline__ void load_words(const uint8_t *p, uint32_t (&w)[N])
+{
+    uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~uintptr_t(3));
+    uint32_t sh = (uint32_t)(a & 3u) * 8u;
+    uint32_t v[N + 1];
+#pragma unroll
+    for (int i = 0; i <= N; i++) v[i] = q[i];
+#pragma unroll
+    for (int i = 0; i < N; i++) w[i] = __funnelshift_r(v[i], v[i + 1], sh);
+}
+
+__device__ __forceinline__ uint32_t smem_word(const uint8_t *base, uint32_t byte_index)
+{
+    return *reinterpret_cast<const uint32_t *>(base + byte_index);
+}
+
+// BF16 field merge of two elements: a = exponent bytes, b = sign|mantissa bytes,
+// each holding element 0 in bits 0-7 and element 1 in bits 16-23.
+__device__ __forceinline__ uint32_t bf16_pair(uint32_t a, uint32_t b)
+{
+    return ((b & 0x00800080u) << 8) | (a << 7) | (b & 0x007f007fu);
+}
+
+__device__ __forceinline__ void bf16_merge8(const uint32_t (&a)[2], const uint32_t (&b)[2],
+                                            uint32_t (&w)[4])
+{
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        uint32_t a_lo = __byte_perm(a[h], 0, 0x4140), a_hi = __byte_perm(a[h], 0, 0x4342);
+        uint32_t b_lo = __byte_perm(b[h], 0, 0x4140), b_hi = __byte_perm(b[h], 0, 0x4342);
+        w[2 * h] = bf16_pair(a_lo, b_lo);
+        w[2 * h + 1] = bf16_pair(a_hi, b_hi);
+    }
+}
+
+// Padded shared-memory layout for per-thread runs of 128 bytes: 4 bytes of
+// padding per 128 keep a warp's accesses on distinct banks.
+__device__ __forceinline__ uint32_t pad128(uint32_t i) { return i + ((i >> 7) << 2); }
+constexpr uint32_t PADDED_PIECE = PIECE_ELEMS + (PIECE_ELEMS >> 7) * 4;
+
+struct FinishArgs {
+    const ChunkJob *chunks;
+    const uint32_t *piece_chunk;   // piece id -> chunk index
+    uint32_t piece_begin, piece_end;
+    const uint8_t *payload;
+    const uint8_t *scratch;
+    uint8_t *out;
+    uint32_t *piece_crc;           // R() of each piece, or NULL to skip checksums
+    const CrcTables *tabs;
+    const CondJob *cond_jobs;
+    const CondState *cond_state;
+    const uint32_t *piece_cnt;     // 8 bucket populations per piece (K_COND chunks)
+};
+
+constexpr uint32_t FINISH_THREADS = 256;
+// crc tables + reduction scratch [+ staged exponent and sign/mantissa pieces + bucket map]
+__host__ __device__ constexpr uint32_t finish_smem(bool cond)
+{
+    return 8192 + 2048 + (cond ? 2 * PADDED_PIECE + 256 : 0);
+}
+
+// COND selects the variant that can un-partition exponent-conditioned chunks;
+// the plain variant needs a tenth of the shared memory and runs at full occupancy.
+template <bool COND>
+__global__ void __launch_bounds__(FINISH_THREADS) k_finish(FinishArgs a)
+{
+    extern __shared__ __align__(16) uint8_t fsm[];
+    uint32_t (*sl)[256] = reinterpret_cast<uint32_t (*)[256]>(fsm);
+    uint32_t (*adv)[256] = reinterpret_cast<uint32_t (*)[256]>(fsm + 4096);
+    uint32_t *s_red = reinterpret_cast<uint32_t *>(fsm + 8192);    // 512 words of scratch
+    uint8_t *s_exp = fsm + 8192 + 2048;
+    uint8_t *s_sm = s_exp + PADDED_PIECE;
+    uint8_t *s_lut = s_sm + PADDED_PIECE;
+    const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const bool do_crc = a.piece_crc != nullptr;
+
+    if (do_crc) {
+        for (uint32_t i = t; i < 1024; i += FINISH_THREADS) {
+            (&sl[0][0])[i] = (&a.tabs->slice[0][0])[i];
+            (&adv[0][0])[i] = (&a.tabs->adv[0][0])[i];
+        }
+    }
+    __syncthreads();
+
+    for (uint32_t q = a.piece_begin + blockIdx.x; q < a.piece_end; q += gridDim.x) {
+        const ChunkJob &c = a.chunks[a.piece_chunk[q]];
+        const uint32_t pbase = (q - c.piece0) * PIECE_BYTES;          // chunk-relative
+        const uint32_t plen = min(PIECE_BYTES, c.rlen - pbase);
+        const uint8_t kind = c.kind, esize = c.esize;
+        uint8_t *dst = a.out + c.dst_off + pbase;
+        const uint8_t *base = c.base_off == NONE64 ? nullptr : a.out + c.base_off + pbase;
+        const uint32_t al = (uint32_t)(reinterpret_cast<uintptr_t>(a.out + c.dst_off) & 15u);
+
+        const uint8_t *pl[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+            pl[k] = (c.scratch_mask >> k & 1 ? a.scratch : a.payload) + c.plane_off[k];
+        if (kind == K_COPY && c.src_is_out) pl[0] = a.out + c.plane_off[0];
+
+        if (COND && kind == K_COND) {
+            // ---- stage the exponent piece and un-partition its sign/mantissa bytes
+            const CondJob &cj = a.cond_jobs[c.aux];
+            const CondState &cs = a.cond_state[c.aux];
+            const uint32_t e0 = pbase / 2, ne = plen / 2;
+            const uint8_t *exp = (cj.exp_in_scratch ? a.scratch : a.payload) + cj.exp_off + e0;
+            __syncthreads();
+            s_lut[t] = cs.lut[t];
+            for (uint32_t i = t * 4; i < PIECE_ELEMS; i += FINISH_THREADS * 4) {
+                uint32_t w[1] = {0};
+                if (i < ne) load_words<1>(exp + i, w);
+                *reinterpret_cast<uint32_t *>(s_exp + pad128(i)) = w[0];
+            }
+            // ranks of this piece's first element within each bucket
+            if (t < 8) s_red[256 + t] = 0;
+            __syncthreads();
+            {
+                const uint32_t p = q - c.piece0, b = t & 7;
+                uint32_t sum = 0;
+                for (uint32_t j = t >> 3; j < p; j += FINISH_THREADS / 8)
+                    sum += a.piece_cnt[(size_t)(c.piece0 + j) * 8 + b];
+                if (sum) atomicAdd(&s_red[256 + b], sum);
+            }
+            // phase A: per-thread bucket counts over its 128 elements, 16 bits each
+            const uint32_t my0 = t * 128;
+            uint64_t lo = 0, hi = 0;
+            for (uint32_t j = 0; j < 128; j += 4) {
+                uint32_t w = smem_word(s_exp, pad128(my0 + j));
+#pragma unroll
+                for (int z = 0; z < 4; z++) {
+                    if (my0 + j + z < ne) {
+                        uint32_t b = s_lut[(w >> (8 * z)) & 0xff];
+                        uint64_t one = 1ull << (16 * (b & 3));
+                        if (b & 4) hi += one; else lo += one;
+                    }
+                }
+            }
+            // phase B: exclusive scan of the packed counts over the 256 threads
+            uint64_t ilo = lo, ihi = hi;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                uint64_t vl = __shfl_up_sync(0xffffffffu, ilo, d);
+                uint64_t vh = __shfl_up_sync(0xffffffffu, ihi, d);
+                if (lane >= (uint32_t)d) { ilo += vl; ihi += vh; }
+            }
+            uint64_t *s_w = reinterpret_cast<uint64_t *>(s_red);     // 8 warps x 2
+            if (lane == 31) { s_w[warp * 2] = ilo; s_w[warp * 2 + 1] = ihi; }
+            __syncthreads();
+            uint64_t blo = 0, bhi = 0;
+            for (uint32_t wv = 0; wv < warp; wv++) { blo += s_w[wv * 2]; bhi += s_w[wv * 2 + 1]; }
+            uint64_t xlo = ilo - lo + blo, xhi = ihi - hi + bhi;   // exclusive, may reach 32768
+            // phase C: walk the run, gathering each element's byte from its segment
+            const uint8_t *segp[8];
+#pragma unroll
+            for (int b = 0; b < 8; b++)
+                segp[b] = (cs.seg_in_scratch >> b & 1 ? a.scratch : a.payload) + cs.seg_ptr[b] +
+                          s_red[256 + b];
+            for (uint32_t j = 0; j < 128; j += 4) {
+                uint32_t w = smem_word(s_exp, pad128(my0 + j)), o = 0;
+#pragma unroll
+                for (int z = 0; z < 4; z++) {
+                    if (my0 + j + z < ne) {
+                        uint32_t b = s_lut[(w >> (8 * z)) & 0xff];
+                        uint32_t sh = 16 * (b & 3);
+                        uint32_t idx;
+                        if (b & 4) { idx = (uint32_t)(xhi >> sh) & 0xffffu; xhi += 1ull << sh; }
+                        else { idx = (uint32_t)(xlo >> sh) & 0xffffu; xlo += 1ull << sh; }
+                        const uint8_t *sp = segp[0];
+#pragma unroll
+                        for (int bb = 1; bb < 8; bb++) sp = b == bb ? segp[bb] : sp;
+                        o |= (uint32_t)sp[idx] << (8 * z);
+                    }
+                }
+                *reinterpret_cast<uint32_t *>(s_sm + pad128(my0 + j)) = o;
+            }
+            __syncthreads();
+        }
+
+        // ---- rows: every thread produces 16 output bytes per row ----------------
+        uint32_t acc = 0;
+#pragma unroll 1
+        for (uint32_t row = 0; row < PIECE_BYTES / ROW_BYTES; row++) {
+            const uint32_t r = row * ROW_BYTES + t * 16;    // piece-relative
+            uint32_t w[4] = {0, 0, 0, 0};
+            if (r < plen) {
+                const uint32_t cr = pbase + r;              // chunk-relative
+                if (kind == K_COPY) {
+                    load_words<4>(pl[0] + cr, w);
+                } else if (kind == K_BF16) {
+                    uint32_t pa[2], pb[2];
+                    load_words<2>(pl[0] + cr / 2, pa);
+                    load_words<2>(pl[1] + cr / 2, pb);
+                    bf16_merge8(pa, pb, w);
+                } else if (COND && kind == K_COND) {
+                    uint32_t i = r / 2;
+                    uint32_t pa[2] = {smem_word(s_exp, pad128(i)), smem_word(s_exp, pad128(i + 4))};
+                    uint32_t pb[2] = {smem_word(s_sm, pad128(i)), smem_word(s_sm, pad128(i + 4))};
+                    bf16_merge8(pa, pb, w);
+                } else if (esize == 4) {
+                    uint32_t p0[1], p1[1], p2[1], p3[1];
+                    load_words<1>(pl[0] + cr / 4, p0);
+                    load_words<1>(pl[1] + cr / 4, p1);
+                    load_words<1>(pl[2] + cr / 4, p2);
+                    load_words<1>(pl[3] + cr / 4, p3);
+                    uint32_t t0 = __byte_perm(p0[0], p1[0], 0x5140), t1 = __byte_perm(p2[0], p3[0], 0x5140);
+                    uint32_t t2 = __byte_perm(p0[0], p1[0], 0x7362), t3 = __byte_perm(p2[0], p3[0], 0x7362);
+                    w[0] = __byte_perm(t0, t1, 0x5410); w[1] = __byte_perm(t0, t1, 0x7632);
+                    w[2] = __byte_perm(t2, t3, 0x5410); w[3] = __byte_perm(t2, t3, 0x7632);
+                } else if (esize == 2) {
+                    uint32_t p0[2], p1[2];
+                    load_words<2>(pl[0] + cr / 2, p0);
+                    load_words<2>(pl[1] + cr / 2, p1);
+                    w[0] = __byte_perm(p0[0], p1[0], 0x5140); w[1] = __byte_perm(p0[0], p1[0], 0x7362);
+                    w[2] = __byte_perm(p0[1], p1[1], 0x5140); w[3] = __byte_perm(p0[1], p1[1], 0x7362);
+                } else {   // esize 8: two elements, one byte from each of eight planes
+                    uint32_t e = cr / 8;
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        uint32_t b0 = pl[k][e], b1 = pl[k][e + 1];
+                        w[k >> 2] |= b0 << (8 * (k & 3));
+                        w[2 + (k >> 2)] |= b1 << (8 * (k & 3));
+                    }
+                }
+                if (base) {
+                    uint32_t bw[4];
+                    load_words<4>(base + r, bw);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) w[i] ^= bw[i];
+                }
+                const uint32_t left = plen - r;
+                if (left >= 16) {
+                    uint8_t *d = dst + r;
+                    if (al == 0) *reinterpret_cast<uint4 *>(d) = make_uint4(w[0], w[1], w[2], w[3]);
+                    else if ((al & 7) == 0) {
+                        reinterpret_cast<uint2 *>(d)[0] = make_uint2(w[0], w[1]);
+                        reinterpret_cast<uint2 *>(d)[1] = make_uint2(w[2], w[3]);
+                    } else if ((al & 3) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) reinterpret_cast<uint32_t *>(d)[i] = w[i];
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) d[i] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        if ((uint32_t)i < left) dst[r + i] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        uint32_t keep = left > 4u * i ? min(left - 4u * i, 4u) : 0u;
+                        w[i] = keep >= 4 ? w[i] : (keep ? w[i] & ((1u << (8 * keep)) - 1u) : 0u);
+                    }
+                }
+            }
+            if (do_crc) {
+                acc = crc_apply(adv, acc);
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc = crc_word(sl, acc, w[i]);
+            }
+        }
+        if (do_crc) {
+            uint32_t v = crc_mulmod(a.tabs->lane_mul[t], acc);
+#pragma unroll
+            for (int d = 16; d; d >>= 1) v ^= __shfl_xor_sync(0xffffffffu, v, d);
+            __syncthreads();
+            if (lane == 0) s_red[300 + warp] = v;
+            __syncthreads();
+            if (t == 0) {
+                uint32_t r = 0;
+                for (int i = 0; i < 8; i++) r ^= s_red[300 + i];
+                if (plen < PIECE_BYTES) r = crc_unshift(a.tabs->x2, r, PIECE_BYTES - plen);
+                a.piece_crc[q] = r;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace lmz

@@ -1,0 +1,191 @@
+// Support kernels for exponent-conditioned BF16 chunks (reference
+// lmz/codec.py:1116-1142) and the per-chunk checksum verdict.
+#pragma once
+#include "chunk_kernels.cuh"
+
+namespace lmz {
+
+struct CondArgs {
+    const ChunkJob *chunks;
+    const uint32_t *piece_chunk;
+    const uint32_t *cond_pieces;   // piece ids that belong to K_COND chunks
+    uint32_t ncond_pieces;
+    const CondJob *cond_jobs;
+    CondState *cond_state;
+    uint32_t ncond;
+    uint32_t *hist;                // ncond x 256, zeroed by the caller
+    uint32_t *piece_cnt;           // npieces x 8
+    StreamJob *seg_jobs;           // 8 slots per cond chunk, filled in by k_cond_plan
+    const uint8_t *payload;
+    const uint8_t *scratch;
+};
+
+__device__ __forceinline__ const uint8_t *cond_exp_piece(const CondArgs &a, uint32_t q,
+                                                         uint32_t &ci, uint32_t &ne)
+{
+    const ChunkJob &c = a.chunks[a.piece_chunk[q]];
+    ci = c.aux;
+    const CondJob &cj = a.cond_jobs[ci];
+    uint32_t e0 = (q - c.piece0) * PIECE_ELEMS;
+    ne = min(PIECE_ELEMS, cj.nelem - e0);
+    return (cj.exp_in_scratch ? a.scratch : a.payload) + cj.exp_off + e0;
+}
+
+// 256-bin histogram of one exponent piece (lmz/native/lmzcore.c:385-397),
+// accumulated per warp in shared memory, then added to the chunk's histogram.
+__global__ void __launch_bounds__(256) k_cond_hist(CondArgs a)
+{
+    __shared__ uint32_t h[8][256];
+    const uint32_t t = threadIdx.x, warp = t >> 5;
+    for (uint32_t i = t; i < 8 * 256; i += 256) (&h[0][0])[i] = 0;
+    __syncthreads();
+    uint32_t ci, ne;
+    const uint8_t *exp = cond_exp_piece(a, a.cond_pieces[blockIdx.x], ci, ne);
+    for (uint32_t i = t * 4; i < ne; i += 256 * 4) {
+        uint32_t w[1];
+        load_words<1>(exp + i, w);
+#pragma unroll
+        for (int z = 0; z < 4; z++)
+            if (i + z < ne) atomicAdd(&h[warp][(w[0] >> (8 * z)) & 0xff], 1u);
+    }
+    __syncthreads();
+    uint32_t s = 0;
+#pragma unroll
+    for (int w = 0; w < 8; w++) s += h[w][t];
+    if (s) atomicAdd(&a.hist[(size_t)ci * 256 + t], s);
+}
+
+// One thread per conditioned chunk: the bucket map (lmz/native/lmzcore.c:525-543,
+// same 64-bit products), the bucket sizes (lmz/kernels.py:481-486), the checks
+// of lmz/codec.py:1120-1142, and the sizes/destinations of the segment decodes.
+__global__ void k_cond_plan(CondArgs a)
+{
+    uint32_t ci = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ci >= a.ncond) return;
+    const CondJob &cj = a.cond_jobs[ci];
+    CondState &cs = a.cond_state[ci];
+    const uint32_t *hist = a.hist + (size_t)ci * 256;
+    uint64_t total = 0;
+    for (int s = 0; s < 256; s++) total += hist[s];
+    uint32_t counts[COND_BUCKETS] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint64_t acc = 0, b = 0;
+    for (int s = 0; s < 256; s++) {
+        cs.lut[s] = (uint8_t)b;
+        uint32_t hs = hist[s];
+        // counts[b] with a dynamic b would go to local memory; select instead
+#pragma unroll
+        for (int j = 0; j < COND_BUCKETS; j++) counts[j] += (b == (uint64_t)j) ? hs : 0u;
+        acc += hs;
+        while (b + 1 < COND_BUCKETS && acc * COND_BUCKETS >= (b + 1) * total) b++;
+    }
+    uint32_t status = total == cj.nelem ? ST_OK : ST_BAD_SHAPE;
+    uint64_t run = 0;
+    uint32_t in_scratch = 0;
+#pragma unroll
+    for (int j = 0; j < COND_BUCKETS; j++) {
+        uint32_t want = counts[j], ln = cj.seg_len[j], m = cj.seg_method[j];
+        cs.counts[j] = want;
+        StreamJob &sj = a.seg_jobs[cj.seg_job0 + j];
+        sj.n = 0;
+        if (want == 0) {
+            if (ln) status = ST_BAD_SHAPE;
+            cs.seg_ptr[j] = cj.seg_src[j];
+        } else if (m == 0) {
+            if (ln != want) status = ST_BAD_SHAPE;
+            cs.seg_ptr[j] = cj.seg_src[j];
+        } else if (m == 3) {
+            cs.seg_ptr[j] = cj.seg_scratch + run;
+            in_scratch |= 1u << j;
+            sj.dst_off = cj.seg_scratch + run;
+            sj.n = want;
+            run += want;
+        } else {
+            status = ST_BAD_SHAPE;
+            cs.seg_ptr[j] = cj.seg_src[j];
+        }
+    }
+    if (status != ST_OK)
+        for (int j = 0; j < COND_BUCKETS; j++) a.seg_jobs[cj.seg_job0 + j].n = 0;
+    cs.seg_in_scratch = in_scratch;
+    cs.status = status;
+}
+
+// Bucket populations of one exponent piece, for the stable un-partition's ranks.
+__global__ void __launch_bounds__(256) k_cond_count(CondArgs a)
+{
+    __shared__ uint32_t cnt[8][COND_BUCKETS];
+    __shared__ uint8_t lut[256];
+    const uint32_t t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const uint32_t q = a.cond_pieces[blockIdx.x];
+    uint32_t ci, ne;
+    const uint8_t *exp = cond_exp_piece(a, q, ci, ne);
+    lut[t] = a.cond_state[ci].lut[t];
+    __syncthreads();
+    uint32_t c[COND_BUCKETS] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (uint32_t i = t * 4; i < ne; i += 256 * 4) {
+        uint32_t w[1];
+        load_words<1>(exp + i, w);
+#pragma unroll
+        for (int z = 0; z < 4; z++) {
+            if (i + z < ne) {
+                uint32_t b = lut[(w[0] >> (8 * z)) & 0xff];
+#pragma unroll
+                for (int j = 0; j < COND_BUCKETS; j++) c[j] += b == (uint32_t)j;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < COND_BUCKETS; j++) {
+        uint32_t v = c[j];
+#pragma unroll
+        for (int d = 16; d; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+        if (lane == 0) cnt[warp][j] = v;
+    }
+    __syncthreads();
+    if (t < COND_BUCKETS) {
+        uint32_t s = 0;
+        for (int w = 0; w < 8; w++) s += cnt[w][t];
+        a.piece_cnt[(size_t)q * 8 + t] = s;
+    }
+}
+
+struct CheckArgs {
+    const ChunkJob *chunks;
+    uint32_t nchunks;
+    const uint32_t *piece_crc;
+    const CrcTables *tabs;
+    const CondState *cond_state;
+    uint32_t *chunk_status;        // one word per chunk
+    uint32_t *chunk_crc;           // computed crc32 per chunk (may be NULL)
+    uint32_t *any_bad;
+};
+
+// One thread per chunk: crc32 = shift(~0, rlen) ^ XOR_j shift(R_j, bytes after piece j) ^ ~0.
+__global__ void k_crc_check(CheckArgs a)
+{
+    uint32_t ci = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ci >= a.nchunks) return;
+    const ChunkJob &c = a.chunks[ci];
+    uint32_t status = ST_OK;
+    if (c.kind == K_COND) status = a.cond_state[c.aux].status;
+    if (a.piece_crc && (c.crc || a.chunk_crc)) {
+        const uint32_t *x2 = a.tabs->x2;
+        uint32_t np = (c.rlen + PIECE_BYTES - 1) / PIECE_BYTES;
+        uint32_t acc = crc_shift(x2, 0xffffffffu, c.rlen);
+        // Horner over the pieces: all but the last are PIECE_BYTES long.
+        uint32_t r = 0;
+        const uint32_t full = crc_xpow(x2, 8ull * PIECE_BYTES);
+        for (uint32_t j = 0; j < np; j++) {
+            uint32_t len = min(PIECE_BYTES, c.rlen - j * PIECE_BYTES);
+            r = (len == PIECE_BYTES ? crc_mulmod(full, r) : crc_shift(x2, r, len)) ^
+                a.piece_crc[c.piece0 + j];
+        }
+        uint32_t crc = acc ^ r ^ 0xffffffffu;
+        if (a.chunk_crc) a.chunk_crc[ci] = crc;
+        if (c.crc && crc != c.crc && status == ST_OK) status = ST_BAD_CRC;
+    }
+    a.chunk_status[ci] = status;
+    if (status != ST_OK && a.any_bad) atomicOr(a.any_bad, 2u);
+}
+
+}  // namespace lmz

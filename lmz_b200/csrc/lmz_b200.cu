@@ -12,6 +12,7 @@
 #include "../../include/lmz_b200.h"
 #include "rans_kernel.cuh"
 #include "chunk_kernels.cuh"
+#include "cond_kernels.cuh"
 
 using namespace lmz;
 

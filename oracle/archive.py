@@ -155,6 +155,9 @@ def parse_safetensors(a: np.ndarray):
     return (regions, tensors) if tensors else None
 
 
+KIND_REF = 2     # lmz/planner.py:146
+
+
 def _chunkify(regions, size: int, chunk_size: int, deltas):
     """(start, end, esize, kind, src) tasks covering [0, size)
     (lmz/planner.py:582-652; `deltas` = {(start, end): src} whole regions)."""
@@ -163,14 +166,18 @@ def _chunkify(regions, size: int, chunk_size: int, deltas):
     for s, e, es, kind in regions:
         if s > pos:
             covered.append([pos, s, 1, codec.KIND_BYTES, -1])
-        covered.append([s, e, es, kind, deltas.get((s, e), -1)])
+        src = deltas.get((s, e), -1)
+        if isinstance(src, tuple):          # an exact duplicate: a ref, not a delta
+            covered.append([s, e, es, KIND_REF, src[0]])
+        else:
+            covered.append([s, e, es, kind, src])
         pos = e
     if pos < size:
         covered.append([pos, size, 1, codec.KIND_BYTES, -1])
     merged = []
     for r in covered:
         p = merged[-1] if merged else None
-        if (p is not None and p[1] == r[0] and p[2] == r[2] and p[3] == r[3]
+        if (p is not None and p[1] == r[0] and (p[2] == r[2] or r[3] == KIND_REF) and p[3] == r[3]
                 and (p[4] >= 0) == (r[4] >= 0)
                 and (p[4] < 0 or p[4] + (p[1] - p[0]) == r[4])):
             p[1] = r[1]
@@ -182,7 +189,7 @@ def _chunkify(regions, size: int, chunk_size: int, deltas):
         p = s
         while p < e:
             stop = min(p + step, e)
-            if (stop - p) % es and stop == e:
+            if kind != KIND_REF and (stop - p) % es and stop == e:
                 out.append((p, stop, 1, codec.KIND_BYTES, -1))
             else:
                 out.append((p, stop, es, kind, src + (p - s) if src >= 0 else -1))
@@ -216,9 +223,13 @@ def write_archive(members, chunk_size: int | None = None, mapped: bool = False,
             for name, t in tensors.items():
                 t0 = first.get(name)
                 s, e = t["offsets"]
-                if (t0 and t0["dtype"] == t["dtype"] and t0["shape"] == t["shape"]
-                        and e - s >= (64 << 10)):
-                    deltas[(s, e)] = t0["offsets"][0]      # member 0 sits at dst 0
+                if not (t0 and t0["dtype"] == t["dtype"] and t0["shape"] == t["shape"]):
+                    continue
+                s0 = t0["offsets"][0]                      # member 0 sits at dst 0
+                if e > s and np.array_equal(a[s:e], datas[0][s0:s0 + (e - s)]):
+                    deltas[(s, e)] = (s0,)                 # dedup: lmz/api.py:748-753
+                elif e - s >= (64 << 10):
+                    deltas[(s, e)] = s0
         m = {"path": path, "size": int(a.size), "dst": base,
              "kind": "safetensors" if parsed else "raw", "mode": 0o644, "crc": 0}
         if tensors:
@@ -232,6 +243,8 @@ def write_archive(members, chunk_size: int | None = None, mapped: bool = False,
     def work(task):
         idx, mbase, s, e, es, kind, src = task
         data = datas[idx][s:e]
+        if kind == KIND_REF:
+            return mbase + s, e - s, [struct.pack("<Q", src)], codec.CODEC_REF, 1, 0, 0
         if src >= 0:
             parts, flags, crc = encode.encode_delta(data, datas[0][src:src + (e - s)], es,
                                                     kind, src, level, True, L)

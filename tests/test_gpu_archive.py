@@ -1,0 +1,141 @@
+"""Whole-archive decode on the GPU against the CPU oracle and the source bytes.
+
+Archives are written by the oracle's writer, which emits the reference
+encoder's exact chunk bytes (tests/test_oracle_vs_reference.py holds it to
+that), and by the reference itself for the committed golden archives."""
+import numpy as np
+import pytest
+
+from oracle import archive as oa, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _roundtrip(blob, source, checksum=True):
+    import zlib
+    from lmz_b200 import decode
+    dec = decode.ArchiveDecoder(blob, checksum=checksum)
+    dec.run()
+    dec.check()
+    got = dec.output.cpu().numpy()
+    want = oa.decode_archive(blob)
+    assert got.size == want.size == source.size
+    assert (want == source).all()
+    assert (got == want).all(), f"first difference at byte {int(np.nonzero(got != want)[0][0])}"
+    if checksum:
+        ar = dec.archive
+        crcs = dec.chunk_crcs()
+        for i, rec in enumerate(ar.records):
+            d, n = int(rec["dst"]), int(rec["rlen"])
+            assert int(crcs[i]) == (zlib.crc32(source[d:d + n]) & 0xFFFFFFFF), f"crc of chunk {i}"
+    return dec
+
+
+@pytest.fixture(scope="module")
+def shard():
+    return synth.llama_shard([0], 5, scale=0.25, vocab=4000, embed=True, head=True)
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(mapped=True), dict(chunk_size=1 << 20),
+                                dict(chunk_size=2 << 20), dict(chunk_size=(1 << 18) + 2)])
+def test_bf16_shard_layouts(shard, kw):
+    blob = oa.write_archive([("m.safetensors", shard)], **kw)
+    dec = _roundtrip(blob, shard)
+    if not kw:
+        assert (dec.archive.records["codec"] == 5).any(), "default chunking should condition"
+
+
+def test_without_checksums(shard):
+    blob = oa.write_archive([("m.safetensors", shard)], mapped=True)
+    _roundtrip(blob, shard, checksum=False)
+
+
+def _float_file(dtype, n, seed):
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal(n) * 0.02).astype(dtype)
+    name = {"float32": "F32", "float64": "F64", "float16": "F16"}[np.dtype(dtype).name]
+    return synth.safetensors_bytes([("w", name, (n,), w.view(np.uint8)),
+                                    ("tail", "U8", (13,), np.arange(13, dtype=np.uint8))])
+
+
+@pytest.mark.parametrize("dtype,n", [("float32", 1 << 20), ("float32", 70001), ("float64", 300001),
+                                     ("float16", 555555)])
+def test_byte_plane_splits(dtype, n):
+    src = _float_file(dtype, n, 3)
+    for kw in (dict(), dict(mapped=True)):
+        _roundtrip(oa.write_archive([("f.safetensors", src)], **kw), src)
+
+
+def test_delta_chain_and_refs():
+    c0 = synth.llama_shard([0, 1], 9, scale=0.25)
+    tensors = oa.parse_safetensors(c0)[1]
+    files = [c0]
+    for step in (1, 2):
+        c = files[-1].copy()
+        for i, (name, info) in enumerate(tensors.items()):
+            s, e = info["offsets"]
+            if i % 5 == 4:
+                continue                        # left identical: becomes a ref
+            if e - s > 100000:
+                c[s:e] = synth.perturbed_bf16(files[-1][s:e], 100 * step + i)
+        files.append(c)
+    members = [(f"ck/{i}.safetensors", f) for i, f in enumerate(files)]
+    for kw in (dict(), dict(chunk_size=1 << 20)):
+        blob = oa.write_archive(members, **kw)
+        dec = _roundtrip(blob, np.concatenate(files))
+        codecs = set(dec.archive.records["codec"].tolist())
+        assert {4, 8} <= codecs, codecs
+
+
+def test_tiny_and_odd_members():
+    rng = np.random.default_rng(0)
+    members = [("a.bin", rng.integers(0, 4, 100001, dtype=np.uint8)),      # one rANS-coded byte stream
+               ("b.bin", rng.integers(0, 256, 777, dtype=np.uint8)),       # stored
+               ("c.bin", np.zeros(1, dtype=np.uint8)),
+               ("d.txt", np.frombuffer(b"hello lmz " * 5000, dtype=np.uint8))]   # deflate on the host
+    blob = oa.write_archive(members)
+    _roundtrip(blob, np.concatenate([m[1] for m in members]))
+
+
+def test_corruption_is_reported(shard):
+    from lmz_b200 import decode
+    from lmz_b200.archive import CorruptArchive, FormatError
+    blob = bytearray(oa.write_archive([("m.safetensors", shard)], chunk_size=1 << 20))
+    ar = oa.Archive(bytes(blob))
+    rec = ar.records[3]
+    hit = bytearray(blob)
+    hit[int(rec["off"]) + int(rec["clen"]) - 100] ^= 0x5A          # inside a stored mantissa plane
+    dec = decode.ArchiveDecoder(bytes(hit))
+    dec.run()
+    with pytest.raises(CorruptArchive, match="checksum"):
+        dec.check()
+    hit = bytearray(blob)
+    hit[int(rec["off"]) + 8 + 600] ^= 0xFF                         # inside the exponent stream
+    dec = decode.ArchiveDecoder(bytes(hit))
+    dec.run()
+    with pytest.raises(CorruptArchive):
+        dec.check()
+    hit = bytearray(blob)
+    hit[int(rec["off"]) + 8] = ord("X")                            # the stream's magic
+    dec = decode.ArchiveDecoder(bytes(hit))
+    dec.run()
+    with pytest.raises(CorruptArchive):
+        dec.check()
+    with pytest.raises(FormatError):
+        decode.ArchiveDecoder(bytes(blob[:-1]))
+
+
+def test_tensor_views(shard):
+    import torch
+    from lmz_b200 import decode
+    blob = oa.write_archive([("m.safetensors", shard)], mapped=True)
+    dec = decode.ArchiveDecoder(blob)
+    dec.run()
+    dec.check()
+    ts = dec.tensors()
+    info = oa.parse_safetensors(shard)[1]
+    assert len(ts) == len(info)
+    for (path, name), t in ts.items():
+        s, e = info[name]["offsets"]
+        assert t.dtype == torch.bfloat16 and list(t.shape) == info[name]["shape"]
+        assert t.contiguous().view(torch.uint8).reshape(-1).cpu().numpy().tobytes() == shard[s:e].tobytes()
