@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark: decoded plaintext GB/s of an lmz archive of a Llama-3.1-8B-shaped
+BF16 model (random-init, seeded) on N B200s of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one decode of the whole archive (every chunk) into HBM.  `value` is
+measured with the compressed bytes already resident in HBM (CUDA events around
+exactly K steps, max over ranks); `e2e` includes, every step, the host->device
+copy of the archive from pinned memory and the device->host read of the
+per-chunk verdicts.  Each rank decodes its own full replica (weak scaling; no
+collective on the data path).  `--impl reference` times the reference's own
+CPU decoder (its C core compiled into oracle/_ref, driven by all host threads)
+on a bounded sample of the same archive.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODELS = {
+    # BASELINE configuration 3: 32 layers, hidden 4096, FFN 14336, 8 KV heads of 128, vocab 128256
+    "llama-3.1-8b": dict(layers=32, hidden=4096, ffn=14336, kv=1024, vocab=128256, shards=4),
+    "llama-tiny": dict(layers=2, hidden=1024, ffn=3584, kv=256, vocab=8000, shards=2),
+}
+METRIC = "decoded plaintext GB/s per B200 & per box (1/2/4/8 GPU), byte-exact vs CPU"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--model", default="llama-3.1-8b", choices=sorted(MODELS))
+    ap.add_argument("--layout", default="mapped", choices=("mapped", "default"),
+                    help="mapped = 64 KiB blocks (lmz compress --mapped); default = 8 MiB chunks")
+    ap.add_argument("--chunk-size", type=int, default=0, help="override the layout's chunk size")
+    ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--no-crc", action="store_true", help="skip the per-chunk crc32")
+    ap.add_argument("--no-cache", action="store_true")
+    ap.add_argument("--cpu-sample-mb", type=int, default=2048)
+    return ap.parse_args()
+
+
+def workload_name(a) -> str:
+    cs = a.chunk_size or ((64 << 10) if a.layout == "mapped" else (8 << 20))
+    return f"{a.model} bf16 N(0,0.02) seed {a.seed}, lmz archive, {cs >> 10} KiB chunks"
+
+
+def get_archive(a, rank: int, barrier) -> np.ndarray:
+    """The benchmark archive as a numpy byte array, generated once per box and
+    cached in /dev/shm (ranks other than 0 wait for rank 0)."""
+    cs = a.chunk_size or None
+    key = f"lmzb200-{a.model}-{a.layout}-{a.chunk_size}-{a.seed}.lmz"
+    cache = os.path.join("/dev/shm" if os.path.isdir("/dev/shm") else "/tmp", key)
+    if rank == 0 and (a.no_cache or not os.path.exists(cache)):
+        from oracle import bigwrite, synth
+        t = time.time()
+        blob, _ = bigwrite.write_model_archive(synth.llama_spec(**MODELS[a.model]), seed=a.seed,
+                                               chunk_size=cs, mapped=a.layout == "mapped")
+        tmp = cache + f".{os.getpid()}"
+        blob.tofile(tmp)
+        os.replace(tmp, cache)
+        print(f"[bench] wrote {cache}: {blob.size / 1e9:.2f} GB in {time.time() - t:.1f}s",
+              file=sys.stderr)
+    barrier()
+    return np.fromfile(cache, dtype=np.uint8)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], 0, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def cpu_decode_sample(blob, sample_mb: int, threads: int, lib_kind: str):
+    """Time the CPU decoder over the first `sample_mb` of plaintext chunks with
+    `threads` threads.  Returns (GB/s, description)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import archive as oa, codec, native
+    lib = native.ref() if lib_kind == "reference" else native.oracle()
+    if lib is None:
+        lib, lib_kind = native.oracle(), "port"
+    ar = oa.Archive(blob)
+    picks, total = [], 0
+    for i, c in enumerate(ar.records):
+        if c["codec"] in (codec.CODEC_REF, codec.CODEC_DELTA):
+            continue
+        picks.append(i)
+        total += int(c["rlen"])
+        if total >= sample_mb << 20:
+            break
+
+    def work(i):
+        c = ar.records[i]
+        codec.decode_chunk(ar.payload(c), int(c["codec"]), int(c["esize"]), int(c["flags"]),
+                           int(c["rlen"]), int(c["crc"]), True, lib)
+        return int(c["rlen"])
+
+    with ThreadPoolExecutor(threads) as ex:
+        list(ex.map(work, picks[:threads]))                       # warm the pool
+        t = time.perf_counter()
+        done = sum(ex.map(work, picks, chunksize=max(1, len(picks) // (threads * 8))))
+        dt = time.perf_counter() - t
+    what = (f"first {len(picks)} chunks ({done / 1e6:.0f} MB plaintext) of the same archive, "
+            f"decode + crc32, {threads} threads, C core = {lib_kind}")
+    return done / dt / 1e9, what, lib_kind
+
+
+def main():
+    a = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if a.impl == "reference":
+        return run_reference(a, rank)
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    from lmz_b200 import decode, gpu
+    ok, why = gpu.available()
+    if not ok:
+        raise SystemExit(f"the CUDA library is unavailable: {why}")
+    blob = get_archive(a, rank, barrier)
+    dec = decode.ArchiveDecoder(blob, checksum=not a.no_crc)
+    p = dec.plan
+    plain, coded = p.total, p.coded_bytes
+
+    # ---- warm-up + correctness gate ---------------------------------------------------
+    for _ in range(max(a.warmup, 3)):
+        dec.run()
+    dec.check()
+    verify_sample(dec, blob)
+    barrier()
+    torch.cuda.synchronize()
+
+    # ---- timed region: K whole-archive decodes, inputs resident -------------------------
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        e0.record()
+        for _ in range(a.steps):
+            dec.run()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    barrier()
+    dec.check()
+    t_all = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+    ms = float(t_all.item())
+    value = world * plain * a.steps / (ms / 1e3) / 1e9
+
+    # ---- per-phase device times (each phase launched alone, CUDA events) ---------------
+    phase_ms = {}
+    for name, mask in (("stream_decode", 1), ("cond", 2), ("finish", 4), ("verdict", 8)):
+        ts = []
+        for _ in range(3):
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record(); dec.run(phases=mask); s1.record()
+            torch.cuda.synchronize()
+            ts.append(s0.elapsed_time(s1))
+        phase_ms[name] = float(np.mean(ts[1:]))
+    dec.run()
+
+    # ---- end to end: pinned host archive -> device, decode, verdicts back ---------------
+    pinned = torch.empty(p.payload.size, dtype=torch.uint8).pin_memory()
+    pinned.numpy()[:] = p.payload
+    host_res = torch.empty(p.chunks.size + 1, dtype=torch.int32).pin_memory()
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        dec.upload(pinned, non_blocking=True)
+        dec.run()
+        host_res[:p.chunks.size].copy_(dec.d_chunk_crc[:p.chunks.size], non_blocking=True)
+        host_res[p.chunks.size:].copy_(dec.d_any_bad, non_blocking=True)
+        torch.cuda.synchronize()
+        if int(host_res[-1]) != 0:
+            raise SystemExit("end-to-end step reported a corrupt chunk")
+    e2e_s = time.perf_counter() - t0
+    t_all = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+    e2e_s = float(t_all.item())
+    e2e_value = world * plain * a.steps / e2e_s / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = measured_peak()
+    # dominant kernel: the one with the largest device time
+    stream_bytes = int(p.stream_jobs["src_len"].sum() + p.stream_jobs["n"].sum())
+    finish_bytes = int(coded - p.stream_jobs["src_len"].sum() + p.stream_jobs["n"].sum()
+                       + plain + p.base_bytes)
+    dom = max(("stream_decode", "finish"), key=lambda k: phase_ms[k])
+    dom_bytes = stream_bytes if dom == "stream_decode" else finish_bytes
+    achieved = dom_bytes / (phase_ms[dom] / 1e3) / 1e9
+    whole = (coded + plain + p.base_bytes) / (ms / a.steps / 1e3) / 1e9
+    cpu_v, cpu_what, cpu_kind = cpu_decode_sample(blob, a.cpu_sample_mb, os.cpu_count() or 1,
+                                                  "reference")
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+        "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": round(ms / a.steps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+        "data": "synthetic",
+        "config": {"workload": workload_name(a), "plaintext_bytes": plain, "coded_bytes": coded,
+                   "chunks": int(p.chunks.size), "rans_streams": int(p.stream_jobs.size + p.seg_jobs.size),
+                   "crc32": not a.no_crc, "per_gpu": "full replica",
+                   "l2": "inputs (10+ GB) and outputs (16 GB) far exceed the 126 MB L2"},
+        "clocks": clk.summary(),
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": int(p.payload.size), "d2h_bytes_per_step": int(host_res.numel() * 4)},
+        "gpu_launches": int(dec.launches_per_run * a.steps),
+        "roofline": {"bound": "hbm", "kernel": "k_rans" if dom == "stream_decode" else "k_finish",
+                     "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_kind,
+                     "algorithmic_bytes_per_launch": dom_bytes,
+                     "whole_decode": {"achieved": round(whole, 1), "frac": round(whole / peak, 4),
+                                      "bytes": coded + plain + p.base_bytes}},
+        "phase_ms": {k: round(v, 3) for k, v in phase_ms.items()},
+        "cpu_baseline": {"value": round(cpu_v, 3), "unit": "GB/s", "cores": os.cpu_count() or 1,
+                         "kind": cpu_kind, "sample": cpu_what},
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def verify_sample(dec, blob, nsample: int = 24):
+    """Byte-compare a spread of chunks against the CPU oracle, and every chunk's
+    device-computed crc32 against the archive's records."""
+    from oracle import archive as oa, codec
+    ar = oa.Archive(blob)
+    recs = ar.records
+    if dec.checksum:
+        crcs = dec.chunk_crcs()
+        have = recs["crc"] != 0
+        if not (crcs[have] == recs["crc"][have]).all():
+            raise SystemExit("device crc32 differs from the archive's records")
+    idx = np.unique(np.linspace(0, recs.size - 1, nsample).astype(np.int64))
+    out = dec.output
+    for i in idx:
+        c = recs[i]
+        if c["codec"] in (codec.CODEC_REF, codec.CODEC_DELTA):
+            continue
+        want = codec.decode_chunk(ar.payload(c), int(c["codec"]), int(c["esize"]), int(c["flags"]),
+                                  int(c["rlen"]), int(c["crc"]), True)
+        got = out[int(c["dst"]):int(c["dst"]) + int(c["rlen"])].cpu().numpy()
+        if not (got == want).all():
+            raise SystemExit(f"chunk {i} differs from the CPU oracle")
+
+
+def run_reference(a, rank: int):
+    """The reference's CPU decode of a bounded sample, all host threads, rank 0 only."""
+    if rank != 0:
+        return
+    blob = get_archive(a, 0, lambda: None)
+    threads = os.cpu_count() or 1
+    from oracle import archive as oa
+    ar = oa.Archive(blob)
+    vals = []
+    for i in range(a.warmup + a.steps):
+        v, what, kind = cpu_decode_sample(blob, a.cpu_sample_mb, threads, "reference")
+        if i >= a.warmup:
+            vals.append(v)
+    v = float(np.mean(vals))
+    sample_bytes = min(ar.total, a.cpu_sample_mb << 20)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(v, 3), "unit": "GB/s",
+        "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": round(sample_bytes / v / 1e6, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": workload_name(a), "plaintext_bytes": int(ar.total)},
+        "cpu_baseline": {"value": round(v, 3), "unit": "GB/s", "cores": threads, "kind": kind,
+                         "sample": what},
+        "e2e": {"value": round(v, 3), "unit": "GB/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -142,7 +142,8 @@ typedef struct lmz_decode_plan {
     void *d_any_bad;            /* uint32: bit 0 a stream failed, bit 1 a chunk failed */
     uint32_t n_stream_jobs, n_seg_jobs, n_chunks, n_pieces, n_cond, n_cond_pieces;
     uint32_t piece_split[5];    /* piece-id boundaries of the four chunk groups */
-    uint32_t reserved;
+    uint32_t phases;            /* 0 = everything; else bit 0 stream decode, bit 1 conditioned-chunk
+                                 * kernels, bit 2 finish, bit 3 verdicts (to time one phase alone) */
 } lmz_decode_plan;
 
 /* Decode every chunk of the plan into d_out: rANS streams, conditioned-chunk

@@ -65,10 +65,13 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     rc = sm_count(&sms);
     if (rc) return rc;
 
-    if (p->d_any_bad) CK("memset any_bad", cudaMemsetAsync(p->d_any_bad, 0, 4, cs));
+    // `phases` selects parts of the sequence (for timing one kernel alone); 0 runs it all.
+    const uint32_t ph = p->phases ? p->phases : 0xfu;
+
+    if (p->d_any_bad && (ph & 1u)) CK("memset any_bad", cudaMemsetAsync(p->d_any_bad, 0, 4, cs));
 
     // 1. every rANS stream whose length is known up front, into scratch
-    if (p->n_stream_jobs) {
+    if (p->n_stream_jobs && (ph & 1u)) {
         RansArgs a{};
         a.src = (const uint8_t *)p->d_payload;
         a.jobs = (const StreamJob *)p->d_stream_jobs;
@@ -81,7 +84,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     }
 
     // 2. exponent-conditioned chunks: histogram -> bucket map -> segment decodes -> ranks
-    if (p->n_cond) {
+    if (p->n_cond && (ph & 2u)) {
         CondArgs c{};
         c.chunks = (const ChunkJob *)p->d_chunks;
         c.piece_chunk = (const uint32_t *)p->d_piece_chunk;
@@ -124,7 +127,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     f.cond_jobs = (const CondJob *)p->d_cond_jobs;
     f.cond_state = (const CondState *)p->d_cond_state;
     f.piece_cnt = (const uint32_t *)p->d_piece_cnt;
-    for (int part = 0; part < 4; part++) {
+    for (int part = 0; part < 4 && (ph & 4u); part++) {
         f.piece_begin = p->piece_split[part];
         f.piece_end = p->piece_split[part + 1];
         rc = (part & 1) ? launch_finish<false>(f, sms, cs) : launch_finish<true>(f, sms, cs);
@@ -132,7 +135,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     }
 
     // 4. verdicts
-    if (p->n_chunks) {
+    if (p->n_chunks && (ph & 8u)) {
         CheckArgs k{};
         k.chunks = (const ChunkJob *)p->d_chunks;
         k.nchunks = p->n_chunks;

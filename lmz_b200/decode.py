@@ -130,9 +130,12 @@ class ArchiveDecoder:
         src = pinned if pinned is not None else torch.from_numpy(self.plan.payload)
         self.d_payload[:self.plan.payload.size].copy_(src, non_blocking=non_blocking)
 
-    def run(self, stream=None):
-        """Launch the decode on `stream` (default: torch's current). Asynchronous."""
+    def run(self, stream=None, phases: int = 0):
+        """Launch the decode on `stream` (default: torch's current). Asynchronous.
+        `phases` restricts the launch sequence (bit 0 stream decode, 1 conditioned-chunk
+        kernels, 2 finish, 3 verdicts) so one phase can be timed alone; 0 runs all."""
         import torch
+        self._c.phases = phases
         with torch.cuda.device(self.device):
             s = stream if stream is not None else torch.cuda.current_stream(self.device)
             rc = self.lib.lmz_gpu_decode_chunks_dev(ctypes.byref(self._c), s.cuda_stream)

@@ -82,3 +82,106 @@ def perturbed_bf16(prev: np.ndarray, seed: int, frac: float = 0.3, sigma: float 
     mask = rng.random(w.size) < frac
     w = w + mask * rng.standard_normal(w.size, dtype=np.float32) * np.float32(sigma)
     return bf16_bytes(w)
+
+
+# ---------------------------------------------------------------- whole models
+# A model is described as shards of (name, dtype string, shape) tensors.  Bytes
+# are generated per 8 MiB block of a shard's data area from a seed, so any
+# process can produce any block without the rest of the model in memory; 1-D
+# "norm" tensors are then overwritten with 1.0.
+
+BLOCK = 8 << 20
+
+
+def llama_spec(layers=32, hidden=4096, ffn=14336, kv=1024, vocab=128256, shards=4):
+    """Llama-architecture tensor list (BF16, untied embeddings) cut into `shards`
+    safetensors files by layer range."""
+    per = -(-layers // shards)
+    out = []
+    for s in range(shards):
+        t = []
+        if s == 0:
+            t.append(("model.embed_tokens.weight", "BF16", (vocab, hidden)))
+        for li in range(s * per, min(layers, (s + 1) * per)):
+            for name, shape in llama_layer_shapes(hidden, ffn, kv):
+                t.append((f"model.layers.{li}.{name}", "BF16", shape))
+        if s == shards - 1:
+            t.append(("model.norm.weight", "BF16", (hidden,)))
+            t.append(("lm_head.weight", "BF16", (vocab, hidden)))
+        out.append(t)
+    return out
+
+
+_ESZ = {"BF16": 2, "F32": 4}
+
+
+class ShardLayout:
+    """Byte layout of one synthetic safetensors shard."""
+
+    def __init__(self, tensors, seed: int, sigma: float = 0.02):
+        self.seed, self.sigma = seed, sigma
+        meta, pos, self.norms = {}, 0, []
+        for name, dt, shape in tensors:
+            n = int(np.prod(shape)) * _ESZ[dt]
+            meta[name] = {"dtype": dt, "shape": list(shape), "data_offsets": [pos, pos + n]}
+            if len(shape) == 1:
+                self.norms.append((pos, pos + n, dt))
+            pos += n
+        self.dtype = tensors[0][1]
+        head = json.dumps(meta, separators=(",", ":")).encode()
+        head += b" " * (-(8 + len(head)) % 8)
+        self.header = len(head).to_bytes(8, "little") + head
+        self.data_start = len(self.header)
+        self.data_size = pos
+        self.size = self.data_start + pos
+        self.tensors = {k: {"dtype": v["dtype"], "shape": v["shape"],
+                            "offsets": [self.data_start + v["data_offsets"][0],
+                                        self.data_start + v["data_offsets"][1]]}
+                        for k, v in meta.items()}
+
+    def _block(self, b: int, n: int) -> np.ndarray:
+        cache = self.__dict__.setdefault("_cache", {})
+        blk = cache.get(b)
+        if blk is None:
+            rng = np.random.default_rng((self.seed, b))
+            if self.dtype == "BF16":
+                blk = bf16_bytes(rng.standard_normal(n // 2, dtype=np.float32) * np.float32(self.sigma))
+            else:
+                blk = (rng.standard_normal(n // 4, dtype=np.float32)
+                       * np.float32(self.sigma)).view(np.uint8)
+            if len(cache) >= 2:
+                cache.pop(next(iter(cache)))
+            cache[b] = blk
+        return blk
+
+    def data(self, lo: int, hi: int) -> np.ndarray:
+        """Bytes [lo, hi) of the data area."""
+        out = np.empty(hi - lo, dtype=np.uint8)
+        for b in range(lo // BLOCK, (hi - 1) // BLOCK + 1):
+            b0 = b * BLOCK
+            n = min(BLOCK, self.data_size - b0)
+            blk = self._block(b, n)
+            a, z = max(lo, b0), min(hi, b0 + n)
+            out[a - lo:z - lo] = blk[a - b0:z - b0]
+        one = {"BF16": np.frombuffer(b"\x80\x3f", dtype=np.uint8),
+               "F32": np.frombuffer(b"\x00\x00\x80\x3f", dtype=np.uint8)}
+        for s, e, dt in self.norms:
+            a, z = max(lo, s), min(hi, e)
+            if a < z:
+                w = one[dt]
+                full = np.tile(w, (e - s) // w.size)
+                out[a - lo:z - lo] = full[a - s:z - s]
+        return out
+
+    def bytes(self, lo: int = 0, hi: int | None = None) -> np.ndarray:
+        """Bytes [lo, hi) of the whole file (header included)."""
+        hi = self.size if hi is None else hi
+        out = np.empty(hi - lo, dtype=np.uint8)
+        hdr = np.frombuffer(self.header, dtype=np.uint8)
+        if lo < self.data_start:
+            z = min(hi, self.data_start)
+            out[:z - lo] = hdr[lo:z]
+        if hi > self.data_start:
+            a = max(lo, self.data_start)
+            out[a - lo:] = self.data(a - self.data_start, hi - self.data_start)
+        return out
