@@ -139,3 +139,32 @@ def test_tensor_views(shard):
         s, e = info[name]["offsets"]
         assert t.dtype == torch.bfloat16 and list(t.shape) == info[name]["shape"]
         assert t.contiguous().view(torch.uint8).reshape(-1).cpu().numpy().tobytes() == shard[s:e].tobytes()
+
+
+def test_reference_written_archives_decode_to_the_reference_plaintext():
+    """The committed archives were written by the reference's own `lmz compress`;
+    the recorded digest is of what its `decompress` restored."""
+    import hashlib
+    import json
+    import os
+    from lmz_b200 import decode
+    gold = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    with open(os.path.join(gold, "manifest.json")) as f:
+        man = json.load(f)
+    for name, info in man.items():
+        blob = np.fromfile(os.path.join(gold, name + ".lmz"), dtype=np.uint8)
+        out = decode.decode_archive(blob).cpu().numpy()
+        assert out.size == info["plain_bytes"], name
+        assert hashlib.sha256(out.tobytes()).hexdigest() == info["plain_sha256"], name
+
+
+def test_reference_written_streams_decode(gpu):
+    import os
+    from helpers import pack_streams
+    gold = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    v = np.load(os.path.join(gold, "rans_vectors.npz"))
+    for case in sorted(k[:-6] for k in v.files if k.endswith("_plain")):
+        plain, stream = v[case + "_plain"], v[case + "_stream"]
+        blob, offs = pack_streams([stream.tobytes()] * 3)
+        out = gpu.decode_batch(blob, offs, 3, plain.size)
+        assert bytes(out) == plain.tobytes() * 3, case
