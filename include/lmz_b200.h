@@ -79,6 +79,12 @@ int lmz_gpu_decode_batch(const void *hdr, const void *streams, size_t nbytes, co
  * current for this thread.  All other calls act on the current device. */
 int lmz_gpu_set_device(int device);
 
+/* No counterpart in the reference: choose the per-stream decode-table layout for
+ * streams that carry their own table.  -1 = by batch size (default), 0 = narrow
+ * (5 KiB per stream, shortest lookup), 2 = compact (2 KiB, twice the streams per
+ * SM).  A tuning and testing knob; results are identical. */
+int lmz_gpu_set_table_mode(int mode);
+
 /* One stream to decode; mirrors struct lmz::StreamJob.  32 bytes. */
 typedef struct lmz_stream_job {
     uint64_t src_off; /* stream start, bytes from d_src */

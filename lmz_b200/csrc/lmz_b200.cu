@@ -64,30 +64,38 @@ static int opt_in_smem(K kernel, uint32_t bytes, bool *done /* [64] by device */
     return LMZ_GPU_OK;
 }
 
-constexpr int WARPS_NARROW = 4;
+constexpr int WARPS_NARROW = 4;    // 2 CTAs/SM: 32 streams resident
 constexpr int WARPS_WIDE = 8;
+constexpr int WARPS_COMPACT = 8;   // 2 CTAs/SM: 64 streams resident
+// Batches at least this large are occupancy-bound and take the compact tables;
+// smaller ones are latency-bound per stream and keep the shorter narrow lookup.
+constexpr unsigned COMPACT_MIN_JOBS = 148 * 32 * 2;
+
+template <int MODE, int WARPS>
+static int launch_rans_mode(const RansArgs &a, cudaStream_t cs)
+{
+    static bool done[64];
+    constexpr uint32_t shm = rans_smem_bytes<MODE>(WARPS);
+    int rc = opt_in_smem(k_rans<MODE, WARPS>, shm, done);
+    if (rc) return rc;
+    unsigned blocks = (a.njobs + WARPS * 4 - 1) / (WARPS * 4);
+    k_rans<MODE, WARPS><<<blocks, WARPS * 32, shm, cs>>>(a);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch k_rans", le);
+    return LMZ_GPU_OK;
+}
+
+// `force_mode` < 0 picks by batch size.
+static int g_force_table_mode = -1;
 
 static int launch_rans(const RansArgs &a, cudaStream_t cs)
 {
     if (a.njobs == 0) return LMZ_GPU_OK;
-    if (a.shared_hdr) {
-        static bool done[64];
-        constexpr uint32_t shm = rans_smem_bytes<true>(WARPS_WIDE);
-        int rc = opt_in_smem(k_rans<true, WARPS_WIDE>, shm, done);
-        if (rc) return rc;
-        unsigned blocks = (a.njobs + WARPS_WIDE * 4 - 1) / (WARPS_WIDE * 4);
-        k_rans<true, WARPS_WIDE><<<blocks, WARPS_WIDE * 32, shm, cs>>>(a);
-    } else {
-        static bool done[64];
-        constexpr uint32_t shm = rans_smem_bytes<false>(WARPS_NARROW);
-        int rc = opt_in_smem(k_rans<false, WARPS_NARROW>, shm, done);
-        if (rc) return rc;
-        unsigned blocks = (a.njobs + WARPS_NARROW * 4 - 1) / (WARPS_NARROW * 4);
-        k_rans<false, WARPS_NARROW><<<blocks, WARPS_NARROW * 32, shm, cs>>>(a);
-    }
-    cudaError_t le = cudaGetLastError();
-    if (le != cudaSuccess) return fail_cuda("launch", le);
-    return LMZ_GPU_OK;
+    if (a.shared_hdr) return launch_rans_mode<T_WIDE, WARPS_WIDE>(a, cs);
+    int mode = g_force_table_mode >= 0 ? g_force_table_mode
+                                       : (a.njobs >= COMPACT_MIN_JOBS ? T_COMPACT : T_NARROW);
+    if (mode == T_COMPACT) return launch_rans_mode<T_COMPACT, WARPS_COMPACT>(a, cs);
+    return launch_rans_mode<T_NARROW, WARPS_NARROW>(a, cs);
 }
 
 // ------------------------------------------------------- the reference's nine
@@ -211,6 +219,14 @@ done:
 }
 
 // ------------------------------------------------------------------- additive
+
+API int lmz_gpu_set_table_mode(int mode)
+{
+    if (mode != -1 && mode != T_NARROW && mode != T_COMPACT)
+        return fail_msg(LMZ_GPU_EUNSUPPORTED, "table mode must be -1 (auto), 0 (narrow) or 2 (compact)");
+    g_force_table_mode = mode;
+    return LMZ_GPU_OK;
+}
 
 API int lmz_gpu_set_device(int device)
 {

@@ -14,14 +14,27 @@
 
 namespace lmz {
 
-// Decode tables in shared memory.
-//   narrow (per-stream tables): slot -> symbol (4096 x u8) and
-//                               symbol -> (freq-1) << 12 | start (256 x u32)
-//   wide   (one table per CTA): slot -> (freq-1) << 20 | start << 8 | symbol
+// Decode tables in shared memory, three layouts:
+//   T_NARROW  per stream, 5 KiB: slot -> symbol (4096 x u8), then
+//             symbol -> (freq-1) << 12 | start (256 x u32).  Two dependent loads.
+//   T_WIDE    one per CTA, 16 KiB: slot -> (freq-1) << 20 | start << 8 | symbol.
+//             One dependent load; only affordable when the whole CTA shares a table.
+//   T_COMPACT per stream, 2 KiB: level 1 has one word per 16 slots holding the
+//             index of the live symbol covering the bucket's first slot (bits 0-7)
+//             and a bit per in-bucket position where another live symbol starts
+//             (bits 8+t); a popcount of the bits at or below the slot's position
+//             gives the live-symbol index exactly, and level 2 holds one wide-style
+//             entry per live symbol.  Two dependent loads and a popcount, at 40 %
+//             of the narrow layout's footprint, so 2.4x as many streams fit an SM.
 // Frequency is stored minus one because a single-symbol stream has f = 4096.
-struct NarrowTab {
-    uint8_t *sym;
-    uint32_t *sf;
+enum : int { T_NARROW = 0, T_WIDE = 1, T_COMPACT = 2 };
+
+struct Tables {
+    uint8_t *sym;        // T_NARROW
+    uint32_t *sf;        // T_NARROW
+    uint32_t *wide;      // T_WIDE
+    uint32_t *l1;        // T_COMPACT: 256 words
+    uint32_t *cf;        // T_COMPACT: up to 256 words
 };
 
 // Per-group streaming state.  Cursor and counters are bytes/slots measured
@@ -75,52 +88,72 @@ struct Ring {
 // this; returns false (on all lanes) if the frequencies do not sum to 4096.
 // Lane j owns symbols 8j..8j+7.  Rare symbols are written by their owner,
 // common ones (f >= 64) by the whole warp so the fill stays balanced.
-template <bool WIDE, class FreqOf>
-__device__ __forceinline__ bool build_table(FreqOf freq_of, uint8_t *sym_tab, uint32_t *sf_tab,
-                                            uint32_t *wide_tab, uint32_t lane)
+template <int MODE, class FreqOf>
+__device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, uint32_t lane)
 {
-    uint32_t f[8], tot = 0;
+    uint32_t f[8], tot = 0, nlive = 0;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         f[i] = freq_of(lane * 8 + i);
         tot += f[i];
+        nlive += f[i] != 0;
     }
-    uint32_t incl = tot;
+    // one scan carries both prefix sums: frequencies (<= 4096 each lane once
+    // sane) in the low half, live-symbol counts in the high half
+    uint32_t both = (tot & 0xffffu) | (nlive << 16), incl = both;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
         uint32_t v = __shfl_up_sync(0xffffffffu, incl, d);
         if (lane >= (uint32_t)d) incl += v;
     }
-    uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-    // A frequency above the scale would index past the tables; the sum test
-    // below rejects the stream, but the fill must not run first.
-    bool sane = __all_sync(0xffffffffu, tot <= PROB_SCALE) && total == PROB_SCALE;
-    if (!sane) return false;
-    uint32_t start = incl - tot;
+    // A frequency above the scale would index past the tables, and a lane total
+    // above 16 bits would corrupt the packed scan: reject before any fill.
+    bool lane_ok = tot <= PROB_SCALE;
+    uint32_t total = __shfl_sync(0xffffffffu, incl, 31) & 0xffffu;
+    uint32_t lanes_sum = __reduce_add_sync(0xffffffffu, lane_ok ? tot : PROB_SCALE + 1);
+    if (!__all_sync(0xffffffffu, lane_ok) || lanes_sum != PROB_SCALE || total != PROB_SCALE)
+        return false;
+    uint32_t start = (incl - both) & 0xffffu, live = (incl - both) >> 16;
+    if (MODE == T_COMPACT) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) tb.l1[lane * 8 + i] = 0;
+        __syncwarp();
+    }
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        uint32_t s = lane * 8 + i, fi = f[i], st = start;
+        uint32_t s = lane * 8 + i, fi = f[i], st = start, li = live;
         start += fi;
-        uint32_t packed_w = ((fi ? fi - 1 : 0) << 20) | (st << 8) | s;
-        if (!WIDE) sf_tab[s] = ((fi ? fi - 1 : 0) << 12) | st;
-        bool big = fi >= 64;
+        live += fi != 0;
+        uint32_t packed = ((fi ? fi - 1 : 0) << 20) | (st << 8) | s;
+        if (MODE == T_NARROW) tb.sf[s] = ((fi ? fi - 1 : 0) << 12) | st;
+        if (MODE == T_COMPACT && fi) {
+            tb.cf[li] = packed;
+            if (st & 15u) atomicOr(&tb.l1[st >> 4], 1u << (8 + (st & 15u)));
+        }
+        // work items of this symbol: slots (narrow/wide) or covered bucket heads (compact)
+        uint32_t lo = MODE == T_COMPACT ? (st + 15) >> 4 : st;
+        uint32_t cnt = MODE == T_COMPACT ? (fi ? ((st + fi - 1) >> 4) + 1 - lo : 0) : fi;
+        if (MODE == T_COMPACT && fi && ((st + fi - 1) >> 4) + 1 < lo) cnt = 0;
+        bool big = cnt >= 64;
         if (!big) {
-            for (uint32_t t = 0; t < fi; t++) {
-                if (WIDE) wide_tab[st + t] = packed_w;
-                else sym_tab[st + t] = (uint8_t)s;
+            for (uint32_t t = 0; t < cnt; t++) {
+                if (MODE == T_WIDE) tb.wide[lo + t] = packed;
+                else if (MODE == T_NARROW) tb.sym[lo + t] = (uint8_t)s;
+                else atomicOr(&tb.l1[lo + t], li);
             }
         }
         uint32_t m = __ballot_sync(0xffffffffu, big);
         while (m) {
             int src = __ffs(m) - 1;
             m &= m - 1;
-            uint32_t bf = __shfl_sync(0xffffffffu, fi, src);
-            uint32_t bs = __shfl_sync(0xffffffffu, st, src);
-            uint32_t bsym = (uint32_t)src * 8 + i;
-            uint32_t bw = ((bf - 1) << 20) | (bs << 8) | bsym;
-            for (uint32_t t = lane; t < bf; t += 32) {
-                if (WIDE) wide_tab[bs + t] = bw;
-                else sym_tab[bs + t] = (uint8_t)bsym;
+            uint32_t bc = __shfl_sync(0xffffffffu, cnt, src);
+            uint32_t bl = __shfl_sync(0xffffffffu, lo, src);
+            uint32_t bp = __shfl_sync(0xffffffffu, packed, src);
+            uint32_t bi = __shfl_sync(0xffffffffu, li, src);
+            for (uint32_t t = lane; t < bc; t += 32) {
+                if (MODE == T_WIDE) tb.wide[bl + t] = bp;
+                else if (MODE == T_NARROW) tb.sym[bl + t] = (uint8_t)bp;
+                else atomicOr(&tb.l1[bl + t], bi);
             }
         }
     }
@@ -130,21 +163,28 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, uint8_t *sym_tab, ui
 
 // One decode step for this lane.  `active` is false for lanes past the end of
 // a ragged stream: they keep their state, refill nothing and emit nothing.
-template <bool WIDE>
+template <int MODE>
 __device__ __forceinline__ uint32_t rans_step(uint32_t &x, uint32_t &cursor, const Ring &ring,
-                                              const NarrowTab &nt, const uint32_t *wide_tab,
-                                              uint32_t lt_mask, uint32_t grp_mask, bool active)
+                                              const Tables &tb, uint32_t lt_mask,
+                                              uint32_t grp_mask, bool active)
 {
     uint32_t slot = x & (PROB_SCALE - 1);
     uint32_t sym, x2;
-    if (WIDE) {
-        uint32_t e = wide_tab[slot];
+    if (MODE == T_NARROW) {
+        sym = tb.sym[slot];
+        uint32_t p = tb.sf[sym];
+        x2 = ((p >> 12) + 1) * (x >> PROB_BITS) + slot - (p & 0xfffu);
+    } else {
+        uint32_t e;
+        if (MODE == T_WIDE) {
+            e = tb.wide[slot];
+        } else {
+            uint32_t e1 = tb.l1[slot >> 4];
+            uint32_t j = (e1 & 0xffu) + __popc((e1 >> 8) & ((2u << (slot & 15u)) - 1u));
+            e = tb.cf[j];
+        }
         sym = e & 0xffu;
         x2 = ((e >> 20) + 1) * (x >> PROB_BITS) + slot - ((e >> 8) & 0xfffu);
-    } else {
-        sym = nt.sym[slot];
-        uint32_t p = nt.sf[sym];
-        x2 = ((p >> 12) + 1) * (x >> PROB_BITS) + slot - (p & 0xfffu);
     }
     bool need = active && x2 < RANS_LOW;
     uint32_t vote = __ballot_sync(0xffffffffu, need);

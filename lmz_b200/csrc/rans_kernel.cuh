@@ -20,34 +20,61 @@ struct RansArgs {
 // Shared-memory footprint.  The per-group stride is chosen so the four staging
 // areas of a warp sit 8 banks apart.
 constexpr uint32_t STAGE_BYTES = 160;
-constexpr uint32_t GROUP_BYTES_NARROW = RING + PROB_SCALE + 1024 + STAGE_BYTES + 32 + 96;  // 6432
-constexpr uint32_t GROUP_BYTES_WIDE = RING + STAGE_BYTES + 32 + 32;                         // 1248
 constexpr uint32_t WIDE_TAB_BYTES = PROB_SCALE * 4;
 
-template <bool WIDE>
+// Bytes of per-stream tables, and the whole per-group footprint, by table layout.
+__host__ __device__ constexpr uint32_t table_bytes(int mode)
+{
+    return mode == T_NARROW ? PROB_SCALE + 1024 : mode == T_COMPACT ? 2048 : 0;
+}
+__host__ __device__ constexpr uint32_t group_bytes(int mode)
+{
+    // ring | tables | staging | mbarriers | pad (stride = 8 banks mod 32)
+    return RING + table_bytes(mode) + STAGE_BYTES + 32 + (mode == T_WIDE ? 32 : 96);
+}
+static_assert(group_bytes(T_NARROW) == 6432 && group_bytes(T_WIDE) == 1248 &&
+              group_bytes(T_COMPACT) == 3360, "per-group shared memory layout");
+
+template <int MODE>
 __host__ __device__ constexpr uint32_t rans_smem_bytes(int warps)
 {
-    return WIDE ? WIDE_TAB_BYTES + warps * 4 * GROUP_BYTES_WIDE : warps * 4 * GROUP_BYTES_NARROW;
+    return (MODE == T_WIDE ? WIDE_TAB_BYTES : 0) + warps * 4 * group_bytes(MODE);
 }
 
-template <bool WIDE, int WARPS>
+// Point a group's table pointers at its slice of shared memory.
+template <int MODE>
+__device__ __forceinline__ Tables group_tables(uint8_t *gp, uint32_t *wide_tab)
+{
+    Tables tb{};
+    if (MODE == T_NARROW) {
+        tb.sym = gp + RING;
+        tb.sf = reinterpret_cast<uint32_t *>(gp + RING + PROB_SCALE);
+    } else if (MODE == T_COMPACT) {
+        tb.l1 = reinterpret_cast<uint32_t *>(gp + RING);
+        tb.cf = reinterpret_cast<uint32_t *>(gp + RING + 1024);
+    } else {
+        tb.wide = wide_tab;
+    }
+    return tb;
+}
+
+template <int MODE, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) k_rans(RansArgs a)
 {
+    constexpr bool WIDE = MODE == T_WIDE;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t k = lane & 7u, g = lane >> 3;
     const uint32_t grp_mask = 0xffu << (g * 8), lt_mask = ((1u << k) - 1u) << (g * 8);
-    constexpr uint32_t GB = WIDE ? GROUP_BYTES_WIDE : GROUP_BYTES_NARROW;
+    constexpr uint32_t GB = group_bytes(MODE);
     uint32_t *wide_tab = WIDE ? reinterpret_cast<uint32_t *>(smem) : nullptr;
     uint8_t *warp_base = smem + (WIDE ? WIDE_TAB_BYTES : 0) + (size_t)warp * 4 * GB;
     uint8_t *gp = warp_base + (size_t)g * GB;
 
     Ring ring;
     ring.buf = gp;
-    NarrowTab nt;
-    nt.sym = WIDE ? nullptr : gp + RING;
-    nt.sf = WIDE ? nullptr : reinterpret_cast<uint32_t *>(gp + RING + PROB_SCALE);
-    uint8_t *stage = gp + RING + (WIDE ? 0 : PROB_SCALE + 1024);
+    const Tables tb = group_tables<MODE>(gp, wide_tab);
+    uint8_t *stage = gp + RING + table_bytes(MODE);
     ring.bars = reinterpret_cast<uint64_t *>(stage + STAGE_BYTES);
 
     // ---- this group's stream ------------------------------------------------
@@ -87,9 +114,9 @@ __global__ void __launch_bounds__(WARPS * 32) k_rans(RansArgs a)
     if (WIDE) {
         if (warp == 0) {
             const uint8_t *h = a.shared_hdr;
-            bool ok = build_table<true>(
+            bool ok = build_table<T_WIDE>(
                 [&](uint32_t s) { return (uint32_t)h[4 + 2 * s] | ((uint32_t)h[5 + 2 * s] << 8); },
-                nullptr, nullptr, wide_tab, lane);
+                tb, lane);
             if (!ok || h[0] != 'R' || h[1] != '1') wide_tab[0] = 0xffffffffu;  // poison marker
         }
         __syncthreads();
@@ -101,13 +128,11 @@ __global__ void __launch_bounds__(WARPS * 32) k_rans(RansArgs a)
             uint32_t on = __shfl_sync(0xffffffffu, n, gg * 8);
             if (!on) continue;
             uint32_t sk = __shfl_sync(0xffffffffu, skew, gg * 8);
-            const uint8_t *rb = warp_base + (size_t)gg * GB;
+            uint8_t *rb = warp_base + (size_t)gg * GB;
             auto rd = [&](uint32_t o) { return (uint32_t)rb[o & (RING - 1)]; };
-            bool ok = build_table<false>(
+            bool ok = build_table<MODE>(
                 [&](uint32_t s) { return rd(sk + 4 + 2 * s) | (rd(sk + 5 + 2 * s) << 8); },
-                const_cast<uint8_t *>(rb) + RING,
-                reinterpret_cast<uint32_t *>(const_cast<uint8_t *>(rb) + RING + PROB_SCALE),
-                nullptr, lane);
+                group_tables<MODE>(rb, nullptr), lane);
             ok = ok && rd(sk) == 'R' && rd(sk + 1) == '1';
             if (!ok && g == gg) { st = ST_BAD_HEADER; n = 0; }
         }
@@ -135,14 +160,14 @@ __global__ void __launch_bounds__(WARPS * 32) k_rans(RansArgs a)
         if (__all_sync(0xffffffffu, rem >= TILE)) {
 #pragma unroll
             for (uint32_t s = 0; s < TILE / NLANES; s++) {
-                uint32_t sym = rans_step<WIDE>(x, cursor, ring, nt, wide_tab, lt_mask, grp_mask, true);
+                uint32_t sym = rans_step<MODE>(x, cursor, ring, tb, lt_mask, grp_mask, true);
                 stage[s * NLANES + k] = (uint8_t)sym;
             }
         } else {
 #pragma unroll 1
             for (uint32_t s = 0; s < TILE / NLANES; s++) {
                 bool active = s * NLANES + k < rem;
-                uint32_t sym = rans_step<WIDE>(x, cursor, ring, nt, wide_tab, lt_mask, grp_mask, active);
+                uint32_t sym = rans_step<MODE>(x, cursor, ring, tb, lt_mask, grp_mask, active);
                 if (active) stage[s * NLANES + k] = (uint8_t)sym;
             }
         }

@@ -93,6 +93,8 @@ def _bind(lib) -> None:
     lib.lmz_gpu_decode_batch_dev.argtypes = [v, v, v, c_uint, c_uint, v, v, c_uint]
     lib.lmz_gpu_set_device.restype = c_int
     lib.lmz_gpu_set_device.argtypes = [c_int]
+    lib.lmz_gpu_set_table_mode.restype = c_int
+    lib.lmz_gpu_set_table_mode.argtypes = [c_int]
     lib.lmz_gpu_decode_streams_dev.restype = c_int
     lib.lmz_gpu_decode_streams_dev.argtypes = [v, c_uint, v, v, v, v, v, v]
     from . import _chunks

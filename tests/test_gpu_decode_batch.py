@@ -8,6 +8,15 @@ from helpers import DISTRIBUTIONS, SHAPES, distribution, pack_streams, shaped
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=[0, 2], ids=["narrow", "compact"])
+def table_mode(request, gpu):
+    """Every test runs with both per-stream table layouts forced."""
+    lib = gpu.library()
+    assert lib.lmz_gpu_set_table_mode(request.param) == 0
+    yield request.param
+    lib.lmz_gpu_set_table_mode(-1)
+
+
 def _check(gpu, orc, plains, header=None, freqs=None):
     nstr, plane = len(plains), plains[0].size
     if header is None:
