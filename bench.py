@@ -34,6 +34,7 @@ sys.path.insert(0, ROOT)
 MODELS = {
     # BASELINE configuration 3: 32 layers, hidden 4096, FFN 14336, 8 KV heads of 128, vocab 128256
     "llama-3.1-8b": dict(layers=32, hidden=4096, ffn=14336, kv=1024, vocab=128256, shards=4),
+    "llama-2layer": dict(layers=2, hidden=4096, ffn=14336, kv=1024, vocab=1024, shards=1),
     "llama-tiny": dict(layers=2, hidden=1024, ffn=3584, kv=256, vocab=8000, shards=2),
 }
 METRIC = "decoded plaintext GB/s per B200 & per box (1/2/4/8 GPU), byte-exact vs CPU"
@@ -224,7 +225,7 @@ def main():
 
     # ---- per-phase device times (each phase launched alone, CUDA events) ---------------
     phase_ms = {}
-    for name, mask in (("stream_decode", 1), ("cond", 2), ("finish", 4), ("verdict", 8)):
+    for name, mask in (("stream_decode", 1), ("cond", 2), ("finish", 4), ("verdict", 8), ("fused", 16)):
         ts = []
         for _ in range(3):
             s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -262,11 +263,18 @@ def main():
         return
     peak, peak_kind = measured_peak()
     # dominant kernel: the one with the largest device time
+    # algorithmic bytes of each kernel: what it must read plus what it must write
+    fj = p.fused_jobs
+    fused_bytes = int(fj["src_len"].sum()) + 3 * int(fj["n"].sum())       # stream + plane in, 2n out
     stream_bytes = int(p.stream_jobs["src_len"].sum() + p.stream_jobs["n"].sum())
-    finish_bytes = int(coded - p.stream_jobs["src_len"].sum() + p.stream_jobs["n"].sum()
-                       + plain + p.base_bytes)
-    dom = max(("stream_decode", "finish"), key=lambda k: phase_ms[k])
-    dom_bytes = stream_bytes if dom == "stream_decode" else finish_bytes
+    fin_plain = plain - 2 * int(fj["n"].sum())
+    finish_bytes = int(coded - fj["src_len"].sum() - fj["n"].sum() - p.stream_jobs["src_len"].sum()
+                       + p.stream_jobs["n"].sum() + fin_plain + p.base_bytes)
+    kbytes = {"stream_decode": stream_bytes, "finish": finish_bytes, "fused": fused_bytes}
+    kname = {"stream_decode": "k_rans / k_stream<bytes>", "finish": "k_finish",
+             "fused": "k_stream<bf16>"}
+    dom = max(kbytes, key=lambda k: phase_ms[k])
+    dom_bytes = kbytes[dom]
     achieved = dom_bytes / (phase_ms[dom] / 1e3) / 1e9
     whole = (coded + plain + p.base_bytes) / (ms / a.steps / 1e3) / 1e9
     cpu_v, cpu_what, cpu_kind = cpu_decode_sample(blob, a.cpu_sample_mb, os.cpu_count() or 1,
@@ -284,7 +292,7 @@ def main():
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s",
                 "h2d_bytes_per_step": int(p.payload.size), "d2h_bytes_per_step": int(host_res.numel() * 4)},
         "gpu_launches": int(dec.launches_per_run * a.steps),
-        "roofline": {"bound": "hbm", "kernel": "k_rans" if dom == "stream_decode" else "k_finish",
+        "roofline": {"bound": "hbm", "kernel": kname[dom],
                      "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_kind,
                      "algorithmic_bytes_per_launch": dom_bytes,

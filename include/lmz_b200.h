@@ -111,9 +111,9 @@ int lmz_gpu_decode_streams_dev(const void *d_jobs, unsigned njobs, const void *d
  * work on the device from descriptors the host planner builds out of the
  * archive's 32-byte chunk records (lmz/format.py:53-56). */
 
-/* sizeof of {stream job, chunk job, cond job, cond state}, so a host planner can
- * check its mirrored layouts. */
-int lmz_gpu_struct_sizes(unsigned *out4);
+/* sizeof of {stream job, chunk job, cond job, cond state, fused job}, so a host
+ * planner can check its mirrored layouts. */
+int lmz_gpu_struct_sizes(unsigned *out5);
 
 /* Output bytes one thread block finishes at a time (65536); chunks are cut into
  * pieces of this size and checksummed piecewise. */
@@ -134,7 +134,9 @@ typedef struct lmz_decode_plan {
     void *d_seg_jobs;           /* 8 per conditioned chunk, sized on the device */
     void *d_stream_status;      /* uint32 per stream job */
     void *d_seg_status;         /* uint32 per segment job */
-    const void *d_chunks;       /* chunk jobs, ordered: pass 1 cond, pass 1 plain, pass 2 cond, pass 2 plain */
+    const void *d_fused_jobs;   /* BF16 chunks decoded, merged and checksummed by one kernel */
+    void *d_fused_status;       /* uint32 per fused job */
+    const void *d_chunks;       /* chunk jobs, ordered: pass 1 cond, pass 1 plain, fused, pass 2 cond, pass 2 plain */
     const void *d_piece_chunk;  /* uint32 per piece: its chunk */
     const void *d_cond_jobs;
     void *d_cond_state;
@@ -146,10 +148,11 @@ typedef struct lmz_decode_plan {
     void *d_chunk_status;       /* uint32 per chunk: 0 ok, 4 bad shape, 5 bad crc */
     void *d_chunk_crc;          /* computed crc32 per chunk, or NULL */
     void *d_any_bad;            /* uint32: bit 0 a stream failed, bit 1 a chunk failed */
-    uint32_t n_stream_jobs, n_seg_jobs, n_chunks, n_pieces, n_cond, n_cond_pieces;
-    uint32_t piece_split[5];    /* piece-id boundaries of the four chunk groups */
+    uint32_t n_stream_jobs, n_seg_jobs, n_chunks, n_pieces, n_cond, n_cond_pieces, n_fused;
+    uint32_t piece_split[6];    /* piece-id boundaries of the five chunk groups */
     uint32_t phases;            /* 0 = everything; else bit 0 stream decode, bit 1 conditioned-chunk
-                                 * kernels, bit 2 finish, bit 3 verdicts (to time one phase alone) */
+                                 * kernels, bit 2 finish, bit 3 verdicts, bit 4 fused BF16 chunks
+                                 * (to time one phase alone) */
 } lmz_decode_plan;
 
 /* Decode every chunk of the plan into d_out: rANS streams, conditioned-chunk

@@ -4,12 +4,13 @@
 
 static_assert(sizeof(lmz_stream_job) == sizeof(StreamJob), "public and device StreamJob differ");
 
-API int lmz_gpu_struct_sizes(unsigned *out4)
+API int lmz_gpu_struct_sizes(unsigned *out5)
 {
-    out4[0] = (unsigned)sizeof(StreamJob);
-    out4[1] = (unsigned)sizeof(ChunkJob);
-    out4[2] = (unsigned)sizeof(CondJob);
-    out4[3] = (unsigned)sizeof(CondState);
+    out5[0] = (unsigned)sizeof(StreamJob);
+    out5[1] = (unsigned)sizeof(ChunkJob);
+    out5[2] = (unsigned)sizeof(CondJob);
+    out5[3] = (unsigned)sizeof(CondState);
+    out5[4] = (unsigned)sizeof(FusedJob);
     return LMZ_GPU_OK;
 }
 
@@ -25,18 +26,22 @@ API int lmz_gpu_crc_tables(void *host_dst, size_t cap)
     return (int)sizeof(CrcTables);
 }
 
+// Plain pieces: 4 sub-blocks (1024 threads) share CRC tables replicated 16x, one CTA
+// per SM.  Conditioned pieces stage 66 KiB per sub-block, so that variant runs one
+// sub-block per CTA with tables replicated 4x and two CTAs per SM.
 template <bool COND>
 static int launch_finish(const FinishArgs &fa, int sms, cudaStream_t cs)
 {
     if (fa.piece_begin >= fa.piece_end) return LMZ_GPU_OK;
+    constexpr int LOGR = COND ? 2 : 4, SUBS = COND ? 1 : 4;
     static bool done[64];
-    constexpr uint32_t shm = finish_smem(COND);
-    int rc = opt_in_smem(k_finish<COND>, shm, done);
+    constexpr uint32_t shm = finish_smem(COND, LOGR, SUBS);
+    int rc = opt_in_smem(k_finish<COND, LOGR, SUBS>, shm, done);
     if (rc) return rc;
-    unsigned per_sm = COND ? 2 : 8;
-    unsigned n = fa.piece_end - fa.piece_begin;
+    unsigned per_sm = COND ? 2 : 1;
+    unsigned n = (fa.piece_end - fa.piece_begin + SUBS - 1) / SUBS;
     unsigned grid = n < (unsigned)sms * per_sm ? n : (unsigned)sms * per_sm;
-    k_finish<COND><<<grid, FINISH_THREADS, shm, cs>>>(fa);
+    k_finish<COND, LOGR, SUBS><<<grid, FINISH_THREADS * SUBS, shm, cs>>>(fa);
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return fail_cuda("launch k_finish", le);
     return LMZ_GPU_OK;
@@ -66,7 +71,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     if (rc) return rc;
 
     // `phases` selects parts of the sequence (for timing one kernel alone); 0 runs it all.
-    const uint32_t ph = p->phases ? p->phases : 0xfu;
+    const uint32_t ph = p->phases ? p->phases : 0x1fu;
 
     if (p->d_any_bad && (ph & 1u)) CK("memset any_bad", cudaMemsetAsync(p->d_any_bad, 0, 4, cs));
 
@@ -80,6 +85,23 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         a.status = (uint32_t *)p->d_stream_status;
         a.any_bad = (uint32_t *)p->d_any_bad;
         rc = launch_rans(a, cs);
+        if (rc) return rc;
+    }
+
+    // 1b. BF16 chunks with a coded exponent plane and a stored sign/mantissa plane:
+    //     decode, merge, write and checksum in one kernel
+    if (p->n_fused && (ph & 16u)) {
+        StreamArgs sa{};
+        sa.src = (const uint8_t *)p->d_payload;
+        sa.jobs = (const FusedJob *)p->d_fused_jobs;
+        sa.njobs = p->n_fused;
+        sa.dst = (uint8_t *)p->d_out;
+        sa.status = (uint32_t *)p->d_fused_status;
+        sa.any_bad = (uint32_t *)p->d_any_bad;
+        sa.piece_crc = (uint32_t *)p->d_piece_crc;
+        sa.tabs = (const CrcTables *)p->d_crc_tables;
+        rc = p->d_piece_crc ? launch_stream<SINK_BF16, true>(sa, cs)
+                            : launch_stream<SINK_BF16, false>(sa, cs);
         if (rc) return rc;
     }
 
@@ -127,10 +149,14 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     f.cond_jobs = (const CondJob *)p->d_cond_jobs;
     f.cond_state = (const CondState *)p->d_cond_state;
     f.piece_cnt = (const uint32_t *)p->d_piece_cnt;
-    for (int part = 0; part < 4 && (ph & 4u); part++) {
+    // piece groups: 0 pass-1 conditioned, 1 pass-1 plain, 2 fused (done above),
+    //               3 pass-2 conditioned, 4 pass-2 plain
+    for (int part = 0; part < 5 && (ph & 4u); part++) {
+        if (part == 2) continue;
         f.piece_begin = p->piece_split[part];
         f.piece_end = p->piece_split[part + 1];
-        rc = (part & 1) ? launch_finish<false>(f, sms, cs) : launch_finish<true>(f, sms, cs);
+        rc = (part == 0 || part == 3) ? launch_finish<true>(f, sms, cs)
+                                      : launch_finish<false>(f, sms, cs);
         if (rc) return rc;
     }
 

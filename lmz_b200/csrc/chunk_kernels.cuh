@@ -122,37 +122,103 @@ struct FinishArgs {
     const uint32_t *piece_cnt;     // 8 bucket populations per piece (K_COND chunks)
 };
 
-constexpr uint32_t FINISH_THREADS = 256;
-// crc tables + reduction scratch [+ staged exponent and sign/mantissa pieces + bucket map]
-__host__ __device__ constexpr uint32_t finish_smem(bool cond)
+constexpr uint32_t FINISH_THREADS = 256;   // threads that finish one piece together
+
+// Shared memory of k_finish:
+//   CRC tables, replicated.  A table lookup is indexed by data, so 32 lanes hit
+//   random banks; with one copy that serialises about 3.4x and made the kernel
+//   shared-memory bound.  Copy r of entry i sits at word i*R + r, which confines a
+//   copy to 32/R banks; lane l uses copy l % R, so with R = 16 two lanes share two
+//   banks.  Eight tables (4 slice + 4 advance) of 1 KiB * R each, the block aligned
+//   to one table's size so an address is (index bits) | (lane's base) in one LOP3.
+//   Then, per 256-thread sub-block: 2 KiB of reduction scratch, and for the COND
+//   variant the staged exponent / sign-mantissa pieces and the bucket map.
+__host__ __device__ constexpr uint32_t finish_table_bytes(int logr) { return 8u * (1024u << logr); }
+__host__ __device__ constexpr uint32_t finish_sub_bytes(bool cond)
 {
-    return 8192 + 2048 + (cond ? 2 * PADDED_PIECE + 256 : 0);
+    return 2048 + (cond ? 2 * PADDED_PIECE + 256 : 0);
+}
+__host__ __device__ constexpr uint32_t finish_smem(bool cond, int logr, int subs)
+{
+    return finish_table_bytes(logr) + (1024u << logr) /*alignment slack*/ + subs * finish_sub_bytes(cond);
 }
 
-// COND selects the variant that can un-partition exponent-conditioned chunks;
-// the plain variant needs a tenth of the shared memory and runs at full occupancy.
-template <bool COND>
-__global__ void __launch_bounds__(FINISH_THREADS) k_finish(FinishArgs a)
+__device__ __forceinline__ uint32_t lds_u32(uint32_t saddr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
+
+// Replicated-table CRC steps.  `tl` = shared address of this lane's copy of table 0;
+// table j lives j table-sizes further on.
+// Byte `b` of s (0 = least significant) as a table offset, OR-ed onto the lane's base.
+template <int LOGR, int B>
+__device__ __forceinline__ uint32_t crc_index(uint32_t tl, uint32_t s)
+{
+    constexpr int SH = 2 + LOGR;
+    constexpr uint32_t MASK = 0xffu << SH;
+    constexpr int RIGHT = 8 * B - SH;          // shift that moves byte B's bits to SH..SH+7
+    uint32_t v;
+    if constexpr (RIGHT >= 0) v = s >> RIGHT;
+    else v = s << (-RIGHT);
+    return (v & MASK) | tl;
+}
+
+// One slice-by-4 step over the replicated tables: the state after feeding the four
+// bytes already XOR-ed into s (tables 0..3 = CrcTables::slice).
+template <int LOGR>
+__device__ __forceinline__ uint32_t crc_feed4(uint32_t tl, uint32_t s)
+{
+    constexpr uint32_t TS = 1024u << LOGR;
+    return lds_u32(crc_index<LOGR, 0>(tl, s) + 3 * TS) ^ lds_u32(crc_index<LOGR, 1>(tl, s) + 2 * TS) ^
+           lds_u32(crc_index<LOGR, 2>(tl, s) + 1 * TS) ^ lds_u32(crc_index<LOGR, 3>(tl, s));
+}
+
+// The state advanced by a row minus 16 bytes of zeros (tables 4..7 = CrcTables::adv).
+template <int LOGR>
+__device__ __forceinline__ uint32_t crc_advance(uint32_t tl, uint32_t s)
+{
+    constexpr uint32_t TS = 1024u << LOGR;
+    return lds_u32(crc_index<LOGR, 0>(tl, s) + 4 * TS) ^ lds_u32(crc_index<LOGR, 1>(tl, s) + 5 * TS) ^
+           lds_u32(crc_index<LOGR, 2>(tl, s) + 6 * TS) ^ lds_u32(crc_index<LOGR, 3>(tl, s) + 7 * TS);
+}
+
+// COND selects the variant that can un-partition exponent-conditioned chunks (it
+// stages two 32 KiB planes per sub-block).  LOGR = log2 of the CRC table
+// replication, SUBS = 256-thread sub-blocks per CTA sharing one table set.
+template <bool COND, int LOGR, int SUBS>
+__global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
 {
     extern __shared__ __align__(16) uint8_t fsm[];
-    uint32_t (*sl)[256] = reinterpret_cast<uint32_t (*)[256]>(fsm);
-    uint32_t (*adv)[256] = reinterpret_cast<uint32_t (*)[256]>(fsm + 4096);
-    uint32_t *s_red = reinterpret_cast<uint32_t *>(fsm + 8192);    // 512 words of scratch
-    uint8_t *s_exp = fsm + 8192 + 2048;
+    constexpr uint32_t TS = 1024u << LOGR;
+    const uint32_t sub = threadIdx.x / FINISH_THREADS, t = threadIdx.x % FINISH_THREADS;
+    const uint32_t lane = t & 31, warp = t >> 5;
+    const uint32_t tab0 = (smem_addr(fsm) + TS - 1) & ~(TS - 1);      // shared address, TS-aligned
+    uint8_t *after = fsm + (tab0 - smem_addr(fsm)) + finish_table_bytes(LOGR);
+    uint8_t *sb = after + sub * finish_sub_bytes(COND);
+    uint32_t *s_red = reinterpret_cast<uint32_t *>(sb);               // 512 words of scratch
+    uint8_t *s_exp = sb + 2048;
     uint8_t *s_sm = s_exp + PADDED_PIECE;
     uint8_t *s_lut = s_sm + PADDED_PIECE;
-    const uint32_t t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const bool do_crc = a.piece_crc != nullptr;
+    const uint32_t tl = tab0 + 4 * (lane & ((1u << LOGR) - 1));
+    // slice tables are tables 0..3 (slice[0..3]), advance tables 4..7 (adv[0..3])
+    auto sub_sync = [&]() {
+        if (SUBS == 1) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(sub + 1), "n"(FINISH_THREADS) : "memory");
+    };
 
     if (do_crc) {
-        for (uint32_t i = t; i < 1024; i += FINISH_THREADS) {
-            (&sl[0][0])[i] = (&a.tabs->slice[0][0])[i];
-            (&adv[0][0])[i] = (&a.tabs->adv[0][0])[i];
-        }
+        uint32_t *tw = reinterpret_cast<uint32_t *>(fsm + (tab0 - smem_addr(fsm)));
+        const uint32_t *src = &a.tabs->slice[0][0];                   // slice then adv, contiguous
+        for (uint32_t i = threadIdx.x; i < 8u * 256u << LOGR; i += FINISH_THREADS * SUBS)
+            tw[i] = src[i >> LOGR];
     }
     __syncthreads();
 
-    for (uint32_t q = a.piece_begin + blockIdx.x; q < a.piece_end; q += gridDim.x) {
+    for (uint32_t q = a.piece_begin + blockIdx.x * SUBS + sub; q < a.piece_end;
+         q += gridDim.x * SUBS) {
         const ChunkJob &c = a.chunks[a.piece_chunk[q]];
         const uint32_t pbase = (q - c.piece0) * PIECE_BYTES;          // chunk-relative
         const uint32_t plen = min(PIECE_BYTES, c.rlen - pbase);
@@ -173,7 +239,7 @@ __global__ void __launch_bounds__(FINISH_THREADS) k_finish(FinishArgs a)
             const CondState &cs = a.cond_state[c.aux];
             const uint32_t e0 = pbase / 2, ne = plen / 2;
             const uint8_t *exp = (cj.exp_in_scratch ? a.scratch : a.payload) + cj.exp_off + e0;
-            __syncthreads();
+            sub_sync();
             s_lut[t] = cs.lut[t];
             for (uint32_t i = t * 4; i < PIECE_ELEMS; i += FINISH_THREADS * 4) {
                 uint32_t w[1] = {0};
@@ -182,7 +248,7 @@ __global__ void __launch_bounds__(FINISH_THREADS) k_finish(FinishArgs a)
             }
             // ranks of this piece's first element within each bucket
             if (t < 8) s_red[256 + t] = 0;
-            __syncthreads();
+            sub_sync();
             {
                 const uint32_t p = q - c.piece0, b = t & 7;
                 uint32_t sum = 0;
@@ -214,7 +280,7 @@ __global__ void __launch_bounds__(FINISH_THREADS) k_finish(FinishArgs a)
             }
             uint64_t *s_w = reinterpret_cast<uint64_t *>(s_red);     // 8 warps x 2
             if (lane == 31) { s_w[warp * 2] = ilo; s_w[warp * 2 + 1] = ihi; }
-            __syncthreads();
+            sub_sync();
             uint64_t blo = 0, bhi = 0;
             for (uint32_t wv = 0; wv < warp; wv++) { blo += s_w[wv * 2]; bhi += s_w[wv * 2 + 1]; }
             uint64_t xlo = ilo - lo + blo, xhi = ihi - hi + bhi;   // exclusive, may reach 32768
@@ -242,7 +308,7 @@ __global__ void __launch_bounds__(FINISH_THREADS) k_finish(FinishArgs a)
                 }
                 *reinterpret_cast<uint32_t *>(s_sm + pad128(my0 + j)) = o;
             }
-            __syncthreads();
+            sub_sync();
         }
 
         // ---- rows: every thread produces 16 output bytes per row ----------------
@@ -323,18 +389,18 @@ __global__ void __launch_bounds__(FINISH_THREADS) k_finish(FinishArgs a)
                 }
             }
             if (do_crc) {
-                acc = crc_apply(adv, acc);
+                acc = crc_advance<LOGR>(tl, acc);
 #pragma unroll
-                for (int i = 0; i < 4; i++) acc = crc_word(sl, acc, w[i]);
+                for (int i = 0; i < 4; i++) acc = crc_feed4<LOGR>(tl, acc ^ w[i]);
             }
         }
         if (do_crc) {
             uint32_t v = crc_mulmod(a.tabs->lane_mul[t], acc);
 #pragma unroll
             for (int d = 16; d; d >>= 1) v ^= __shfl_xor_sync(0xffffffffu, v, d);
-            __syncthreads();
+            sub_sync();
             if (lane == 0) s_red[300 + warp] = v;
-            __syncthreads();
+            sub_sync();
             if (t == 0) {
                 uint32_t r = 0;
                 for (int i = 0; i < 8; i++) r ^= s_red[300 + i];
@@ -342,7 +408,7 @@ __global__ void __launch_bounds__(FINISH_THREADS) k_finish(FinishArgs a)
                 a.piece_crc[q] = r;
             }
         }
-        __syncthreads();
+        sub_sync();
     }
 }
 

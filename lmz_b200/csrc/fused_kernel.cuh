@@ -1,0 +1,399 @@
+// k_stream: the throughput kernel.  One 8-lane group per rANS stream, compact
+// per-stream tables, and the stream's consumer fused into the decode loop:
+//
+//   SINK_BYTES  the decoded plane is written as is (decode_batch, scratch planes)
+//   SINK_BF16   a CODEC_BF16 chunk whose exponent plane is rANS and whose
+//               sign/mantissa plane is stored: each 128-symbol tile is merged with
+//               128 stored bytes (lmz/native/lmzcore.c:439-447), written once as
+//               256 bytes of BF16, and folded into the chunk's CRC-32 -- no
+//               scratch plane, no second pass
+//
+// Differences from k_rans that buy instructions and occupancy:
+//   * shared memory is laid out by kind (all level-1 tables, all level-2 tables,
+//     all rings ...) so each table base is 1 KiB aligned and an address is
+//     (index bits) | base in one logic op
+//   * the input ring (4 x 128 B) is followed by a mirror of its first 272 bytes,
+//     filled by the same bulk copies, so a tile reads linearly with no wrap masks
+//   * 3 KiB per stream: 64 streams (16 warps) per SM beside 32 KiB of CRC tables
+#pragma once
+#include "chunk_kernels.cuh"
+#include "rans.cuh"
+
+namespace lmz {
+
+constexpr uint32_t F_SLOT = 128, F_NSLOT = 4, F_RING = F_SLOT * F_NSLOT;
+constexpr uint32_t F_MIRROR = 272;                 // a tile reads at most 256 + 2 bytes ahead
+constexpr uint32_t F_RING_BYTES = F_RING + F_MIRROR + 16;   // 800
+constexpr uint32_t F_STAGE = 144;                  // 128 + 16: groups land 4 banks apart
+constexpr uint32_t F_LOGR = 2;                     // CRC tables replicated 4x (32 KiB)
+constexpr uint32_t F_ROW = 256, F_UNIT = 32;       // bytes of BF16 one group / one lane emits per tile
+enum : int { SINK_BYTES = 0, SINK_BF16 = 1 };
+
+struct FusedJob {
+    uint64_t src_off;    // rANS stream, bytes from the source base
+    uint64_t mant_off;   // SINK_BF16: the stored sign/mantissa plane, bytes from the source base
+    uint64_t dst_off;    // first output byte
+    uint32_t src_len;
+    uint32_t n;          // symbols (= BF16 elements)
+    uint32_t piece0;     // SINK_BF16: first piece id of the chunk (for piece_crc)
+    uint32_t flags;
+};
+static_assert(sizeof(FusedJob) == 40, "FusedJob layout is shared with the host");
+
+struct StreamArgs {
+    const uint8_t *src;
+    const FusedJob *jobs;       // SINK_BF16 jobs, or NULL
+    const StreamJob *sjobs;     // plain stream jobs, or NULL
+    const uint64_t *offs;       // neither: reference layout, (offset, length) pairs + plane
+    uint32_t plane;
+    uint32_t njobs;
+    uint8_t *dst;
+    uint32_t *status;
+    uint32_t *any_bad;
+    uint32_t *piece_crc;        // SINK_BF16 with checksums: R() per 64 KiB piece
+    const CrcTables *tabs;
+};
+
+__host__ __device__ constexpr uint32_t stream_group_bytes()
+{
+    return 1024 + 1024 + F_RING_BYTES + F_STAGE + 32;     // 3024
+}
+__host__ __device__ constexpr uint32_t stream_smem_bytes(int warps, bool crc)
+{
+    return 4096 /*alignment slack*/ + (crc ? 8u * (1024u << F_LOGR) : 0u) +
+           warps * 4 * stream_group_bytes();
+}
+
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u8_1(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1+1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts_u8(uint32_t a, uint32_t v)
+{
+    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 lds_u128(uint32_t a)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void bulk_g2s_sa(uint32_t dst_sa, const void *src, uint32_t bytes,
+                                            uint32_t bar_sa)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst_sa), "l"(src), "r"(bytes), "r"(bar_sa) : "memory");
+}
+
+// Input ring with a mirror of its head behind it.  Offsets are bytes from `abase`.
+struct MRing {
+    uint32_t sa;           // shared address of the ring
+    uint64_t *bars;
+    const uint8_t *abase;
+    uint32_t valid_slots, issued, ready;
+    bool dead;
+
+    __device__ __forceinline__ void issue(uint32_t cursor, bool leader)
+    {
+        if (!leader) return;
+        uint32_t lim = cursor / F_SLOT + F_NSLOT;
+        if (lim > valid_slots) lim = valid_slots;
+        while (issued < lim) {
+            uint32_t j = issued % F_NSLOT;
+            uint32_t m = j * F_SLOT < F_MIRROR ? min(F_SLOT, F_MIRROR - j * F_SLOT) : 0u;
+            const uint8_t *g = abase + (size_t)issued * F_SLOT;
+            mbar_expect_tx(&bars[j], F_SLOT + m);
+            bulk_g2s_sa(sa + j * F_SLOT, g, F_SLOT, smem_addr(&bars[j]));
+            if (m) bulk_g2s_sa(sa + F_RING + j * F_SLOT, g, m, smem_addr(&bars[j]));
+            issued++;
+        }
+    }
+    __device__ __forceinline__ void require(uint32_t upto)
+    {
+        uint32_t need = (upto + F_SLOT - 1) / F_SLOT;
+        if (need > valid_slots) need = valid_slots;
+        while (ready < need) {
+            if (!dead && !mbar_wait(&bars[ready % F_NSLOT], (ready / F_NSLOT) & 1u)) dead = true;
+            ready++;
+        }
+    }
+    __device__ __forceinline__ uint32_t byte_at(uint32_t o) const { return lds_u8(sa + (o & (F_RING - 1))); }
+    __device__ __forceinline__ uint32_t u16_at(uint32_t o) const { return byte_at(o) | (byte_at(o + 1) << 8); }
+    __device__ __forceinline__ uint32_t u32_at(uint32_t o) const { return u16_at(o) | (u16_at(o + 2) << 16); }
+};
+
+// One decode step.  `caddr` is the shared address of the cursor (linear within a
+// tile thanks to the mirror).  Returns the level-2 entry; its low byte is the symbol.
+__device__ __forceinline__ uint32_t stream_step(uint32_t &x, uint32_t &caddr, uint32_t l1_sa,
+                                                uint32_t cf_sa, uint32_t lt_mask, uint32_t grp_mask,
+                                                bool active)
+{
+    const uint32_t slot = x & (PROB_SCALE - 1);
+    const uint32_t e1 = lds_u32(((x >> 2) & 0x3fcu) | l1_sa);
+    const uint32_t upto = 0xffffffffu >> ((~x) & 15u);                 // bits 0 .. 16 + (slot & 15)
+    const uint32_t pc = __popc(e1 & upto & 0xffff0000u);
+    const uint32_t e = lds_u32(((e1 & 0x3fcu) | cf_sa) + (pc << 2));
+    const uint32_t xs = x >> PROB_BITS;
+    const uint32_t x2 = (e >> 20) * xs + xs + slot - ((e >> 8) & 0xfffu);
+    const bool need = active && x2 < RANS_LOW;
+    const uint32_t vote = __ballot_sync(0xffffffffu, need);
+    const uint32_t addr = caddr + 2 * __popc(vote & lt_mask);
+    const uint32_t w = lds_u8(addr) | (lds_u8_1(addr) << 8);
+    if (active) x = need ? __byte_perm(w, x2, 0x5410) : x2;
+    caddr += 2 * __popc(vote & grp_mask);
+    return e;
+}
+
+template <int SINK, bool CRC, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
+{
+    extern __shared__ __align__(16) uint8_t ssm[];
+    constexpr uint32_t G = WARPS * 4, TS = 1024u << F_LOGR;
+    constexpr uint32_t LEAD = HDR_BYTES + STATE_BYTES;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t k = lane & 7u, g = lane >> 3, gi = warp * 4 + g;
+    const uint32_t grp_mask = 0xffu << (g * 8), lt_mask = ((1u << k) - 1u) << (g * 8);
+
+    // ---- carve shared memory (addresses are 32-bit shared-space addresses) --------
+    const uint32_t base0 = (smem_addr(ssm) + 4095u) & ~4095u;
+    uint8_t *gen0 = ssm + (base0 - smem_addr(ssm));
+    const uint32_t tab0 = base0;
+    const uint32_t l1_0 = base0 + (CRC ? 8 * TS : 0);
+    const uint32_t cf_0 = l1_0 + G * 1024;
+    const uint32_t ring_0 = cf_0 + G * 1024;
+    const uint32_t stage_0 = ring_0 + G * F_RING_BYTES;
+    const uint32_t bars_0 = stage_0 + G * F_STAGE;
+    const uint32_t l1_sa = l1_0 + gi * 1024, cf_sa = cf_0 + gi * 1024;
+    const uint32_t stage_sa = stage_0 + gi * F_STAGE;
+    const uint32_t tl = tab0 + 4 * (lane & ((1u << F_LOGR) - 1));
+
+    MRing ring;
+    ring.sa = ring_0 + gi * F_RING_BYTES;
+    ring.bars = reinterpret_cast<uint64_t *>(gen0 + (bars_0 - base0)) + gi * F_NSLOT;
+
+    // ---- this group's stream ------------------------------------------------------
+    const uint32_t job = (blockIdx.x * WARPS + warp) * 4 + g;
+    const bool have = job < a.njobs;
+    uint64_t soff = 0, doff = 0, moff = 0;
+    uint32_t slen = 0, n = 0, piece0 = 0;
+    if (have) {
+        if (a.jobs) {
+            FusedJob j = a.jobs[job];
+            soff = j.src_off; doff = j.dst_off; moff = j.mant_off;
+            slen = j.src_len; n = j.n; piece0 = j.piece0;
+        } else if (a.sjobs) {
+            StreamJob j = a.sjobs[job];
+            soff = j.src_off; doff = j.dst_off; slen = j.src_len; n = j.n;
+        } else {
+            soff = a.offs[2 * job]; slen = (uint32_t)a.offs[2 * job + 1];
+            n = a.plane; doff = (uint64_t)job * a.plane;
+        }
+    }
+    uint32_t st = ST_OK;
+    if (n != 0 && slen < LEAD) { st = ST_BAD_HEADER; n = 0; }
+    if (n == 0) slen = 0;
+    const uint8_t *sbase = a.src + soff;
+    const uint32_t skew = (uint32_t)(reinterpret_cast<uintptr_t>(sbase) & 15u);
+    ring.abase = sbase - skew;
+    ring.valid_slots = n ? (skew + slen + F_SLOT - 1) / F_SLOT : 0;
+    ring.issued = 0; ring.ready = 0; ring.dead = false;
+
+    if (k == 0)
+        for (uint32_t j = 0; j < F_NSLOT; j++) mbar_init(&ring.bars[j], 1);
+    mbar_fence_init();
+    if (CRC) {
+        // tables 0..3 = slice-by-4, 4..7 = advance by one row minus one lane unit
+        uint32_t *tw = reinterpret_cast<uint32_t *>(gen0);
+        for (uint32_t i = threadIdx.x; i < (8u * 256u) << F_LOGR; i += WARPS * 32) {
+            uint32_t e = i >> F_LOGR;
+            tw[i] = e < 1024 ? (&a.tabs->slice[0][0])[e] : (&a.tabs->adv_row[0][0])[e - 1024];
+        }
+    }
+    __syncthreads();
+
+    // The stream's first 576 bytes (table + states, wherever the 16-byte boundary
+    // falls) land linearly across ring + mirror: four 144-byte copies, one per
+    // slot barrier, so every barrier has completed one phase -- as if ring slots
+    // 0..3 had been filled and consumed -- when normal ring operation takes over.
+    if (k == 0 && n) {
+        for (uint32_t j = 0; j < F_NSLOT; j++) {
+            mbar_expect_tx(&ring.bars[j], 144);
+            bulk_g2s_sa(ring.sa + 144 * j, ring.abase + 144 * j, 144, smem_addr(&ring.bars[j]));
+        }
+    }
+    __syncwarp();
+    if (n)
+        for (uint32_t j = 0; j < F_NSLOT; j++)
+            if (!ring.dead && !mbar_wait(&ring.bars[j], 0)) ring.dead = true;
+    ring.issued = ring.ready = F_NSLOT;
+
+    // ---- per-stream tables, built by the whole warp one stream at a time ------------
+#pragma unroll 1
+    for (uint32_t gg = 0; gg < 4; gg++) {
+        uint32_t on = __shfl_sync(0xffffffffu, n, gg * 8);
+        if (!on) continue;
+        uint32_t sk = __shfl_sync(0xffffffffu, skew, gg * 8);
+        const uint32_t rsa = ring_0 + (warp * 4 + gg) * F_RING_BYTES;
+        auto rd = [&](uint32_t o) { return lds_u8(rsa + o); };     // header sits in the first 548+15 bytes
+        Tables tb{};
+        tb.l1 = reinterpret_cast<uint32_t *>(gen0 + (l1_0 - base0) + (warp * 4 + gg) * 1024);
+        tb.cf = reinterpret_cast<uint32_t *>(gen0 + (cf_0 - base0) + (warp * 4 + gg) * 1024);
+        bool ok = build_table<T_COMPACT>(
+            [&](uint32_t s) { return rd(sk + 4 + 2 * s) | (rd(sk + 5 + 2 * s) << 8); }, tb, lane);
+        ok = ok && rd(sk) == 'R' && rd(sk + 1) == '1';
+        if (!ok && g == gg) { st = ST_BAD_HEADER; n = 0; }
+    }
+    __syncwarp();
+
+    const uint32_t xo = ring.sa + skew + HDR_BYTES + 4 * k;
+    uint32_t x = lds_u8(xo) | (lds_u8(xo + 1) << 8) | (lds_u8(xo + 2) << 16) | (lds_u8(xo + 3) << 24);
+    uint32_t cursor = skew + LEAD;
+    uint8_t *out = a.dst + doff;
+    const uint32_t al = (uint32_t)(reinterpret_cast<uintptr_t>(out) & 15u);
+
+    // SINK_BF16: the stored plane, read as aligned words and funnel-shifted
+    const uint8_t *mant = a.src + moff + 16 * k;
+    const uint32_t msh = (uint32_t)(reinterpret_cast<uintptr_t>(mant) & 3u) * 8u;
+    const uint32_t *mq = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(mant) & ~uintptr_t(3));
+    uint32_t m[5] = {0, 0, 0, 0, 0};
+    const uint32_t my_tiles = (n + TILE - 1) / TILE;
+    if (SINK == SINK_BF16 && my_tiles) {
+#pragma unroll
+        for (int i = 0; i < 5; i++) m[i] = __ldg(mq + i);
+    }
+    uint32_t acc = 0;
+
+    // ---- tiles of 128 symbols ---------------------------------------------------------
+    const uint32_t warp_tiles = __reduce_max_sync(0xffffffffu, my_tiles);
+#pragma unroll 1
+    for (uint32_t t = 0; t < warp_tiles; t++) {
+        const uint32_t done = t * TILE;
+        const uint32_t rem = n > done ? n - done : 0;
+        __syncwarp();
+        if (rem) {
+            ring.issue(cursor, k == 0);
+            ring.require(cursor + 2 * TILE);
+        }
+        __syncwarp();
+        const uint32_t caddr0 = ring.sa + (cursor & (F_RING - 1));
+        uint32_t caddr = caddr0;
+        const bool full = __all_sync(0xffffffffu, rem >= TILE);
+        if (full) {
+#pragma unroll
+            for (uint32_t s = 0; s < TILE / NLANES; s++) {
+                uint32_t e = stream_step(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, true);
+                sts_u8(stage_sa + s * NLANES + k, e);
+            }
+        } else {
+#pragma unroll 1
+            for (uint32_t s = 0; s < TILE / NLANES; s++) {
+                bool active = s * NLANES + k < rem;
+                uint32_t e = stream_step(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
+                if (active) sts_u8(stage_sa + s * NLANES + k, e);
+            }
+        }
+        cursor += caddr - caddr0;
+        __syncwarp();
+        if (!rem) continue;
+        const uint4 ev = lds_u128(stage_sa + 16 * k);        // this lane's 16 symbols
+
+        if (SINK == SINK_BYTES) {
+            if (rem >= TILE && al == 0) {
+                *reinterpret_cast<uint4 *>(out + done + k * 16) = ev;
+            } else {
+                const uint32_t cnt = rem < TILE ? rem : TILE;
+                const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w};
+#pragma unroll
+                for (uint32_t i = 0; i < 16; i++)
+                    if (k * 16 + i < cnt) out[done + k * 16 + i] = (uint8_t)(ew[i >> 2] >> (8 * (i & 3)));
+            }
+            continue;
+        }
+
+        // ---- SINK_BF16: merge with the stored plane, write, checksum ------------------
+        const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w};
+        uint32_t w[8];
+#pragma unroll
+        for (int h = 0; h < 4; h++) {
+            const uint32_t b = __funnelshift_r(m[h], m[h + 1], msh), e4 = ew[h];
+            w[2 * h] = bf16_pair(__byte_perm(e4, 0, 0x4140), __byte_perm(b, 0, 0x4140));
+            w[2 * h + 1] = bf16_pair(__byte_perm(e4, 0, 0x4342), __byte_perm(b, 0, 0x4342));
+        }
+        if (t + 1 < my_tiles) {                                // next tile's stored bytes
+#pragma unroll
+            for (int i = 0; i < 5; i++) m[i] = __ldg(mq + (size_t)(t + 1) * (TILE / 4) + i);
+        }
+        uint8_t *d = out + (size_t)done * 2 + k * F_UNIT;
+        const uint32_t ve = rem > 16 * k ? min(rem - 16 * k, 16u) : 0u;   // valid elements of this lane
+        if (ve == 16) {
+            if (al == 0) {
+                reinterpret_cast<uint4 *>(d)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                reinterpret_cast<uint4 *>(d)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            } else if ((al & 7) == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) reinterpret_cast<uint2 *>(d)[i] = make_uint2(w[2 * i], w[2 * i + 1]);
+            } else if ((al & 3) == 0) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) reinterpret_cast<uint32_t *>(d)[i] = w[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) d[i] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+            }
+        } else {
+            const uint32_t vb = 2 * ve;
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if ((uint32_t)i < vb) d[i] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t keep = vb > 4u * i ? min(vb - 4u * i, 4u) : 0u;
+                w[i] = keep >= 4 ? w[i] : (keep ? w[i] & ((1u << (8 * keep)) - 1u) : 0u);
+            }
+        }
+        if (CRC) {
+            acc = crc_advance<F_LOGR>(tl, acc);
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc = crc_feed4<F_LOGR>(tl, acc ^ w[i]);
+            const bool last = t + 1 == my_tiles;
+            if ((t & 255u) == 255u || last) {
+                // close the 64 KiB piece: lane units -> row end, XOR over the group
+                uint32_t v = crc_mulmod(a.tabs->lane_mul8[k], acc);
+                v ^= __shfl_xor_sync(grp_mask, v, 1);
+                v ^= __shfl_xor_sync(grp_mask, v, 2);
+                v ^= __shfl_xor_sync(grp_mask, v, 4);
+                if (k == 0) {
+                    const uint32_t p = t >> 8, rows = (t & 255u) + 1;
+                    const uint32_t plen = min(PIECE_BYTES, 2 * n - p * PIECE_BYTES);
+                    if (rows * F_ROW != plen) v = crc_unshift(a.tabs->x2, v, rows * F_ROW - plen);
+                    a.piece_crc[piece0 + p] = v;
+                }
+                acc = 0;
+            }
+        }
+    }
+
+    // ---- verdict -----------------------------------------------------------------------
+    const uint32_t all_rest = __ballot_sync(0xffffffffu, x == RANS_LOW) & grp_mask;
+    if (have && k == 0) {
+        if (st == ST_OK && n) {
+            const uint32_t used = cursor - skew;
+            if (ring.dead) st = ST_TIMEOUT;
+            else if (used > slen) st = ST_OVERRUN;
+            else if (used != slen || all_rest != grp_mask) st = ST_SLACK;
+        }
+        if (a.status) a.status[job] = st;
+        if (a.any_bad && st != ST_OK && st != ST_SLACK) atomicOr(a.any_bad, 1u);
+    }
+}
+
+}  // namespace lmz

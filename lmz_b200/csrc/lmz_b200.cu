@@ -13,6 +13,7 @@
 #include "rans_kernel.cuh"
 #include "chunk_kernels.cuh"
 #include "cond_kernels.cuh"
+#include "fused_kernel.cuh"
 
 using namespace lmz;
 
@@ -66,7 +67,6 @@ static int opt_in_smem(K kernel, uint32_t bytes, bool *done /* [64] by device */
 
 constexpr int WARPS_NARROW = 4;    // 2 CTAs/SM: 32 streams resident
 constexpr int WARPS_WIDE = 8;
-constexpr int WARPS_COMPACT = 8;   // 2 CTAs/SM: 64 streams resident
 // Batches at least this large are occupancy-bound and take the compact tables;
 // smaller ones are latency-bound per stream and keep the shorter narrow lookup.
 constexpr unsigned COMPACT_MIN_JOBS = 148 * 32 * 2;
@@ -85,6 +85,23 @@ static int launch_rans_mode(const RansArgs &a, cudaStream_t cs)
     return LMZ_GPU_OK;
 }
 
+constexpr int WARPS_STREAM = 16;   // 64 streams per SM, one CTA
+
+template <int SINK, bool CRC>
+static int launch_stream(const StreamArgs &a, cudaStream_t cs)
+{
+    if (a.njobs == 0) return LMZ_GPU_OK;
+    static bool done[64];
+    constexpr uint32_t shm = stream_smem_bytes(WARPS_STREAM, CRC);
+    int rc = opt_in_smem(k_stream<SINK, CRC, WARPS_STREAM>, shm, done);
+    if (rc) return rc;
+    unsigned blocks = (a.njobs + WARPS_STREAM * 4 - 1) / (WARPS_STREAM * 4);
+    k_stream<SINK, CRC, WARPS_STREAM><<<blocks, WARPS_STREAM * 32, shm, cs>>>(a);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch k_stream", le);
+    return LMZ_GPU_OK;
+}
+
 // `force_mode` < 0 picks by batch size.
 static int g_force_table_mode = -1;
 
@@ -94,7 +111,12 @@ static int launch_rans(const RansArgs &a, cudaStream_t cs)
     if (a.shared_hdr) return launch_rans_mode<T_WIDE, WARPS_WIDE>(a, cs);
     int mode = g_force_table_mode >= 0 ? g_force_table_mode
                                        : (a.njobs >= COMPACT_MIN_JOBS ? T_COMPACT : T_NARROW);
-    if (mode == T_COMPACT) return launch_rans_mode<T_COMPACT, WARPS_COMPACT>(a, cs);
+    if (mode == T_COMPACT) {
+        StreamArgs sa{};
+        sa.src = a.src; sa.sjobs = a.jobs; sa.offs = a.offs; sa.plane = a.plane;
+        sa.njobs = a.njobs; sa.dst = a.dst; sa.status = a.status; sa.any_bad = a.any_bad;
+        return launch_stream<SINK_BYTES, false>(sa, cs);
+    }
     return launch_rans_mode<T_NARROW, WARPS_NARROW>(a, cs);
 }
 

@@ -19,13 +19,14 @@ namespace lmz {
 //             symbol -> (freq-1) << 12 | start (256 x u32).  Two dependent loads.
 //   T_WIDE    one per CTA, 16 KiB: slot -> (freq-1) << 20 | start << 8 | symbol.
 //             One dependent load; only affordable when the whole CTA shares a table.
-//   T_COMPACT per stream, 2 KiB: level 1 has one word per 16 slots holding the
-//             index of the live symbol covering the bucket's first slot (bits 0-7)
-//             and a bit per in-bucket position where another live symbol starts
-//             (bits 8+t); a popcount of the bits at or below the slot's position
-//             gives the live-symbol index exactly, and level 2 holds one wide-style
-//             entry per live symbol.  Two dependent loads and a popcount, at 40 %
-//             of the narrow layout's footprint, so 2.4x as many streams fit an SM.
+//   T_COMPACT per stream, 2 KiB: level 1 has one word per 16 slots holding four
+//             times the index of the live symbol covering the bucket's first slot
+//             (bits 0-9, i.e. its byte offset in level 2) and a bit per in-bucket
+//             position t where another live symbol starts (bit 16+t); a popcount
+//             of the bits at or below the slot's position gives the live-symbol
+//             index exactly, and level 2 holds one wide-style entry per live
+//             symbol.  Two dependent loads and a popcount, at 40 % of the narrow
+//             layout's footprint, so 2.4x as many streams fit an SM.
 // Frequency is stored minus one because a single-symbol stream has f = 4096.
 enum : int { T_NARROW = 0, T_WIDE = 1, T_COMPACT = 2 };
 
@@ -128,7 +129,7 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, ui
         if (MODE == T_NARROW) tb.sf[s] = ((fi ? fi - 1 : 0) << 12) | st;
         if (MODE == T_COMPACT && fi) {
             tb.cf[li] = packed;
-            if (st & 15u) atomicOr(&tb.l1[st >> 4], 1u << (8 + (st & 15u)));
+            if (st & 15u) atomicOr(&tb.l1[st >> 4], 1u << (16 + (st & 15u)));
         }
         // work items of this symbol: slots (narrow/wide) or covered bucket heads (compact)
         uint32_t lo = MODE == T_COMPACT ? (st + 15) >> 4 : st;
@@ -139,7 +140,7 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, ui
             for (uint32_t t = 0; t < cnt; t++) {
                 if (MODE == T_WIDE) tb.wide[lo + t] = packed;
                 else if (MODE == T_NARROW) tb.sym[lo + t] = (uint8_t)s;
-                else atomicOr(&tb.l1[lo + t], li);
+                else atomicOr(&tb.l1[lo + t], li << 2);
             }
         }
         uint32_t m = __ballot_sync(0xffffffffu, big);
@@ -153,7 +154,7 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, ui
             for (uint32_t t = lane; t < bc; t += 32) {
                 if (MODE == T_WIDE) tb.wide[bl + t] = bp;
                 else if (MODE == T_NARROW) tb.sym[bl + t] = (uint8_t)bp;
-                else atomicOr(&tb.l1[bl + t], bi);
+                else atomicOr(&tb.l1[bl + t], bi << 2);
             }
         }
     }
@@ -180,8 +181,9 @@ __device__ __forceinline__ uint32_t rans_step(uint32_t &x, uint32_t &cursor, con
             e = tb.wide[slot];
         } else {
             uint32_t e1 = tb.l1[slot >> 4];
-            uint32_t j = (e1 & 0xffu) + __popc((e1 >> 8) & ((2u << (slot & 15u)) - 1u));
-            e = tb.cf[j];
+            uint32_t upto = 0xffffffffu >> (15u - (slot & 15u));       // bits 0 .. 16+t
+            uint32_t j4 = (e1 & 0x3fcu) + 4u * __popc(e1 & upto & 0xffff0000u);
+            e = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(tb.cf) + j4);
         }
         sym = e & 0xffu;
         x2 = ((e >> 20) + 1) * (x >> PROB_BITS) + slot - ((e >> 8) & 0xfffu);

@@ -53,19 +53,20 @@ class ArchiveDecoder:
     `verify_checksums=False`).  `payload` may be given as an already-uploaded CUDA
     uint8 tensor holding `plan.payload` followed by `gpu.pad_bytes()` of slack."""
 
-    def __init__(self, ar, device=None, checksum: bool = True, out=None, plan=None):
+    def __init__(self, ar, device=None, checksum: bool = True, out=None, plan=None,
+                 fuse: bool = True):
         import torch
 
         lib = gpu.library()
         self.lib = lib
-        sizes = (ctypes.c_uint * 4)()
+        sizes = (ctypes.c_uint * 5)()
         lib.lmz_gpu_struct_sizes(ctypes.byref(sizes))
         want = (planner.STREAM_JOB.itemsize, planner.CHUNK_JOB.itemsize,
-                planner.COND_JOB.itemsize, planner.COND_STATE_BYTES)
+                planner.COND_JOB.itemsize, planner.COND_STATE_BYTES, planner.FUSED_JOB.itemsize)
         if tuple(sizes) != want or lib.lmz_gpu_piece_bytes() != planner.PIECE:
             raise RuntimeError("the CUDA library and the planner disagree on job layouts")
         self.archive = ar if isinstance(ar, fmt.Archive) else fmt.Archive(ar)
-        self.plan = p = plan if plan is not None else planner.build_plan(self.archive)
+        self.plan = p = plan if plan is not None else planner.build_plan(self.archive, fuse=fuse)
         self.device = torch.device(device if device is not None else
                                    f"cuda:{torch.cuda.current_device()}")
         self.checksum = checksum
@@ -83,6 +84,7 @@ class ArchiveDecoder:
                 raise ValueError("the output buffer needs total + 64 bytes")
             self.d_stream_jobs = _dev(p.stream_jobs, d)
             self.d_seg_jobs = _dev(p.seg_jobs, d)
+            self.d_fused_jobs = _dev(p.fused_jobs, d)
             self.d_chunks = _dev(p.chunks, d)
             self.d_piece_chunk = _dev(p.piece_chunk, d)
             self.d_cond_jobs = _dev(p.cond_jobs, d)
@@ -96,6 +98,7 @@ class ArchiveDecoder:
             self.d_piece_crc = torch.zeros(max(1, p.n_pieces), **u32)
             self.d_stream_status = torch.zeros(max(1, p.stream_jobs.size), **u32)
             self.d_seg_status = torch.zeros(max(1, p.seg_jobs.size), **u32)
+            self.d_fused_status = torch.zeros(max(1, p.fused_jobs.size), **u32)
             self.d_chunk_status = torch.zeros(max(1, p.chunks.size), **u32)
             self.d_chunk_crc = torch.zeros(max(1, p.chunks.size), **u32)
             self.d_any_bad = torch.zeros(1, **u32)
@@ -105,6 +108,8 @@ class ArchiveDecoder:
         c.d_out = self.d_out.data_ptr()
         c.d_stream_jobs, c.d_seg_jobs = self.d_stream_jobs.data_ptr(), self.d_seg_jobs.data_ptr()
         c.d_stream_status, c.d_seg_status = self.d_stream_status.data_ptr(), self.d_seg_status.data_ptr()
+        c.d_fused_jobs, c.d_fused_status = self.d_fused_jobs.data_ptr(), self.d_fused_status.data_ptr()
+        c.n_fused = p.fused_jobs.size
         c.d_chunks, c.d_piece_chunk = self.d_chunks.data_ptr(), self.d_piece_chunk.data_ptr()
         c.d_cond_jobs, c.d_cond_state = self.d_cond_jobs.data_ptr(), self.d_cond_state.data_ptr()
         c.d_cond_pieces = self.d_cond_pieces.data_ptr()
@@ -116,13 +121,14 @@ class ArchiveDecoder:
         c.n_stream_jobs, c.n_seg_jobs = p.stream_jobs.size, p.seg_jobs.size
         c.n_chunks, c.n_pieces = p.chunks.size, p.n_pieces
         c.n_cond, c.n_cond_pieces = ncond, p.cond_pieces.size
-        for i in range(5):
+        for i in range(6):
             c.piece_split[i] = int(p.piece_split[i])
         self._c = c
         # kernels launched by one run(): stream decode, 3 cond kernels + segment decode,
         # up to four finish launches, the verdict kernel
         self.launches_per_run = (1 if p.stream_jobs.size else 0) + (4 if ncond else 0) + \
-            int(sum(p.piece_split[i + 1] > p.piece_split[i] for i in range(4))) + 1
+            (1 if p.fused_jobs.size else 0) + \
+            int(sum(p.piece_split[i + 1] > p.piece_split[i] for i in (0, 1, 3, 4))) + 1
 
     def upload(self, pinned=None, non_blocking: bool = False):
         """Copy the payload host -> device (from `pinned` if given)."""
@@ -133,7 +139,8 @@ class ArchiveDecoder:
     def run(self, stream=None, phases: int = 0):
         """Launch the decode on `stream` (default: torch's current). Asynchronous.
         `phases` restricts the launch sequence (bit 0 stream decode, 1 conditioned-chunk
-        kernels, 2 finish, 3 verdicts) so one phase can be timed alone; 0 runs all."""
+        kernels, 2 finish, 3 verdicts, 4 fused BF16 chunks) so one phase can be timed
+        alone; 0 runs all."""
         import torch
         self._c.phases = phases
         with torch.cuda.device(self.device):
@@ -166,6 +173,11 @@ class ArchiveDecoder:
         if hard.size:
             rec = int(p.stream_owner[hard[0]])
             raise CorruptArchive(f"a plane of chunk {rec}: {_ST_NAMES.get(int(ss[hard[0]]), '?')}")
+        fs = self.d_fused_status.cpu().numpy()[:p.fused_jobs.size]
+        hard = np.nonzero((fs != 0) & (fs != 0x100))[0]
+        if hard.size:
+            raise CorruptArchive(f"the exponent plane of a bf16 chunk: "
+                                 f"{_ST_NAMES.get(int(fs[hard[0]]), '?')}")
         raise CorruptArchive("a bucket segment of a conditioned chunk failed to decode")
 
     def chunk_crcs(self) -> np.ndarray:

@@ -40,11 +40,14 @@ COND_JOB = np.dtype([("exp_off", "<u8"), ("seg_src", "<u8", 8), ("seg_scratch", 
                      ("seg_len", "<u4", 8), ("nelem", "<u4"), ("seg_job0", "<u4"),
                      ("piece0", "<u4"), ("chunk", "<u4"), ("seg_method", "u1", 8),
                      ("exp_in_scratch", "u1"), ("pad", "u1", 7)])
+FUSED_JOB = np.dtype([("src_off", "<u8"), ("mant_off", "<u8"), ("dst_off", "<u8"),
+                      ("src_len", "<u4"), ("n", "<u4"), ("piece0", "<u4"), ("flags", "<u4")])
 COND_STATE_BYTES = 360
 BF16C_HDR = np.dtype([("k", "u1"), ("exp_m", "u1"), ("sm_m", "u1", 8), ("exp_len", "<u4"),
                       ("seg_len", "<u4", 8)])       # lmz/codec.py:50
 assert (STREAM_JOB.itemsize, CHUNK_JOB.itemsize, COND_JOB.itemsize, BF16C_HDR.itemsize) == \
     (32, 104, 144, 46)
+assert FUSED_JOB.itemsize == 40
 
 
 @dataclass
@@ -56,9 +59,10 @@ class Plan:
     seg_jobs: np.ndarray
     chunks: np.ndarray
     piece_chunk: np.ndarray
-    piece_split: np.ndarray        # 5 boundaries
+    piece_split: np.ndarray        # 6 boundaries: p1 cond, p1 plain, fused, p2 cond, p2 plain
     cond_jobs: np.ndarray
     cond_pieces: np.ndarray
+    fused_jobs: np.ndarray = field(default=None)
     stream_owner: np.ndarray = field(default=None)   # record index of each stream job
     coded_bytes: int = 0           # sum of clen: algorithmic bytes read
     base_bytes: int = 0            # bytes of delta bases read back
@@ -76,7 +80,9 @@ def _align16(x):
     return (x + 15) & ~15
 
 
-def build_plan(ar: fmt.Archive) -> Plan:
+def build_plan(ar: fmt.Archive, fuse: bool = True) -> Plan:
+    """`fuse` routes BF16 chunks whose exponent plane is rANS and whose sign/mantissa
+    plane is stored to the fused decode+merge+checksum kernel (no scratch plane)."""
     ar.check_coverage()
     blob, r = ar.blob, ar.records
     N = r.size
@@ -134,6 +140,10 @@ def build_plan(ar: fmt.Archive) -> Plan:
         sj_owner.append(owner); sj_plane.append(np.broadcast_to(plane, owner.shape))
 
     known = np.zeros(N, dtype=bool)
+    fused = np.zeros(N, dtype=bool)
+    f_src = np.zeros(N, dtype=np.int64)
+    f_len = np.zeros(N, dtype=np.int64)
+    f_mant = np.zeros(N, dtype=np.int64)
 
     # stored, and refs (a copy out of the output space)
     i = np.nonzero((ecodec == fmt.CODEC_STORED) & ~is_ref)[0]
@@ -197,6 +207,12 @@ def build_plan(ar: fmt.Archive) -> Plan:
             if (stored & (lens != nelem[:, None])).any():
                 raise CorruptArchive("a stored plane's length differs from the element count")
             plane_off[i[:, None], np.arange(npl)[None, :]] = starts
+            if fuse and cid == fmt.CODEC_BF16:
+                fz = ~pass2[i] & ~stored[:, 0] & stored[:, 1] & (nelem > 0)
+                fi = i[fz]
+                fused[fi] = True
+                f_src[fi], f_len[fi], f_mant[fi] = starts[fz, 0], lens[fz, 0], starts[fz, 1]
+                stored = stored | fz[:, None]          # no scratch stream for these
             rr, pp = np.nonzero(~stored)
             add_streams(starts[rr, pp], lens[rr, pp], nelem[rr], i[rr], pp)
             np.bitwise_or.at(scratch_mask, i[rr], (1 << pp).astype(np.uint8))
@@ -280,7 +296,7 @@ def build_plan(ar: fmt.Archive) -> Plan:
         seg_jobs["src_len"] = cond["seg_len"].reshape(-1)
 
     # ---- chunk jobs in launch order ----------------------------------------------
-    group = pass2.astype(np.int64) * 2 + (kind != K_COND)
+    group = np.where(pass2, 3, 0) + (kind != K_COND) + (fused & ~pass2)
     corder = np.argsort(group, kind="stable")
     chunks = np.zeros(N, dtype=CHUNK_JOB)
     chunks["dst_off"] = dst[corder]
@@ -295,7 +311,7 @@ def build_plan(ar: fmt.Archive) -> Plan:
     chunks["piece0"] = piece0
     piece_chunk = np.repeat(np.arange(N, dtype=np.uint32), npieces)
     g = group[corder]
-    split = np.array([0] + [int(npieces[g <= k].sum()) for k in range(4)], dtype=np.uint32)
+    split = np.array([0] + [int(npieces[g <= k].sum()) for k in range(5)], dtype=np.uint32)
     if ci.size:
         pos_of = np.empty(N, dtype=np.int64)
         pos_of[corder] = np.arange(N)
@@ -303,6 +319,12 @@ def build_plan(ar: fmt.Archive) -> Plan:
         cond["piece0"] = piece0[pos_of[ci]]
         chunks["aux"][pos_of[ci]] = np.arange(ci.size)
     cond_pieces = np.nonzero(chunks["kind"][piece_chunk] == K_COND)[0].astype(np.uint32)
+    fpos = np.nonzero(g == 2)[0]                    # fused chunks, in launch order
+    fused_jobs = np.zeros(fpos.size, dtype=FUSED_JOB)
+    frec = corder[fpos]
+    fused_jobs["src_off"], fused_jobs["src_len"] = f_src[frec], f_len[frec]
+    fused_jobs["mant_off"], fused_jobs["dst_off"] = f_mant[frec], dst[frec]
+    fused_jobs["n"], fused_jobs["piece0"] = rlen[frec] // 2, piece0[fpos]
 
     payload = blob[:int(ar.table_off)]
     if extras:
@@ -310,7 +332,7 @@ def build_plan(ar: fmt.Archive) -> Plan:
     return Plan(payload=payload, total=ar.total, scratch_bytes=scratch_pos + 64,
                 stream_jobs=stream_jobs, seg_jobs=seg_jobs, chunks=chunks,
                 piece_chunk=piece_chunk, piece_split=split, cond_jobs=cond,
-                cond_pieces=cond_pieces, stream_owner=s_owner[order],
+                cond_pieces=cond_pieces, stream_owner=s_owner[order], fused_jobs=fused_jobs,
                 coded_bytes=int(clen.sum()), base_bytes=int(rlen[is_delta].sum()))
 
 

@@ -36,11 +36,11 @@ def test_library_exports_every_declared_symbol(lib_path):
     assert lib.lmz_gpu_abi_version() == 1
     assert lib.lmz_gpu_header_bytes() == 516 and lib.lmz_gpu_grain() == 1
     assert lib.lmz_gpu_pad_bytes() >= 272
-    sizes = (ctypes.c_uint * 4)()
+    sizes = (ctypes.c_uint * 5)()
     lib.lmz_gpu_struct_sizes(ctypes.byref(sizes))
     from lmz_b200 import plan
     assert tuple(sizes) == (plan.STREAM_JOB.itemsize, plan.CHUNK_JOB.itemsize,
-                            plan.COND_JOB.itemsize, plan.COND_STATE_BYTES)
+                            plan.COND_JOB.itemsize, plan.COND_STATE_BYTES, plan.FUSED_JOB.itemsize)
     assert lib.lmz_gpu_piece_bytes() == plan.PIECE
 
 
@@ -169,7 +169,7 @@ def test_planner_enforces_single_hop_sources():
     blob = oa.write_archive([("a/0.safetensors", c0), ("a/1.safetensors", c1)])
     ar = archive.Archive(blob)
     p = plan.build_plan(ar)
-    assert p.piece_split[2] < p.piece_split[4], "expected refs/deltas in pass 2"
+    assert p.piece_split[3] < p.piece_split[5], "expected refs/deltas in pass 2"
     assert p.base_bytes > 0
     delta = int(np.nonzero(ar.records["codec"] == 8)[0][0])
     other = int(np.nonzero(ar.records["codec"] == 4)[0][0])
