@@ -271,7 +271,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
 #pragma unroll
         for (int i = 0; i < 5; i++) m[i] = __ldg(mq + i);
     }
-    uint32_t acc = 0;
+    // CRC of a tile is folded in while the NEXT tile decodes (its 36 dependent table
+    // lookups hide behind the decode chain); `wp` holds the tile waiting to be folded.
+    uint32_t acc = 0, wp[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    bool pending = false;
 
     // ---- tiles of 128 symbols ---------------------------------------------------------
     const uint32_t warp_tiles = __reduce_max_sync(0xffffffffu, my_tiles);
@@ -289,12 +292,22 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
         uint32_t caddr = caddr0;
         const bool full = __all_sync(0xffffffffu, rem >= TILE);
         if (full) {
+            if (SINK == SINK_BF16 && CRC && pending) acc = crc_advance<F_LOGR>(tl, acc);
 #pragma unroll
             for (uint32_t s = 0; s < TILE / NLANES; s++) {
                 uint32_t e = stream_step(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, true);
                 sts_u8(stage_sa + s * NLANES + k, e);
+                if (SINK == SINK_BF16 && CRC && (s & 1u) && pending)
+                    acc = crc_feed4<F_LOGR>(tl, acc ^ wp[s >> 1]);
             }
+            pending = false;
         } else {
+            if (SINK == SINK_BF16 && CRC && pending) {
+                acc = crc_advance<F_LOGR>(tl, acc);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc = crc_feed4<F_LOGR>(tl, acc ^ wp[i]);
+                pending = false;
+            }
 #pragma unroll 1
             for (uint32_t s = 0; s < TILE / NLANES; s++) {
                 bool active = s * NLANES + k < rem;
@@ -361,11 +374,15 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
             }
         }
         if (CRC) {
-            acc = crc_advance<F_LOGR>(tl, acc);
-#pragma unroll
-            for (int i = 0; i < 8; i++) acc = crc_feed4<F_LOGR>(tl, acc ^ w[i]);
             const bool last = t + 1 == my_tiles;
-            if ((t & 255u) == 255u || last) {
+            if (!((t & 255u) == 255u || last)) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) wp[i] = w[i];
+                pending = true;
+            } else {
+                acc = crc_advance<F_LOGR>(tl, acc);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc = crc_feed4<F_LOGR>(tl, acc ^ w[i]);
                 // close the 64 KiB piece: lane units -> row end, XOR over the group
                 uint32_t v = crc_mulmod(a.tabs->lane_mul8[k], acc);
                 v ^= __shfl_xor_sync(grp_mask, v, 1);

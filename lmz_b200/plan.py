@@ -80,11 +80,14 @@ def _align16(x):
     return (x + 15) & ~15
 
 
-def build_plan(ar: fmt.Archive, fuse: bool = True) -> Plan:
+def build_plan(ar: fmt.Archive, fuse: bool = True, select=None) -> Plan:
     """`fuse` routes BF16 chunks whose exponent plane is rANS and whose sign/mantissa
-    plane is stored to the fused decode+merge+checksum kernel (no scratch plane)."""
+    plane is stored to the fused decode+merge+checksum kernel (no scratch plane).
+    `select` (record indices) plans only those chunks -- one rank's share of a
+    partitioned decode, sources of its refs and deltas included by the caller."""
     ar.check_coverage()
-    blob, r = ar.blob, ar.records
+    blob = ar.blob
+    r = ar.records if select is None else ar.records[np.asarray(select, dtype=np.int64)]
     N = r.size
     codec = r["codec"].astype(np.int64)
     off = r["off"].astype(np.int64)
