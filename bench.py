@@ -53,6 +53,8 @@ def parse_args():
     ap.add_argument("--chunk-size", type=int, default=0, help="override the layout's chunk size")
     ap.add_argument("--seed", type=int, default=1)
     ap.add_argument("--no-crc", action="store_true", help="skip the per-chunk crc32")
+    ap.add_argument("--no-fuse", action="store_true",
+                    help="decode planes to scratch and merge in k_finish instead of the fused kernel")
     ap.add_argument("--no-cache", action="store_true")
     ap.add_argument("--cpu-sample-mb", type=int, default=2048)
     return ap.parse_args()
@@ -195,7 +197,7 @@ def main():
     if not ok:
         raise SystemExit(f"the CUDA library is unavailable: {why}")
     blob = get_archive(a, rank, barrier)
-    dec = decode.ArchiveDecoder(blob, checksum=not a.no_crc)
+    dec = decode.ArchiveDecoder(blob, checksum=not a.no_crc, fuse=not a.no_fuse)
     p = dec.plan
     plain, coded = p.total, p.coded_bytes
 
@@ -278,6 +280,17 @@ def main():
     dom_bytes = kbytes[dom]
     achieved = dom_bytes / (phase_ms[dom] / 1e3) / 1e9
     whole = (coded + plain + p.base_bytes) / (ms / a.steps / 1e3) / 1e9
+    traffic = None
+    if dom == "fused":
+        # DRAM bytes of one launch, scaled from the committed ncu capture of a smaller
+        # archive of the same chunks (traffic is proportional to the chunks processed)
+        try:
+            with open(os.path.join(ROOT, "profiles", "k_stream_bf16_dram_traffic.json")) as f:
+                tj = json.load(f)
+            traffic = int((tj["dram_bytes_read"] + tj["dram_bytes_write"])
+                          * (2 * int(fj["n"].sum())) / tj["plaintext_bytes"])
+        except Exception:
+            traffic = None
     cpu_v, cpu_what, cpu_kind = cpu_decode_sample(blob, a.cpu_sample_mb, os.cpu_count() or 1,
                                                   "reference")
     line = {
@@ -295,7 +308,7 @@ def main():
         "gpu_launches": int(dec.launches_per_run * a.steps),
         "roofline": {"bound": "hbm", "kernel": kname[dom],
                      "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_kind,
+                     "frac": round(achieved / peak, 4), "traffic": traffic, "peak_source": peak_kind,
                      "algorithmic_bytes_per_launch": dom_bytes,
                      "whole_decode": {"achieved": round(whole, 1), "frac": round(whole / peak, 4),
                                       "bytes": coded + plain + p.base_bytes}},
