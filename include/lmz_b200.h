@@ -104,6 +104,25 @@ int lmz_gpu_decode_streams_dev(const void *d_jobs, unsigned njobs, const void *d
                                void *d_dst, const void *d_shared_hdr, void *d_status,
                                void *d_any_bad, void *cuda_stream);
 
+/* No counterpart in the reference.  lmz_gpu_decode_batch_dev with per-stream
+ * verdicts, for callers that may not allocate device memory -- a server or trainer
+ * whose own pool already owns all of HBM, or a loader running where its host
+ * framework forbids driver allocations.  The verdicts live in a fixed device array
+ * inside the library (LMZ_GPU_NOALLOC_MAX_STREAMS * 4 + 256 bytes on every GPU that
+ * loads it, held until the process exits); nothing is allocated or freed here.
+ *
+ * Arguments as lmz_gpu_decode_batch_dev (no tpb).  h_status is host memory for nstr
+ * uint32 verdicts (0 ok, 1 bad header, 2 truncated, 3 input timeout, 0x100 trailing
+ * slack) or NULL.  The call waits for cuda_stream and returns LMZ_GPU_EBADSTREAM if
+ * any stream failed, LMZ_GPU_EUNSUPPORTED if nstr exceeds the maximum (split the
+ * batch).  The first call on each device looks up the array's device address; make
+ * that call before starting any stream capture.  All calls on a device share the
+ * array: calls that overlap on the GPU race on it, so issue them one at a time. */
+#define LMZ_GPU_NOALLOC_MAX_STREAMS 65536u
+int lmz_gpu_decode_batch_dev_noalloc(const void *d_hdr, const void *d_streams, const void *d_off,
+                                     unsigned nstr, unsigned plane, void *d_out,
+                                     void *cuda_stream, uint32_t *h_status);
+
 /* ---- whole-archive decode ---------------------------------------------------
  * The reference has no GPU counterpart for anything below: its chunk framing,
  * plane merge, exponent conditioning, delta undo and checksum run on the CPU

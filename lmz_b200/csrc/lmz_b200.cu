@@ -277,3 +277,80 @@ API int lmz_gpu_decode_streams_dev(const void *d_jobs, unsigned njobs, const voi
 }
 
 #include "chunk_abi.inl"
+
+// ------------------------------------------------- checked decode, no allocation
+
+// Some hosts cannot let a plug-in allocate device memory: an inference server or
+// training job whose own pool has already claimed all of HBM (cudaMalloc then fails
+// or fragments the pool), or a loader that runs where the embedding framework
+// forbids driver allocations.  lmz_gpu_decode_batch_dev serves them but cannot say
+// whether a stream was truncated, because its per-stream verdicts need memory the
+// reference's signature has no argument for.  This entry point keeps those verdicts
+// in a fixed device array that is part of the library image instead.
+//
+// The array costs LMZ_GPU_NOALLOC_MAX_STREAMS * 4 + 256 bytes on every GPU that
+// loads the library, until the process exits.  Every call on a device shares it:
+// calls that overlap on the GPU (different CUDA streams, different host threads)
+// race on the verdicts and must be serialised by the caller.
+static __device__ __align__(256) uint32_t g_noalloc_verdicts[64 + LMZ_GPU_NOALLOC_MAX_STREAMS];
+
+// In host code the array's name only stands for the symbol; the address a kernel
+// can use comes from cudaGetSymbolAddress, per device, with that device current.
+static int noalloc_scratch(uint32_t **out)
+{
+    static uint32_t *ptr_of[64];
+    static std::mutex mu;
+    int dev = 0;
+    CK("cudaGetDevice", cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail_msg(LMZ_GPU_EUNSUPPORTED, "device index above 63");
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptr_of[dev]) {
+        void *p = nullptr;
+        CK("cudaGetSymbolAddress(verdicts)", cudaGetSymbolAddress(&p, g_noalloc_verdicts));
+        ptr_of[dev] = static_cast<uint32_t *>(p);
+    }
+    *out = ptr_of[dev];
+    return LMZ_GPU_OK;
+}
+
+API int lmz_gpu_decode_batch_dev_noalloc(const void *d_hdr, const void *d_streams,
+                                         const void *d_off, unsigned nstr, unsigned plane,
+                                         void *d_out, void *cuda_stream, uint32_t *h_status)
+{
+    if (nstr == 0) return LMZ_GPU_OK;
+    if (plane == 0) return fail_msg(LMZ_GPU_EUNSUPPORTED, "plane is zero");
+    if (nstr > LMZ_GPU_NOALLOC_MAX_STREAMS) {
+        snprintf(g_err, sizeof g_err,
+                 "lmz_gpu_decode_batch_dev_noalloc takes at most %u streams per call, got %u; "
+                 "split the batch", (unsigned)LMZ_GPU_NOALLOC_MAX_STREAMS, nstr);
+        return LMZ_GPU_EUNSUPPORTED;
+    }
+    int rc = device_ready();
+    if (rc) return rc;
+    uint32_t *scratch = nullptr;
+    rc = noalloc_scratch(&scratch);          // first call on a device resolves the symbol
+    if (rc) return rc;
+    cudaStream_t cs = (cudaStream_t)cuda_stream;
+    // the summary word keeps the previous call's value: it must start at zero
+    CK("cudaMemsetAsync(verdict summary)", cudaMemsetAsync(scratch, 0, 256, cs));
+    RansArgs a{};
+    a.src = (const uint8_t *)d_streams;
+    a.offs = (const uint64_t *)d_off;
+    a.plane = plane;
+    a.njobs = nstr;
+    a.dst = (uint8_t *)d_out;
+    a.shared_hdr = (const uint8_t *)d_hdr;
+    a.status = scratch + 64;                 // every job writes its own word
+    a.any_bad = scratch;
+    rc = launch_rans(a, cs);
+    if (rc) return rc;
+    uint32_t bad = 0;
+    CK("cudaMemcpyAsync(verdict summary)",
+       cudaMemcpyAsync(&bad, scratch, sizeof bad, cudaMemcpyDeviceToHost, cs));
+    if (h_status)
+        CK("cudaMemcpyAsync(verdicts)", cudaMemcpyAsync(h_status, scratch + 64, (size_t)nstr * 4,
+                                                        cudaMemcpyDeviceToHost, cs));
+    CK("cudaStreamSynchronize", cudaStreamSynchronize(cs));
+    if (bad) return fail_msg(LMZ_GPU_EBADSTREAM, "a stream is malformed or truncated");
+    return LMZ_GPU_OK;
+}
