@@ -73,10 +73,13 @@ class ArchiveDecoder:
         d = self.device
         with torch.cuda.device(d):
             pad = gpu.pad_bytes()
-            self.d_payload = torch.empty(p.payload.size + pad, dtype=torch.uint8, device=d)
-            self.h2d_bytes = int(p.payload.size)
+            nbytes = p.payload.size + p.extras.size
+            self.d_payload = torch.empty(nbytes + pad, dtype=torch.uint8, device=d)
+            self.h2d_bytes = int(nbytes)
+            self.d_payload[nbytes:].zero_()
+            if p.extras.size:
+                self.d_payload[p.payload.size:nbytes].copy_(torch.from_numpy(p.extras.copy()))
             self.upload()
-            self.d_payload[p.payload.size:].zero_()
             self.d_scratch = torch.empty(max(p.scratch_bytes, 64), dtype=torch.uint8, device=d)
             self.d_out = out if out is not None else \
                 torch.empty(p.total + 64, dtype=torch.uint8, device=d)
@@ -131,10 +134,16 @@ class ArchiveDecoder:
             int(sum(p.piece_split[i + 1] > p.piece_split[i] for i in (0, 1, 3, 4))) + 1
 
     def upload(self, pinned=None, non_blocking: bool = False):
-        """Copy the payload host -> device (from `pinned` if given)."""
+        """Copy the archive's payload region host -> device (from `pinned`, a host
+        uint8 tensor of `plan.payload.size` bytes, if given)."""
+        import warnings
+
         import torch
-        src = pinned if pinned is not None else torch.from_numpy(self.plan.payload)
-        self.d_payload[:self.plan.payload.size].copy_(src, non_blocking=non_blocking)
+        if pinned is None:
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")          # read-only numpy views are fine to read
+                pinned = torch.from_numpy(self.plan.payload)
+        self.d_payload[:self.plan.payload.size].copy_(pinned, non_blocking=non_blocking)
 
     def run(self, stream=None, phases: int = 0):
         """Launch the decode on `stream` (default: torch's current). Asynchronous.

@@ -52,7 +52,8 @@ assert FUSED_JOB.itemsize == 40
 
 @dataclass
 class Plan:
-    payload: np.ndarray            # bytes to upload: archive payload region (+ host-inflated chunks)
+    payload: np.ndarray            # archive bytes [0, table_off): a view, never copied
+    extras: np.ndarray             # host-inflated header chunks, placed right after the payload
     total: int                     # size of the output space
     scratch_bytes: int
     stream_jobs: np.ndarray
@@ -330,9 +331,8 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None) -> Plan:
     fused_jobs["n"], fused_jobs["piece0"] = rlen[frec] // 2, piece0[fpos]
 
     payload = blob[:int(ar.table_off)]
-    if extras:
-        payload = np.concatenate([payload] + extras)
-    return Plan(payload=payload, total=ar.total, scratch_bytes=scratch_pos + 64,
+    extra = np.concatenate(extras) if extras else np.zeros(0, dtype=np.uint8)
+    return Plan(payload=payload, extras=extra, total=ar.total, scratch_bytes=scratch_pos + 64,
                 stream_jobs=stream_jobs, seg_jobs=seg_jobs, chunks=chunks,
                 piece_chunk=piece_chunk, piece_split=split, cond_jobs=cond,
                 cond_pieces=cond_pieces, stream_owner=s_owner[order], fused_jobs=fused_jobs,
