@@ -136,7 +136,7 @@ constexpr uint32_t FINISH_THREADS = 256;   // threads that finish one piece toge
 __host__ __device__ constexpr uint32_t finish_table_bytes(int logr) { return 8u * (1024u << logr); }
 __host__ __device__ constexpr uint32_t finish_sub_bytes(bool cond)
 {
-    return 2048 + (cond ? 2 * PADDED_PIECE + 256 : 0);
+    return 2048 + (cond ? 2 * PADDED_PIECE + 256 + 8 * FINISH_THREADS * 4 + 64 : 0);
 }
 __host__ __device__ constexpr uint32_t finish_smem(bool cond, int logr, int subs)
 {
@@ -283,27 +283,33 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
             sub_sync();
             uint64_t blo = 0, bhi = 0;
             for (uint32_t wv = 0; wv < warp; wv++) { blo += s_w[wv * 2]; bhi += s_w[wv * 2 + 1]; }
-            uint64_t xlo = ilo - lo + blo, xhi = ihi - hi + bhi;   // exclusive, may reach 32768
-            // phase C: walk the run, gathering each element's byte from its segment
-            const uint8_t *segp[8];
+            const uint64_t xlo = ilo - lo + blo, xhi = ihi - hi + bhi;   // exclusive, may reach 32768
+            // phase C: walk the run, gathering each element's byte from its segment.  The
+            // running rank of each bucket lives in shared memory ([bucket][thread], one
+            // bank per lane) and the eight segment pointers in a small shared table, so an
+            // element costs a handful of instructions instead of an 8-way select chain.
+            uint32_t *s_rank = reinterpret_cast<uint32_t *>(s_lut + 256);           // 8 x 256
+            uint64_t *s_seg = reinterpret_cast<uint64_t *>(s_rank + 8 * FINISH_THREADS);
 #pragma unroll
             for (int b = 0; b < 8; b++)
-                segp[b] = (cs.seg_in_scratch >> b & 1 ? a.scratch : a.payload) + cs.seg_ptr[b] +
-                          s_red[256 + b];
+                s_rank[b * FINISH_THREADS + t] =
+                    (uint32_t)((b & 4 ? xhi : xlo) >> (16 * (b & 3))) & 0xffffu;
+            if (t < 8)
+                s_seg[t] = reinterpret_cast<uint64_t>(
+                    (cs.seg_in_scratch >> t & 1 ? a.scratch : a.payload) + cs.seg_ptr[t] +
+                    s_red[256 + t]);
+            sub_sync();
             for (uint32_t j = 0; j < 128; j += 4) {
                 uint32_t w = smem_word(s_exp, pad128(my0 + j)), o = 0;
 #pragma unroll
                 for (int z = 0; z < 4; z++) {
                     if (my0 + j + z < ne) {
-                        uint32_t b = s_lut[(w >> (8 * z)) & 0xff];
-                        uint32_t sh = 16 * (b & 3);
-                        uint32_t idx;
-                        if (b & 4) { idx = (uint32_t)(xhi >> sh) & 0xffffu; xhi += 1ull << sh; }
-                        else { idx = (uint32_t)(xlo >> sh) & 0xffffu; xlo += 1ull << sh; }
-                        const uint8_t *sp = segp[0];
-#pragma unroll
-                        for (int bb = 1; bb < 8; bb++) sp = b == bb ? segp[bb] : sp;
-                        o |= (uint32_t)sp[idx] << (8 * z);
+                        const uint32_t b = s_lut[(w >> (8 * z)) & 0xff];
+                        uint32_t *rk = s_rank + b * FINISH_THREADS + t;
+                        const uint32_t idx = *rk;
+                        *rk = idx + 1;
+                        const uint8_t *sp = reinterpret_cast<const uint8_t *>(s_seg[b]);
+                        o |= (uint32_t)__ldg(sp + idx) << (8 * z);
                     }
                 }
                 *reinterpret_cast<uint32_t *>(s_sm + pad128(my0 + j)) = o;

@@ -15,7 +15,7 @@ struct CondArgs {
     uint32_t ncond;
     uint32_t *hist;                // ncond x 256, zeroed by the caller
     uint32_t *piece_cnt;           // npieces x 8
-    StreamJob *seg_jobs;           // 8 slots per cond chunk, filled in by k_cond_plan
+    StreamJob *seg_jobs;           // one slot per rANS-coded segment, sized by k_cond_plan
     const uint8_t *payload;
     const uint8_t *scratch;
 };
@@ -80,20 +80,21 @@ __global__ void k_cond_plan(CondArgs a)
     }
     uint32_t status = total == cj.nelem ? ST_OK : ST_BAD_SHAPE;
     uint64_t run = 0;
-    uint32_t in_scratch = 0;
+    uint32_t in_scratch = 0, nj = 0;      // nj: this chunk's rANS segments seen so far
 #pragma unroll
     for (int j = 0; j < COND_BUCKETS; j++) {
         uint32_t want = counts[j], ln = cj.seg_len[j], m = cj.seg_method[j];
         cs.counts[j] = want;
-        StreamJob &sj = a.seg_jobs[cj.seg_job0 + j];
-        sj.n = 0;
+        cs.seg_ptr[j] = cj.seg_src[j];
+        // the host made one job slot per rANS-coded, non-empty segment, in bucket order
+        const bool slot = m == 3 && ln != 0;
+        if (slot) a.seg_jobs[cj.seg_job0 + nj].n = 0;
         if (want == 0) {
             if (ln) status = ST_BAD_SHAPE;
-            cs.seg_ptr[j] = cj.seg_src[j];
         } else if (m == 0) {
             if (ln != want) status = ST_BAD_SHAPE;
-            cs.seg_ptr[j] = cj.seg_src[j];
-        } else if (m == 3) {
+        } else if (slot) {
+            StreamJob &sj = a.seg_jobs[cj.seg_job0 + nj];
             cs.seg_ptr[j] = cj.seg_scratch + run;
             in_scratch |= 1u << j;
             sj.dst_off = cj.seg_scratch + run;
@@ -101,11 +102,11 @@ __global__ void k_cond_plan(CondArgs a)
             run += want;
         } else {
             status = ST_BAD_SHAPE;
-            cs.seg_ptr[j] = cj.seg_src[j];
         }
+        nj += slot;
     }
     if (status != ST_OK)
-        for (int j = 0; j < COND_BUCKETS; j++) a.seg_jobs[cj.seg_job0 + j].n = 0;
+        for (uint32_t j = 0; j < nj; j++) a.seg_jobs[cj.seg_job0 + j].n = 0;
     cs.seg_in_scratch = in_scratch;
     cs.status = status;
 }
@@ -121,19 +122,18 @@ __global__ void __launch_bounds__(256) k_cond_count(CondArgs a)
     const uint8_t *exp = cond_exp_piece(a, q, ci, ne);
     lut[t] = a.cond_state[ci].lut[t];
     __syncthreads();
-    uint32_t c[COND_BUCKETS] = {0, 0, 0, 0, 0, 0, 0, 0};
+    // one 8-bit field per bucket in a 64-bit word: a thread sees at most 128 elements
+    uint64_t packed = 0;
     for (uint32_t i = t * 4; i < ne; i += 256 * 4) {
         uint32_t w[1];
         load_words<1>(exp + i, w);
 #pragma unroll
-        for (int z = 0; z < 4; z++) {
-            if (i + z < ne) {
-                uint32_t b = lut[(w[0] >> (8 * z)) & 0xff];
-#pragma unroll
-                for (int j = 0; j < COND_BUCKETS; j++) c[j] += b == (uint32_t)j;
-            }
-        }
+        for (int z = 0; z < 4; z++)
+            if (i + z < ne) packed += 1ull << (8 * lut[(w[0] >> (8 * z)) & 0xff]);
     }
+    uint32_t c[COND_BUCKETS];
+#pragma unroll
+    for (int j = 0; j < COND_BUCKETS; j++) c[j] = (uint32_t)(packed >> (8 * j)) & 0xffu;
 #pragma unroll
     for (int j = 0; j < COND_BUCKETS; j++) {
         uint32_t v = c[j];

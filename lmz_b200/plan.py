@@ -289,15 +289,19 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None) -> Plan:
         seg_sizes = _align16(seg_rans_total)
         cond["seg_scratch"] = scratch_pos + np.cumsum(seg_sizes) - seg_sizes
         scratch_pos += int(seg_sizes.sum())
-        cond["seg_job0"] = np.arange(ci.size) * 8
+        is_job = (cond["seg_method"] == fmt.METHOD_RANS) & (cond["seg_len"] > 0)
+        per = is_job.sum(axis=1)
+        cond["seg_job0"] = np.cumsum(per) - per
     order = np.argsort(-s_n, kind="stable")         # long streams first
     stream_jobs = np.zeros(s_n.size, dtype=STREAM_JOB)
     stream_jobs["src_off"], stream_jobs["dst_off"] = s_src[order], s_dst[order]
     stream_jobs["src_len"], stream_jobs["n"] = s_len[order], s_n[order]
-    seg_jobs = np.zeros(ci.size * 8, dtype=STREAM_JOB)
     if ci.size:
-        seg_jobs["src_off"] = cond["seg_src"].reshape(-1)
-        seg_jobs["src_len"] = cond["seg_len"].reshape(-1)
+        seg_jobs = np.zeros(int(is_job.sum()), dtype=STREAM_JOB)
+        seg_jobs["src_off"] = cond["seg_src"][is_job]        # row-major: chunk, then bucket
+        seg_jobs["src_len"] = cond["seg_len"][is_job]
+    else:
+        seg_jobs = np.zeros(0, dtype=STREAM_JOB)
 
     # ---- chunk jobs in launch order ----------------------------------------------
     group = np.where(pass2, 3, 0) + (kind != K_COND) + (fused & ~pass2)

