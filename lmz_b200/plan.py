@@ -81,18 +81,23 @@ def _align16(x):
     return (x + 15) & ~15
 
 
-def build_plan(ar: fmt.Archive, fuse: bool = True, select=None) -> Plan:
+def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=None) -> Plan:
     """`fuse` routes BF16 chunks whose exponent plane is rANS and whose sign/mantissa
     plane is stored to the fused decode+merge+checksum kernel (no scratch plane).
     `select` (record indices) plans only those chunks -- one rank's share of a
-    partitioned decode, sources of its refs and deltas included by the caller."""
+    partitioned decode, sources of its refs and deltas included by the caller.
+    `payload_range` = (lo, hi) uploads only those archive bytes (every selected chunk's
+    payload must lie inside); offsets in the plan are then relative to `lo`."""
     ar.check_coverage()
-    blob = ar.blob
     r = ar.records if select is None else ar.records[np.asarray(select, dtype=np.int64)]
+    lo, hi = (0, int(ar.table_off)) if payload_range is None else map(int, payload_range)
+    blob = ar.blob[lo:]
     N = r.size
     codec = r["codec"].astype(np.int64)
-    off = r["off"].astype(np.int64)
+    off = r["off"].astype(np.int64) - lo
     clen = r["clen"].astype(np.int64)
+    if r.size and ((off < 0).any() or (off + clen > hi - lo).any()):
+        raise FormatError("a selected chunk's payload lies outside the payload range")
     rlen = r["rlen"].astype(np.int64)
     dst = r["dst"].astype(np.int64)
     flags = r["flags"].astype(np.int64)
@@ -135,7 +140,7 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None) -> Plan:
     plane_off = np.zeros((N, 8), dtype=np.uint64)
     scratch_mask = np.zeros(N, dtype=np.uint8)
     src_is_out = np.zeros(N, dtype=np.uint8)
-    extras, extra_pos = [], int(ar.table_off)
+    extras, extra_pos = [], hi - lo
     # stream jobs, collected as columns; dst assigned once all are known
     sj_src, sj_len, sj_n, sj_owner, sj_plane = [], [], [], [], []
 
@@ -334,7 +339,7 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None) -> Plan:
     fused_jobs["mant_off"], fused_jobs["dst_off"] = f_mant[frec], dst[frec]
     fused_jobs["n"], fused_jobs["piece0"] = rlen[frec] // 2, piece0[fpos]
 
-    payload = blob[:int(ar.table_off)]
+    payload = blob[:hi - lo]
     extra = np.concatenate(extras) if extras else np.zeros(0, dtype=np.uint8)
     return Plan(payload=payload, extras=extra, total=ar.total, scratch_bytes=scratch_pos + 64,
                 stream_jobs=stream_jobs, seg_jobs=seg_jobs, chunks=chunks,

@@ -168,3 +168,16 @@ def test_reference_written_streams_decode(gpu):
         blob, offs = pack_streams([stream.tobytes()] * 3)
         out = gpu.decode_batch(blob, offs, 3, plain.size)
         assert bytes(out) == plain.tobytes() * 3, case
+
+
+def test_pipelined_upload_decodes_the_same_bytes(shard):
+    import torch
+    from lmz_b200 import decode
+    for kw in (dict(mapped=True), dict()):
+        blob = oa.write_archive([("m.safetensors", shard)], **kw)
+        pd = decode.PipelinedDecoder(blob, nslices=5)
+        assert len(pd.slices) == (5 if kw else min(5, len(pd.slices)))
+        pinned = torch.frombuffer(bytearray(blob), dtype=torch.uint8).pin_memory()
+        out = pd.run_from_host(pinned)
+        pd.check()
+        assert (out.cpu().numpy() == shard).all()
