@@ -60,6 +60,31 @@ static int sm_count(int *out)
     return LMZ_GPU_OK;
 }
 
+// A second stream per device, so the fused kernel (most of the work) overlaps the
+// few latency-bound streams and pieces that cannot be fused.  Created on first use.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+
+static int side_stream(SideStream **out)
+{
+    static SideStream per_dev[64];
+    static std::mutex mu;
+    int dev = 0;
+    CK("cudaGetDevice", cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) { *out = nullptr; return LMZ_GPU_OK; }
+    std::lock_guard<std::mutex> lock(mu);
+    SideStream &s = per_dev[dev];
+    if (!s.stream) {
+        CK("cudaStreamCreate", cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+        CK("cudaEventCreate", cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming));
+        CK("cudaEventCreate", cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming));
+    }
+    *out = &s;
+    return LMZ_GPU_OK;
+}
+
 API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
 {
     if (!p) return fail_msg(LMZ_GPU_EUNSUPPORTED, "no plan");
@@ -75,6 +100,41 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
 
     if (p->d_any_bad && (ph & 1u)) CK("memset any_bad", cudaMemsetAsync(p->d_any_bad, 0, 4, cs));
 
+    // 0. BF16 chunks with a coded exponent plane and a stored sign/mantissa plane:
+    //     decode, merge, write and checksum in one kernel
+    SideStream *side = nullptr;
+    const bool other_work = p->n_stream_jobs || p->n_cond || p->piece_split[2] > p->piece_split[0] ||
+                            p->piece_split[5] > p->piece_split[3];
+    if (p->n_fused && (ph & 16u)) {
+        cudaStream_t fs = cs;
+        if (ph == 0x1fu && other_work) {        // whole decode: run the fused kernel beside the rest
+            rc = side_stream(&side);
+            if (rc) return rc;
+            if (side) {
+                // record + wait as a pair: another host thread must not re-record the
+                // event in between
+                static std::mutex fork_mu;
+                std::lock_guard<std::mutex> lock(fork_mu);
+                CK("cudaEventRecord", cudaEventRecord(side->fork, cs));
+                CK("cudaStreamWaitEvent", cudaStreamWaitEvent(side->stream, side->fork, 0));
+                fs = side->stream;
+            }
+        }
+        StreamArgs sa{};
+        sa.src = (const uint8_t *)p->d_payload;
+        sa.jobs = (const FusedJob *)p->d_fused_jobs;
+        sa.njobs = p->n_fused;
+        sa.dst = (uint8_t *)p->d_out;
+        sa.status = (uint32_t *)p->d_fused_status;
+        sa.any_bad = (uint32_t *)p->d_any_bad;
+        sa.piece_crc = (uint32_t *)p->d_piece_crc;
+        sa.tabs = (const CrcTables *)p->d_crc_tables;
+        rc = p->d_piece_crc ? launch_stream<SINK_BF16, true>(sa, fs)
+                            : launch_stream<SINK_BF16, false>(sa, fs);
+        if (rc) return rc;
+        if (side) CK("cudaEventRecord", cudaEventRecord(side->join, side->stream));
+    }
+
     // 1. every rANS stream whose length is known up front, into scratch
     if (p->n_stream_jobs && (ph & 1u)) {
         RansArgs a{};
@@ -85,23 +145,6 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         a.status = (uint32_t *)p->d_stream_status;
         a.any_bad = (uint32_t *)p->d_any_bad;
         rc = launch_rans(a, cs);
-        if (rc) return rc;
-    }
-
-    // 1b. BF16 chunks with a coded exponent plane and a stored sign/mantissa plane:
-    //     decode, merge, write and checksum in one kernel
-    if (p->n_fused && (ph & 16u)) {
-        StreamArgs sa{};
-        sa.src = (const uint8_t *)p->d_payload;
-        sa.jobs = (const FusedJob *)p->d_fused_jobs;
-        sa.njobs = p->n_fused;
-        sa.dst = (uint8_t *)p->d_out;
-        sa.status = (uint32_t *)p->d_fused_status;
-        sa.any_bad = (uint32_t *)p->d_any_bad;
-        sa.piece_crc = (uint32_t *)p->d_piece_crc;
-        sa.tabs = (const CrcTables *)p->d_crc_tables;
-        rc = p->d_piece_crc ? launch_stream<SINK_BF16, true>(sa, cs)
-                            : launch_stream<SINK_BF16, false>(sa, cs);
         if (rc) return rc;
     }
 
@@ -151,8 +194,13 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     f.piece_cnt = (const uint32_t *)p->d_piece_cnt;
     // piece groups: 0 pass-1 conditioned, 1 pass-1 plain, 2 fused (done above),
     //               3 pass-2 conditioned, 4 pass-2 plain
+    if (side && !(ph & 4u)) CK("cudaStreamWaitEvent", cudaStreamWaitEvent(cs, side->join, 0));
     for (int part = 0; part < 5 && (ph & 4u); part++) {
-        if (part == 2) continue;
+        if (part == 2) {
+            // pass 2 (and the verdicts) read what the fused kernel wrote
+            if (side) CK("cudaStreamWaitEvent", cudaStreamWaitEvent(cs, side->join, 0));
+            continue;
+        }
         f.piece_begin = p->piece_split[part];
         f.piece_end = p->piece_split[part + 1];
         rc = (part == 0 || part == 3) ? launch_finish<true>(f, sms, cs)
