@@ -181,3 +181,49 @@ def test_pipelined_upload_decodes_the_same_bytes(shard):
         out = pd.run_from_host(pinned)
         pd.check()
         assert (out.cpu().numpy() == shard).all()
+
+
+def test_pythia_shaped_delta_chain():
+    """Checkpoint delta chain on the Pythia-160m architecture (12 layers, hidden 768,
+    FFN 3072, vocab 50304) at half width: checkpoint 0 from N(0, 0.02), each later one
+    the previous plus N(0, 1e-4) on a random 30 % of elements; both later checkpoints
+    are coded as deltas against checkpoint 0 (the earliest member holding the tensor)."""
+    h, f, v, layers = 384, 1536, 25152, 12
+    names = [("embed.weight", (v, h))]
+    for li in range(layers):
+        names += [(f"l{li}.attn.qkv.weight", (3 * h, h)), (f"l{li}.attn.o.weight", (h, h)),
+                  (f"l{li}.mlp.up.weight", (f, h)), (f"l{li}.mlp.down.weight", (h, f)),
+                  (f"l{li}.ln.weight", (h,))]
+    files, prev = [], None
+    for ck in range(3):
+        tensors = []
+        for i, (name, shape) in enumerate(names):
+            if len(shape) == 1:
+                data = synth.bf16_bytes(np.ones(shape, np.float32))
+            elif ck == 0:
+                data = synth.normal_bf16(shape, 7000 + i)
+            else:
+                data = synth.perturbed_bf16(prev[i], 100 * ck + i, frac=0.3, sigma=1e-4)
+            tensors.append((name, "BF16", shape, data))
+        prev = [t[3] for t in tensors]
+        files.append(synth.safetensors_bytes(tensors))
+    blob = oa.write_archive([(f"step{i}/model.safetensors", f) for i, f in enumerate(files)])
+    dec = _roundtrip(blob, np.concatenate(files))
+    recs = dec.archive.records
+    assert (recs["codec"] == 8).sum() >= 2 and (recs["codec"] == 4).sum() >= 1
+    assert len(blob) < 0.6 * sum(f.size for f in files)
+
+
+def test_per_rank_tensor_parallel_slices():
+    """Tensor-parallel slices as separate members: each rank's archive holds only its
+    slice (here FP32, esize-4 byte-plane chunks) and decodes on its own."""
+    rng = np.random.default_rng(11)
+    full = (rng.standard_normal((1024, 4096)) * 0.02).astype("<f4")
+    for rank in range(2):
+        col = np.ascontiguousarray(full[rank * 512:(rank + 1) * 512])          # column-parallel
+        row = np.ascontiguousarray(full[:, rank * 2048:(rank + 1) * 2048])     # row-parallel
+        src = synth.safetensors_bytes([("q.weight", "F32", col.shape, col.view(np.uint8).reshape(-1)),
+                                       ("o.weight", "F32", row.shape, row.view(np.uint8).reshape(-1))])
+        dec = _roundtrip(oa.write_archive([(f"rank{rank}.safetensors", src)]), src)
+        t = dec.tensors()[(f"rank{rank}.safetensors", "o.weight")]
+        assert t.cpu().numpy().tobytes() == row.tobytes()

@@ -105,3 +105,29 @@ def test_verify_reports_ok(gpu):
     r = gpu.verify(quick=True)
     assert r["ok"], r
     assert r["checked"] >= 5 and r["gbps"] > 0
+
+
+@pytest.mark.parametrize("dist", ["exponent", "uniform", "two"])
+def test_stress_extremes_long_streams_and_wide_batches(gpu, orc, dist, table_mode):
+    """The corners of the decoder stress matrix: 4 MiB streams (batch 1 and 7) and a
+    4096-stream batch, per-stream and shared tables.  The wide batch cycles a pool of
+    256 distinct streams so the CPU encoder stays out of the way."""
+    if table_mode == 0 and dist != "exponent":
+        pytest.skip("one distribution is enough for the plain narrow kernel")
+    big = [distribution(dist, 4 << 20, 1000 + i) for i in range(7)]
+    _check(gpu, orc, big[:1])
+    _check(gpu, orc, big)
+    pool = [distribution(dist, 4096, 50 + i) for i in range(256)]
+    plains = [pool[i % 256] for i in range(4096)]
+    streams = [orc.rans_encode(p) for p in pool]
+    blob, offs = pack_streams([streams[i % 256] for i in range(4096)])
+    out = np.frombuffer(gpu.decode_batch(blob, offs, 4096, 4096), dtype=np.uint8).reshape(4096, 4096)
+    assert (out == np.stack(plains)).all()
+    counts = np.sum([np.bincount(p, minlength=256) for p in pool], axis=0)
+    freqs = orc.rans_freqs(counts)
+    header = b"R1\0\0" + freqs.astype("<u2").tobytes()
+    shared = [orc.rans_encode_shared(p, freqs) for p in pool]
+    blob, offs = pack_streams([shared[i % 256] for i in range(4096)])
+    out = np.frombuffer(gpu.decode_batch(blob, offs, 4096, 4096, header=header),
+                        dtype=np.uint8).reshape(4096, 4096)
+    assert (out == np.stack(plains)).all()
