@@ -17,6 +17,7 @@
 #pragma once
 #include "common.cuh"
 #include "crc.cuh"
+#include <type_traits>
 
 namespace lmz {
 
@@ -75,6 +76,20 @@ __device__ __forceinline__ void load_words(const uint8_t *p, uint32_t (&w)[N])
     uint32_t v[N + 1];
 #pragma unroll
     for (int i = 0; i <= N; i++) v[i] = q[i];
+#pragma unroll
+    for (int i = 0; i < N; i++) w[i] = __funnelshift_r(v[i], v[i + 1], sh);
+}
+
+// The same through the read-only path, for data no thread of the kernel writes.
+template <int N>
+__device__ __forceinline__ void load_words_nc(const uint8_t *p, uint32_t (&w)[N])
+{
+    uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~uintptr_t(3));
+    uint32_t sh = (uint32_t)(a & 3u) * 8u;
+    uint32_t v[N + 1];
+#pragma unroll
+    for (int i = 0; i <= N; i++) v[i] = __ldg(q + i);
 #pragma unroll
     for (int i = 0; i < N; i++) w[i] = __funnelshift_r(v[i], v[i + 1], sh);
 }
@@ -241,10 +256,17 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
             const uint8_t *exp = (cj.exp_in_scratch ? a.scratch : a.payload) + cj.exp_off + e0;
             sub_sync();
             s_lut[t] = cs.lut[t];
-            for (uint32_t i = t * 4; i < PIECE_ELEMS; i += FINISH_THREADS * 4) {
-                uint32_t w[1] = {0};
-                if (i < ne) load_words<1>(exp + i, w);
-                *reinterpret_cast<uint32_t *>(s_exp + pad128(i)) = w[0];
+            for (uint32_t i0 = t * 4; i0 < PIECE_ELEMS; i0 += FINISH_THREADS * 4 * 8) {
+                uint32_t w[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    uint32_t i = i0 + u * FINISH_THREADS * 4, v[1] = {0};
+                    if (i < ne) load_words<1>(exp + i, v);
+                    w[u] = v[0];
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    *reinterpret_cast<uint32_t *>(s_exp + pad128(i0 + u * FINISH_THREADS * 4)) = w[u];
             }
             // ranks of this piece's first element within each bucket
             if (t < 8) s_red[256 + t] = 0;
@@ -299,28 +321,76 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
                     (cs.seg_in_scratch >> t & 1 ? a.scratch : a.payload) + cs.seg_ptr[t] +
                     s_red[256 + t]);
             sub_sync();
-            for (uint32_t j = 0; j < 128; j += 4) {
-                uint32_t w = smem_word(s_exp, pad128(my0 + j)), o = 0;
+            // 16 elements at a time: first every address (shared-memory work only), then
+            // the 16 byte loads back to back so they are all in flight together
+            for (uint32_t j = 0; j < 128; j += 16) {
+                const uint8_t *src[16];
 #pragma unroll
-                for (int z = 0; z < 4; z++) {
-                    if (my0 + j + z < ne) {
+                for (int q4 = 0; q4 < 4; q4++) {
+                    const uint32_t w = smem_word(s_exp, pad128(my0 + j + 4 * q4));
+#pragma unroll
+                    for (int z = 0; z < 4; z++) {
                         const uint32_t b = s_lut[(w >> (8 * z)) & 0xff];
                         uint32_t *rk = s_rank + b * FINISH_THREADS + t;
                         const uint32_t idx = *rk;
-                        *rk = idx + 1;
-                        const uint8_t *sp = reinterpret_cast<const uint8_t *>(s_seg[b]);
-                        o |= (uint32_t)__ldg(sp + idx) << (8 * z);
+                        const bool live = my0 + j + 4 * q4 + z < ne;
+                        if (live) *rk = idx + 1;
+                        // elements past the piece's end read the segment's first byte (unused)
+                        src[4 * q4 + z] = reinterpret_cast<const uint8_t *>(s_seg[b]) + (live ? idx : 0);
                     }
                 }
-                *reinterpret_cast<uint32_t *>(s_sm + pad128(my0 + j)) = o;
+                uint32_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int e = 0; e < 16; e++) o[e >> 2] |= (uint32_t)__ldg(src[e]) << (8 * (e & 3));
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++)
+                    *reinterpret_cast<uint32_t *>(s_sm + pad128(my0 + j + 4 * q4)) = o[q4];
             }
             sub_sync();
         }
 
         // ---- rows: every thread produces 16 output bytes per row ----------------
         uint32_t acc = 0;
+        // Fast path for the overwhelmingly common piece: full, 16-byte aligned, no delta
+        // base, copy or BF16 merge.  No per-row dispatch, loads on the read-only path and
+        // four rows unrolled so the loads of later rows overlap the CRC chain of earlier ones.
+        const bool fast = plen == PIECE_BYTES && al == 0 && base == nullptr &&
+                          (kind == K_COPY || kind == K_BF16 || (COND && kind == K_COND)) &&
+                          !(kind == K_COPY && c.src_is_out);
+        if (fast) {
+            auto rows = [&](auto kind_c) {
+                constexpr int KIND = decltype(kind_c)::value;
+#pragma unroll 4
+                for (uint32_t row = 0; row < PIECE_BYTES / ROW_BYTES; row++) {
+                    const uint32_t r = row * ROW_BYTES + t * 16;
+                    uint32_t w[4];
+                    if (KIND == K_COPY) {
+                        load_words_nc<4>(pl[0] + pbase + r, w);
+                    } else if (KIND == K_BF16) {
+                        uint32_t pa[2], pb[2];
+                        load_words_nc<2>(pl[0] + (pbase + r) / 2, pa);
+                        load_words_nc<2>(pl[1] + (pbase + r) / 2, pb);
+                        bf16_merge8(pa, pb, w);
+                    } else {
+                        const uint32_t i = pad128(r / 2);
+                        uint32_t pa[2] = {smem_word(s_exp, i), smem_word(s_exp, i + 4)};
+                        uint32_t pb[2] = {smem_word(s_sm, i), smem_word(s_sm, i + 4)};
+                        bf16_merge8(pa, pb, w);
+                    }
+                    *reinterpret_cast<uint4 *>(dst + r) = make_uint4(w[0], w[1], w[2], w[3]);
+                    if (do_crc) {
+                        acc = crc_advance<LOGR>(tl, acc);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) acc = crc_feed4<LOGR>(tl, acc ^ w[i]);
+                    }
+                }
+            };
+            if (kind == K_COPY) rows(std::integral_constant<int, K_COPY>{});
+            else if (kind == K_BF16) rows(std::integral_constant<int, K_BF16>{});
+            else rows(std::integral_constant<int, K_COND>{});
+        }
 #pragma unroll 1
-        for (uint32_t row = 0; row < PIECE_BYTES / ROW_BYTES; row++) {
+        for (uint32_t row = 0; !fast && row < PIECE_BYTES / ROW_BYTES; row++) {
             const uint32_t r = row * ROW_BYTES + t * 16;    // piece-relative
             uint32_t w[4] = {0, 0, 0, 0};
             if (r < plen) {

@@ -41,12 +41,22 @@ __global__ void __launch_bounds__(256) k_cond_hist(CondArgs a)
     __syncthreads();
     uint32_t ci, ne;
     const uint8_t *exp = cond_exp_piece(a, a.cond_pieces[blockIdx.x], ci, ne);
-    for (uint32_t i = t * 4; i < ne; i += 256 * 4) {
-        uint32_t w[1];
-        load_words<1>(exp + i, w);
+    // 32 KiB per piece = 32 words per thread; loaded 8 at a time so the reads overlap
+    for (uint32_t i0 = t * 4; i0 < ne; i0 += 256 * 4 * 8) {
+        uint32_t w[8];
 #pragma unroll
-        for (int z = 0; z < 4; z++)
-            if (i + z < ne) atomicAdd(&h[warp][(w[0] >> (8 * z)) & 0xff], 1u);
+        for (int u = 0; u < 8; u++) {
+            uint32_t i = i0 + u * 256 * 4, v[1] = {0};
+            if (i < ne) load_words<1>(exp + i, v);
+            w[u] = v[0];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            uint32_t i = i0 + u * 256 * 4;
+#pragma unroll
+            for (int z = 0; z < 4; z++)
+                if (i + z < ne) atomicAdd(&h[warp][(w[u] >> (8 * z)) & 0xff], 1u);
+        }
     }
     __syncthreads();
     uint32_t s = 0;
@@ -124,12 +134,21 @@ __global__ void __launch_bounds__(256) k_cond_count(CondArgs a)
     __syncthreads();
     // one 8-bit field per bucket in a 64-bit word: a thread sees at most 128 elements
     uint64_t packed = 0;
-    for (uint32_t i = t * 4; i < ne; i += 256 * 4) {
-        uint32_t w[1];
-        load_words<1>(exp + i, w);
+    for (uint32_t i0 = t * 4; i0 < ne; i0 += 256 * 4 * 8) {
+        uint32_t w[8];
 #pragma unroll
-        for (int z = 0; z < 4; z++)
-            if (i + z < ne) packed += 1ull << (8 * lut[(w[0] >> (8 * z)) & 0xff]);
+        for (int u = 0; u < 8; u++) {
+            uint32_t i = i0 + u * 256 * 4, v[1] = {0};
+            if (i < ne) load_words<1>(exp + i, v);
+            w[u] = v[0];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            uint32_t i = i0 + u * 256 * 4;
+#pragma unroll
+            for (int z = 0; z < 4; z++)
+                if (i + z < ne) packed += 1ull << (8 * lut[(w[u] >> (8 * z)) & 0xff]);
+        }
     }
     uint32_t c[COND_BUCKETS];
 #pragma unroll
