@@ -1,6 +1,7 @@
 // Additive C-ABI entry points for whole-archive decode (included by lmz_b200.cu).
 
 #include "cond_kernels.cuh"
+#include "cond_finish.cuh"
 
 static_assert(sizeof(lmz_stream_job) == sizeof(StreamJob), "public and device StreamJob differ");
 
@@ -26,24 +27,36 @@ API int lmz_gpu_crc_tables(void *host_dst, size_t cap)
     return (int)sizeof(CrcTables);
 }
 
-// Plain pieces: 4 sub-blocks (1024 threads) share CRC tables replicated 16x, one CTA
-// per SM.  Conditioned pieces stage 66 KiB per sub-block, so that variant runs one
-// sub-block per CTA with tables replicated 4x and two CTAs per SM.
-template <bool COND>
+// Plain pieces: 4 sub-blocks (1024 threads) share CRC tables replicated 16x, one CTA per SM.
 static int launch_finish(const FinishArgs &fa, int sms, cudaStream_t cs)
 {
     if (fa.piece_begin >= fa.piece_end) return LMZ_GPU_OK;
-    constexpr int LOGR = COND ? 2 : 4, SUBS = COND ? 1 : 4;
+    constexpr int LOGR = 4, SUBS = 4;
     static bool done[64];
-    constexpr uint32_t shm = finish_smem(COND, LOGR, SUBS);
-    int rc = opt_in_smem(k_finish<COND, LOGR, SUBS>, shm, done);
+    constexpr uint32_t shm = finish_smem(LOGR, SUBS);
+    int rc = opt_in_smem(k_finish<LOGR, SUBS>, shm, done);
     if (rc) return rc;
-    unsigned per_sm = COND ? 2 : 1;
     unsigned n = (fa.piece_end - fa.piece_begin + SUBS - 1) / SUBS;
-    unsigned grid = n < (unsigned)sms * per_sm ? n : (unsigned)sms * per_sm;
-    k_finish<COND, LOGR, SUBS><<<grid, FINISH_THREADS * SUBS, shm, cs>>>(fa);
+    unsigned grid = n < (unsigned)sms ? n : (unsigned)sms;
+    k_finish<LOGR, SUBS><<<grid, FINISH_THREADS * SUBS, shm, cs>>>(fa);
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return fail_cuda("launch k_finish", le);
+    return LMZ_GPU_OK;
+}
+
+static int launch_cond_finish(const FinishArgs &fa, int sms, cudaStream_t cs)
+{
+    if (fa.piece_begin >= fa.piece_end) return LMZ_GPU_OK;
+    static bool done[64];
+    constexpr uint32_t shm = cond_finish_smem();
+    int rc = opt_in_smem(k_cond_finish, shm, done);
+    if (rc) return rc;
+    unsigned per_sm = 227u * 1024u / (shm + 1024u);
+    unsigned n = fa.piece_end - fa.piece_begin;
+    unsigned grid = n < (unsigned)sms * per_sm ? n : (unsigned)sms * per_sm;
+    k_cond_finish<<<grid, CF_THREADS, shm, cs>>>(fa);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch k_cond_finish", le);
     return LMZ_GPU_OK;
 }
 
@@ -203,8 +216,8 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         }
         f.piece_begin = p->piece_split[part];
         f.piece_end = p->piece_split[part + 1];
-        rc = (part == 0 || part == 3) ? launch_finish<true>(f, sms, cs)
-                                      : launch_finish<false>(f, sms, cs);
+        rc = (part == 0 || part == 3) ? launch_cond_finish(f, sms, cs)
+                                      : launch_finish(f, sms, cs);
         if (rc) return rc;
     }
 

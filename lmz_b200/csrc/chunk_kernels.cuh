@@ -1,9 +1,9 @@
 // Whole-chunk kernels: everything between "planes are decoded" and "the chunk's
 // plaintext sits at its destination, checksummed".
 //
-//   k_finish      merge planes (BF16 field merge, byte-plane interleave, copy),
-//                 exponent-conditioned un-partition, XOR with a delta base,
-//                 CRC-32 of the result; output written once, 16 bytes a thread
+//   k_finish      merge planes (BF16 field merge, byte-plane interleave, copy), XOR
+//                 with a delta base, CRC-32 of the result; output written once,
+//                 16 bytes a thread (conditioned chunks: k_cond_finish)
 //   k_cond_hist   256-bin histogram of a decoded exponent plane
 //   k_cond_plan   bucket map + bucket sizes from that histogram; sizes the
 //                 sign/mantissa segment decodes
@@ -146,16 +146,12 @@ constexpr uint32_t FINISH_THREADS = 256;   // threads that finish one piece toge
 //   copy to 32/R banks; lane l uses copy l % R, so with R = 16 two lanes share two
 //   banks.  Eight tables (4 slice + 4 advance) of 1 KiB * R each, the block aligned
 //   to one table's size so an address is (index bits) | (lane's base) in one LOP3.
-//   Then, per 256-thread sub-block: 2 KiB of reduction scratch, and for the COND
-//   variant the staged exponent / sign-mantissa pieces and the bucket map.
+//   Then, per 256-thread sub-block, 2 KiB of reduction scratch.
 __host__ __device__ constexpr uint32_t finish_table_bytes(int logr) { return 8u * (1024u << logr); }
-__host__ __device__ constexpr uint32_t finish_sub_bytes(bool cond)
+__host__ __device__ constexpr uint32_t finish_sub_bytes() { return 2048; }
+__host__ __device__ constexpr uint32_t finish_smem(int logr, int subs)
 {
-    return 2048 + (cond ? 2 * PADDED_PIECE + 256 + 8 * FINISH_THREADS * 4 + 64 : 0);
-}
-__host__ __device__ constexpr uint32_t finish_smem(bool cond, int logr, int subs)
-{
-    return finish_table_bytes(logr) + (1024u << logr) /*alignment slack*/ + subs * finish_sub_bytes(cond);
+    return finish_table_bytes(logr) + (1024u << logr) /*alignment slack*/ + subs * finish_sub_bytes();
 }
 
 __device__ __forceinline__ uint32_t lds_u32(uint32_t saddr)
@@ -199,10 +195,9 @@ __device__ __forceinline__ uint32_t crc_advance(uint32_t tl, uint32_t s)
            lds_u32(crc_index<LOGR, 2>(tl, s) + 6 * TS) ^ lds_u32(crc_index<LOGR, 3>(tl, s) + 7 * TS);
 }
 
-// COND selects the variant that can un-partition exponent-conditioned chunks (it
-// stages two 32 KiB planes per sub-block).  LOGR = log2 of the CRC table
-// replication, SUBS = 256-thread sub-blocks per CTA sharing one table set.
-template <bool COND, int LOGR, int SUBS>
+// LOGR = log2 of the CRC table replication, SUBS = 256-thread sub-blocks per CTA
+// sharing one table set.  Exponent-conditioned chunks go to k_cond_finish instead.
+template <int LOGR, int SUBS>
 __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
 {
     extern __shared__ __align__(16) uint8_t fsm[];
@@ -211,11 +206,8 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
     const uint32_t lane = t & 31, warp = t >> 5;
     const uint32_t tab0 = (smem_addr(fsm) + TS - 1) & ~(TS - 1);      // shared address, TS-aligned
     uint8_t *after = fsm + (tab0 - smem_addr(fsm)) + finish_table_bytes(LOGR);
-    uint8_t *sb = after + sub * finish_sub_bytes(COND);
+    uint8_t *sb = after + sub * finish_sub_bytes();
     uint32_t *s_red = reinterpret_cast<uint32_t *>(sb);               // 512 words of scratch
-    uint8_t *s_exp = sb + 2048;
-    uint8_t *s_sm = s_exp + PADDED_PIECE;
-    uint8_t *s_lut = s_sm + PADDED_PIECE;
     const bool do_crc = a.piece_crc != nullptr;
     const uint32_t tl = tab0 + 4 * (lane & ((1u << LOGR) - 1));
     // slice tables are tables 0..3 (slice[0..3]), advance tables 4..7 (adv[0..3])
@@ -248,115 +240,13 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
             pl[k] = (c.scratch_mask >> k & 1 ? a.scratch : a.payload) + c.plane_off[k];
         if (kind == K_COPY && c.src_is_out) pl[0] = a.out + c.plane_off[0];
 
-        if (COND && kind == K_COND) {
-            // ---- stage the exponent piece and un-partition its sign/mantissa bytes
-            const CondJob &cj = a.cond_jobs[c.aux];
-            const CondState &cs = a.cond_state[c.aux];
-            const uint32_t e0 = pbase / 2, ne = plen / 2;
-            const uint8_t *exp = (cj.exp_in_scratch ? a.scratch : a.payload) + cj.exp_off + e0;
-            sub_sync();
-            s_lut[t] = cs.lut[t];
-            for (uint32_t i0 = t * 4; i0 < PIECE_ELEMS; i0 += FINISH_THREADS * 4 * 8) {
-                uint32_t w[8];
-#pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    uint32_t i = i0 + u * FINISH_THREADS * 4, v[1] = {0};
-                    if (i < ne) load_words<1>(exp + i, v);
-                    w[u] = v[0];
-                }
-#pragma unroll
-                for (int u = 0; u < 8; u++)
-                    *reinterpret_cast<uint32_t *>(s_exp + pad128(i0 + u * FINISH_THREADS * 4)) = w[u];
-            }
-            // ranks of this piece's first element within each bucket
-            if (t < 8) s_red[256 + t] = 0;
-            sub_sync();
-            {
-                const uint32_t p = q - c.piece0, b = t & 7;
-                uint32_t sum = 0;
-                for (uint32_t j = t >> 3; j < p; j += FINISH_THREADS / 8)
-                    sum += a.piece_cnt[(size_t)(c.piece0 + j) * 8 + b];
-                if (sum) atomicAdd(&s_red[256 + b], sum);
-            }
-            // phase A: per-thread bucket counts over its 128 elements, 16 bits each
-            const uint32_t my0 = t * 128;
-            uint64_t lo = 0, hi = 0;
-            for (uint32_t j = 0; j < 128; j += 4) {
-                uint32_t w = smem_word(s_exp, pad128(my0 + j));
-#pragma unroll
-                for (int z = 0; z < 4; z++) {
-                    if (my0 + j + z < ne) {
-                        uint32_t b = s_lut[(w >> (8 * z)) & 0xff];
-                        uint64_t one = 1ull << (16 * (b & 3));
-                        if (b & 4) hi += one; else lo += one;
-                    }
-                }
-            }
-            // phase B: exclusive scan of the packed counts over the 256 threads
-            uint64_t ilo = lo, ihi = hi;
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                uint64_t vl = __shfl_up_sync(0xffffffffu, ilo, d);
-                uint64_t vh = __shfl_up_sync(0xffffffffu, ihi, d);
-                if (lane >= (uint32_t)d) { ilo += vl; ihi += vh; }
-            }
-            uint64_t *s_w = reinterpret_cast<uint64_t *>(s_red);     // 8 warps x 2
-            if (lane == 31) { s_w[warp * 2] = ilo; s_w[warp * 2 + 1] = ihi; }
-            sub_sync();
-            uint64_t blo = 0, bhi = 0;
-            for (uint32_t wv = 0; wv < warp; wv++) { blo += s_w[wv * 2]; bhi += s_w[wv * 2 + 1]; }
-            const uint64_t xlo = ilo - lo + blo, xhi = ihi - hi + bhi;   // exclusive, may reach 32768
-            // phase C: walk the run, gathering each element's byte from its segment.  The
-            // running rank of each bucket lives in shared memory ([bucket][thread], one
-            // bank per lane) and the eight segment pointers in a small shared table, so an
-            // element costs a handful of instructions instead of an 8-way select chain.
-            uint32_t *s_rank = reinterpret_cast<uint32_t *>(s_lut + 256);           // 8 x 256
-            uint64_t *s_seg = reinterpret_cast<uint64_t *>(s_rank + 8 * FINISH_THREADS);
-#pragma unroll
-            for (int b = 0; b < 8; b++)
-                s_rank[b * FINISH_THREADS + t] =
-                    (uint32_t)((b & 4 ? xhi : xlo) >> (16 * (b & 3))) & 0xffffu;
-            if (t < 8)
-                s_seg[t] = reinterpret_cast<uint64_t>(
-                    (cs.seg_in_scratch >> t & 1 ? a.scratch : a.payload) + cs.seg_ptr[t] +
-                    s_red[256 + t]);
-            sub_sync();
-            // 16 elements at a time: first every address (shared-memory work only), then
-            // the 16 byte loads back to back so they are all in flight together
-            for (uint32_t j = 0; j < 128; j += 16) {
-                const uint8_t *src[16];
-#pragma unroll
-                for (int q4 = 0; q4 < 4; q4++) {
-                    const uint32_t w = smem_word(s_exp, pad128(my0 + j + 4 * q4));
-#pragma unroll
-                    for (int z = 0; z < 4; z++) {
-                        const uint32_t b = s_lut[(w >> (8 * z)) & 0xff];
-                        uint32_t *rk = s_rank + b * FINISH_THREADS + t;
-                        const uint32_t idx = *rk;
-                        const bool live = my0 + j + 4 * q4 + z < ne;
-                        if (live) *rk = idx + 1;
-                        // elements past the piece's end read the segment's first byte (unused)
-                        src[4 * q4 + z] = reinterpret_cast<const uint8_t *>(s_seg[b]) + (live ? idx : 0);
-                    }
-                }
-                uint32_t o[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int e = 0; e < 16; e++) o[e >> 2] |= (uint32_t)__ldg(src[e]) << (8 * (e & 3));
-#pragma unroll
-                for (int q4 = 0; q4 < 4; q4++)
-                    *reinterpret_cast<uint32_t *>(s_sm + pad128(my0 + j + 4 * q4)) = o[q4];
-            }
-            sub_sync();
-        }
-
         // ---- rows: every thread produces 16 output bytes per row ----------------
         uint32_t acc = 0;
         // Fast path for the overwhelmingly common piece: full, 16-byte aligned, no delta
         // base, copy or BF16 merge.  No per-row dispatch, loads on the read-only path and
         // four rows unrolled so the loads of later rows overlap the CRC chain of earlier ones.
         const bool fast = plen == PIECE_BYTES && al == 0 && base == nullptr &&
-                          (kind == K_COPY || kind == K_BF16 || (COND && kind == K_COND)) &&
-                          !(kind == K_COPY && c.src_is_out);
+                          (kind == K_COPY || kind == K_BF16) && !(kind == K_COPY && c.src_is_out);
         if (fast) {
             auto rows = [&](auto kind_c) {
                 constexpr int KIND = decltype(kind_c)::value;
@@ -366,15 +256,10 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
                     uint32_t w[4];
                     if (KIND == K_COPY) {
                         load_words_nc<4>(pl[0] + pbase + r, w);
-                    } else if (KIND == K_BF16) {
+                    } else {
                         uint32_t pa[2], pb[2];
                         load_words_nc<2>(pl[0] + (pbase + r) / 2, pa);
                         load_words_nc<2>(pl[1] + (pbase + r) / 2, pb);
-                        bf16_merge8(pa, pb, w);
-                    } else {
-                        const uint32_t i = pad128(r / 2);
-                        uint32_t pa[2] = {smem_word(s_exp, i), smem_word(s_exp, i + 4)};
-                        uint32_t pb[2] = {smem_word(s_sm, i), smem_word(s_sm, i + 4)};
                         bf16_merge8(pa, pb, w);
                     }
                     *reinterpret_cast<uint4 *>(dst + r) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -386,8 +271,7 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
                 }
             };
             if (kind == K_COPY) rows(std::integral_constant<int, K_COPY>{});
-            else if (kind == K_BF16) rows(std::integral_constant<int, K_BF16>{});
-            else rows(std::integral_constant<int, K_COND>{});
+            else rows(std::integral_constant<int, K_BF16>{});
         }
 #pragma unroll 1
         for (uint32_t row = 0; !fast && row < PIECE_BYTES / ROW_BYTES; row++) {
@@ -401,11 +285,6 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
                     uint32_t pa[2], pb[2];
                     load_words<2>(pl[0] + cr / 2, pa);
                     load_words<2>(pl[1] + cr / 2, pb);
-                    bf16_merge8(pa, pb, w);
-                } else if (COND && kind == K_COND) {
-                    uint32_t i = r / 2;
-                    uint32_t pa[2] = {smem_word(s_exp, pad128(i)), smem_word(s_exp, pad128(i + 4))};
-                    uint32_t pb[2] = {smem_word(s_sm, pad128(i)), smem_word(s_sm, pad128(i + 4))};
                     bf16_merge8(pa, pb, w);
                 } else if (esize == 4) {
                     uint32_t p0[1], p1[1], p2[1], p3[1];
