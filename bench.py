@@ -142,10 +142,29 @@ def measured_peak():
         return 6650.0, "fallback"
 
 
+_CPU = {}
+
+
+def _cpu_work(span):
+    """Decode records[lo:hi] of the sample in a worker process (reference C core)."""
+    from oracle import codec
+    ar, picks, lib = _CPU["ar"], _CPU["picks"], _CPU["lib"]
+    done = 0
+    for i in picks[span[0]:span[1]]:
+        c = ar.records[i]
+        codec.decode_chunk(ar.payload(c), int(c["codec"]), int(c["esize"]), int(c["flags"]),
+                           int(c["rlen"]), int(c["crc"]), True, lib)
+        done += int(c["rlen"])
+    return done
+
+
 def cpu_decode_sample(blob, sample_mb: int, threads: int, lib_kind: str):
-    """Time the CPU decoder over the first `sample_mb` of plaintext chunks with
-    `threads` threads.  Returns (GB/s, description)."""
-    from concurrent.futures import ThreadPoolExecutor
+    """Time the CPU decoder over the first `sample_mb` of plaintext chunks on `threads`
+    cores.  Worker processes rather than threads: the reference's Python driver is
+    GIL-bound on small chunks (it caps itself at 2 threads there, lmz/api.py:1001-1017),
+    and the baseline should show what its C core does with every core.
+    Returns (GB/s, description, kind)."""
+    import multiprocessing as mp
     from oracle import archive as oa, codec, native
     lib = native.ref() if lib_kind == "reference" else native.oracle()
     if lib is None:
@@ -159,20 +178,17 @@ def cpu_decode_sample(blob, sample_mb: int, threads: int, lib_kind: str):
         total += int(c["rlen"])
         if total >= sample_mb << 20:
             break
-
-    def work(i):
-        c = ar.records[i]
-        codec.decode_chunk(ar.payload(c), int(c["codec"]), int(c["esize"]), int(c["flags"]),
-                           int(c["rlen"]), int(c["crc"]), True, lib)
-        return int(c["rlen"])
-
-    with ThreadPoolExecutor(threads) as ex:
-        list(ex.map(work, picks[:threads]))                       # warm the pool
+    _CPU.update(ar=ar, picks=picks, lib=lib)
+    nspan = threads * 8
+    edges = np.linspace(0, len(picks), nspan + 1).astype(int)
+    spans = [(int(a), int(b)) for a, b in zip(edges[:-1], edges[1:]) if b > a]
+    with mp.get_context("fork").Pool(threads) as pool:
+        pool.map(_cpu_work, [(0, min(len(picks), threads))])       # warm the workers
         t = time.perf_counter()
-        done = sum(ex.map(work, picks, chunksize=max(1, len(picks) // (threads * 8))))
+        done = sum(pool.map(_cpu_work, spans, chunksize=1))
         dt = time.perf_counter() - t
     what = (f"first {len(picks)} chunks ({done / 1e6:.0f} MB plaintext) of the same archive, "
-            f"decode + crc32, {threads} threads, C core = {lib_kind}")
+            f"decode + crc32, {threads} worker processes, C core = {lib_kind}")
     return done / dt / 1e9, what, lib_kind
 
 
@@ -311,10 +327,7 @@ def main():
         except Exception:
             traffic = None
     if world == 1:
-        cpu_v, cpu_what, cpu_kind = cpu_decode_sample(blob, a.cpu_sample_mb, os.cpu_count() or 1,
-                                                      "reference")
-        cpu_base = {"value": round(cpu_v, 3), "unit": "GB/s", "cores": os.cpu_count() or 1,
-                    "kind": cpu_kind, "sample": cpu_what}
+        cpu_base = cpu_baseline_subprocess(a)
     else:
         cpu_base = None        # timed at N=1 only
     line = {
@@ -343,6 +356,26 @@ def main():
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def cpu_baseline_subprocess(a):
+    """The CPU baseline, timed in a fresh interpreter: its worker processes are forked,
+    which a process holding a CUDA context and page-locked mappings should not do."""
+    import subprocess
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", "1",
+           "--warmup", "0", "--model", a.model, "--layout", a.layout, "--seed", str(a.seed),
+           "--cpu-sample-mb", str(a.cpu_sample_mb)]
+    if a.chunk_size:
+        cmd += ["--chunk-size", str(a.chunk_size)]
+    if a.no_cache:
+        cmd += ["--no-cache"]
+    env = dict(os.environ)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE"):
+        env.pop(k, None)
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=1200)
+    if r.returncode != 0:
+        raise SystemExit("cpu baseline failed: " + r.stderr[-400:])
+    return json.loads(r.stdout.strip().splitlines()[-1])["cpu_baseline"]
 
 
 def pin_host(arr):
