@@ -142,6 +142,13 @@ int lmz_gpu_piece_bytes(void);
  * per device).  Returns the size in bytes; if cap is too small nothing is written. */
 int lmz_gpu_crc_tables(void *host_dst, size_t cap);
 
+/* Host helper for planners: out[i] = number of symbols with a non-zero frequency
+ * in the 516-byte table of the stream that starts at base + offs[i] (host
+ * pointers; the caller has checked that offs[i] + 516 is inside the buffer).
+ * Streams with at most 104 live symbols may be listed first in d_fused_jobs and
+ * counted in n_fused_small. */
+int lmz_host_alphabet_sizes(const void *base, const uint64_t *offs, size_t n, uint16_t *out);
+
 /* Everything lmz_gpu_decode_chunks_dev needs.  All pointers are device pointers.
  * Layouts of the job arrays are those of csrc/common.cuh and csrc/chunk_kernels.cuh;
  * lmz_b200/plan.py builds them. */
@@ -153,7 +160,8 @@ typedef struct lmz_decode_plan {
     void *d_seg_jobs;           /* 8 per conditioned chunk, sized on the device */
     void *d_stream_status;      /* uint32 per stream job */
     void *d_seg_status;         /* uint32 per segment job */
-    const void *d_fused_jobs;   /* BF16 chunks decoded, merged and checksummed by one kernel */
+    const void *d_fused_jobs;   /* BF16 chunks decoded, merged and checksummed by one kernel; the
+                                 * first n_fused_small have at most 104 live symbols */
     void *d_fused_status;       /* uint32 per fused job */
     const void *d_chunks;       /* chunk jobs, ordered: pass 1 cond, pass 1 plain, fused, pass 2 cond, pass 2 plain */
     const void *d_piece_chunk;  /* uint32 per piece: its chunk */
@@ -168,6 +176,8 @@ typedef struct lmz_decode_plan {
     void *d_chunk_crc;          /* computed crc32 per chunk, or NULL */
     void *d_any_bad;            /* uint32: bit 0 a stream failed, bit 1 a chunk failed */
     uint32_t n_stream_jobs, n_seg_jobs, n_chunks, n_pieces, n_cond, n_cond_pieces, n_fused;
+    uint32_t n_fused_small;     /* leading fused jobs whose streams have small alphabets (see
+                                 * lmz_host_alphabet_sizes); they take the denser kernel instance */
     uint32_t piece_split[6];    /* piece-id boundaries of the five chunk groups */
     uint32_t phases;            /* 0 = everything; else bit 0 stream decode, bit 1 conditioned-chunk
                                  * kernels, bit 2 finish, bit 3 verdicts, bit 4 fused BF16 chunks

@@ -14,7 +14,7 @@ class DecodePlan(ctypes.Structure):
         "d_cond_pieces", "d_hist", "d_piece_cnt", "d_piece_crc", "d_crc_tables",
         "d_chunk_status", "d_chunk_crc", "d_any_bad")] + [(n, _u32) for n in (
             "n_stream_jobs", "n_seg_jobs", "n_chunks", "n_pieces", "n_cond", "n_cond_pieces",
-            "n_fused")] + [("piece_split", _u32 * 6), ("phases", _u32)]
+            "n_fused", "n_fused_small")] + [("piece_split", _u32 * 6), ("phases", _u32)]
 
 
 def bind(lib) -> None:
@@ -23,5 +23,7 @@ def bind(lib) -> None:
     lib.lmz_gpu_piece_bytes.restype = ctypes.c_int
     lib.lmz_gpu_crc_tables.restype = ctypes.c_int
     lib.lmz_gpu_crc_tables.argtypes = [_v, ctypes.c_size_t]
+    lib.lmz_host_alphabet_sizes.restype = ctypes.c_int
+    lib.lmz_host_alphabet_sizes.argtypes = [_v, _v, ctypes.c_size_t, _v]
     lib.lmz_gpu_decode_chunks_dev.restype = ctypes.c_int
     lib.lmz_gpu_decode_chunks_dev.argtypes = [ctypes.POINTER(DecodePlan), _v]

@@ -38,6 +38,12 @@ def build(force: bool = False, verbose: bool = False) -> str | None:
     """Path of the built library, compiling it if sources are newer. None on failure
     (reason in `last_error`); never raises."""
     global last_error
+    prebuilt = os.environ.get("LMZ_B200_LIBRARY")
+    if prebuilt:                       # a library built elsewhere (deployment without nvcc)
+        if os.path.exists(prebuilt):
+            return prebuilt
+        last_error = f"LMZ_B200_LIBRARY names a missing file: {prebuilt}"
+        return None
     if not force and not _stale():
         return LIB
     nvcc = find_nvcc()

@@ -98,6 +98,19 @@ static int side_stream(SideStream **out)
     return LMZ_GPU_OK;
 }
 
+API int lmz_host_alphabet_sizes(const void *base, const uint64_t *offs, size_t n, uint16_t *out)
+{
+    if (!base || !offs || !out) return fail_msg(LMZ_GPU_EUNSUPPORTED, "null argument");
+    const uint8_t *b = (const uint8_t *)base;
+    for (size_t i = 0; i < n; i++) {
+        const uint8_t *h = b + offs[i] + 4;
+        unsigned live = 0;
+        for (unsigned s = 0; s < 256; s++) live += (h[2 * s] | h[2 * s + 1]) != 0;
+        out[i] = (uint16_t)live;
+    }
+    return LMZ_GPU_OK;
+}
+
 API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
 {
     if (!p) return fail_msg(LMZ_GPU_EUNSUPPORTED, "no plan");
@@ -142,8 +155,17 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         sa.any_bad = (uint32_t *)p->d_any_bad;
         sa.piece_crc = (uint32_t *)p->d_piece_crc;
         sa.tabs = (const CrcTables *)p->d_crc_tables;
-        rc = p->d_piece_crc ? launch_stream<SINK_BF16, true>(sa, fs)
-                            : launch_stream<SINK_BF16, false>(sa, fs);
+        // small alphabets first (denser instance), then the rest
+        const uint32_t nsmall = p->n_fused_small < p->n_fused ? p->n_fused_small : p->n_fused;
+        sa.njobs = nsmall;
+        rc = p->d_piece_crc ? launch_stream<SINK_BF16, true, 128>(sa, fs)
+                            : launch_stream<SINK_BF16, false, 128>(sa, fs);
+        if (rc) return rc;
+        sa.jobs += nsmall;
+        sa.status += nsmall;
+        sa.njobs = p->n_fused - nsmall;
+        rc = p->d_piece_crc ? launch_stream<SINK_BF16, true, 256>(sa, fs)
+                            : launch_stream<SINK_BF16, false, 256>(sa, fs);
         if (rc) return rc;
         if (side) CK("cudaEventRecord", cudaEventRecord(side->join, side->stream));
     }

@@ -99,23 +99,22 @@ __device__ __forceinline__ uint32_t smem_word(const uint8_t *base, uint32_t byte
     return *reinterpret_cast<const uint32_t *>(base + byte_index);
 }
 
-// BF16 field merge of two elements: a = exponent bytes, b = sign|mantissa bytes,
-// each holding element 0 in bits 0-7 and element 1 in bits 16-23.
-__device__ __forceinline__ uint32_t bf16_pair(uint32_t a, uint32_t b)
+// BF16 field merge of four elements at once (lmz/native/lmzcore.c:439-447): the low
+// byte of an element is b's bits 0-6 under a's bit 0, the high byte b's sign over
+// a >> 1; both are byte-wise selects on the packed words, then the bytes interleave.
+__device__ __forceinline__ void bf16_merge4(uint32_t a4, uint32_t b4, uint32_t &w0, uint32_t &w1)
 {
-    return ((b & 0x00800080u) << 8) | (a << 7) | (b & 0x007f007fu);
+    const uint32_t lo4 = (b4 & 0x7f7f7f7fu) | ((a4 << 7) & 0x80808080u);
+    const uint32_t hi4 = (b4 & 0x80808080u) | ((a4 >> 1) & 0x7f7f7f7fu);
+    w0 = __byte_perm(lo4, hi4, 0x5140);
+    w1 = __byte_perm(lo4, hi4, 0x7362);
 }
 
 __device__ __forceinline__ void bf16_merge8(const uint32_t (&a)[2], const uint32_t (&b)[2],
                                             uint32_t (&w)[4])
 {
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-        uint32_t a_lo = __byte_perm(a[h], 0, 0x4140), a_hi = __byte_perm(a[h], 0, 0x4342);
-        uint32_t b_lo = __byte_perm(b[h], 0, 0x4140), b_hi = __byte_perm(b[h], 0, 0x4342);
-        w[2 * h] = bf16_pair(a_lo, b_lo);
-        w[2 * h + 1] = bf16_pair(a_hi, b_hi);
-    }
+    for (int h = 0; h < 2; h++) bf16_merge4(a[h], b[h], w[2 * h], w[2 * h + 1]);
 }
 
 // Padded shared-memory layout for per-thread runs of 128 bytes: 4 bytes of

@@ -10,11 +10,17 @@
 //
 // Differences from k_rans that buy instructions and occupancy:
 //   * shared memory is laid out by kind (all level-1 tables, all level-2 tables,
-//     all rings ...) so each table base is 1 KiB aligned and an address is
-//     (index bits) | base in one logic op
+//     all rings ...) so each table base is aligned to its size and an address is
+//     (index bits) | base in one logic op; a warp's four level-1 tables interleave
+//     word by word, which drops the index shift and keeps the four streams' lookups
+//     in different banks
 //   * the input ring (4 x 128 B) is followed by a mirror of its first 272 bytes,
 //     filled by the same bulk copies, so a tile reads linearly with no wrap masks
-//   * 3 KiB per stream: 64 streams (16 warps) per SM beside 32 KiB of CRC tables
+//   * refill offsets come from a 4-step history of the group's votes: one
+//     byte-permute and one popcount per step instead of two popcounts
+//   * CFN = 128: level 2 has 128 slots, the four streams of a warp rotated 8
+//     entries apart so their popular symbols sit in different banks; streams with
+//     more than 104 live symbols must be given to the CFN = 256 instance
 #pragma once
 #include "chunk_kernels.cuh"
 #include "rans.cuh"
@@ -25,8 +31,13 @@ constexpr uint32_t F_SLOT = 128, F_NSLOT = 4, F_RING = F_SLOT * F_NSLOT;
 constexpr uint32_t F_MIRROR = 272;                 // a tile reads at most 256 + 2 bytes ahead
 constexpr uint32_t F_RING_BYTES = F_RING + F_MIRROR + 16;   // 800
 constexpr uint32_t F_STAGE = 144;                  // 128 + 16: groups land 4 banks apart
-constexpr uint32_t F_LOGR = 2;                     // CRC tables replicated 4x (32 KiB)
+#ifndef LMZ_CRC_LOGS
+#define LMZ_CRC_LOGS 3
+#endif
+constexpr uint32_t F_LOGS = LMZ_CRC_LOGS;          // CRC slice tables replicated 2^F_LOGS times (32 KiB at 8x)
+constexpr uint32_t F_CRC_BYTES = (4096u << F_LOGS) + 4096u;   // + the row-advance tables, once
 constexpr uint32_t F_ROW = 256, F_UNIT = 32;       // bytes of BF16 one group / one lane emits per tile
+constexpr uint32_t F_SMALL_LIVE = 104;             // largest alphabet the CFN = 128 instance takes
 enum : int { SINK_BYTES = 0, SINK_BF16 = 1 };
 
 struct FusedJob {
@@ -54,15 +65,30 @@ struct StreamArgs {
     const CrcTables *tabs;
 };
 
-__host__ __device__ constexpr uint32_t stream_group_bytes()
+__host__ __device__ constexpr uint32_t stream_group_bytes(int cfn)
 {
-    return 1024 + 1024 + F_RING_BYTES + F_STAGE + 32;     // 3024
+    return 1024 + 4 * cfn + F_RING_BYTES + F_STAGE + 32;     // 3024 / 2512
 }
-__host__ __device__ constexpr uint32_t stream_smem_bytes(int warps, bool crc)
+// Streams are carved from the bottom of the CTA's shared memory and the CRC tables
+// from the top (slice tables 8 KiB aligned, row-advance tables above them), so the
+// launch asks for everything the device lets one CTA have: 227 KiB that start
+// F_SMEM_BASE bytes into the shared window (the launcher checks that reservation).
+constexpr uint32_t F_SMEM_BASE = 1024, F_SMEM_DYN = 232448;
+__host__ __device__ constexpr uint32_t stream_crc_adv(uint32_t top) { return (top - 4096u) & ~1023u; }
+__host__ __device__ constexpr uint32_t stream_crc_slice(uint32_t top)
 {
-    return 4096 /*alignment slack*/ + (crc ? 8u * (1024u << F_LOGR) : 0u) +
-           warps * 4 * stream_group_bytes();
+    return (stream_crc_adv(top) - (4096u << F_LOGS)) & ~((1024u << F_LOGS) - 1u);
 }
+__host__ __device__ constexpr int stream_warps(int cfn, bool crc)
+{
+    constexpr uint32_t top = F_SMEM_BASE + F_SMEM_DYN;
+    int w = (int)(((crc ? stream_crc_slice(top) : top) - F_SMEM_BASE) / (4u * stream_group_bytes(cfn)));
+#ifdef LMZ_STREAM_WARPS_MAX
+    if (crc && w > LMZ_STREAM_WARPS_MAX) w = LMZ_STREAM_WARPS_MAX;
+#endif
+    return w;
+}
+static_assert(F_LOGS != 3 || (stream_warps(128, true) == 19 && stream_warps(256, true) == 16), "shared memory budget");
 
 __device__ __forceinline__ uint32_t lds_u8(uint32_t a)
 {
@@ -132,54 +158,104 @@ struct MRing {
     __device__ __forceinline__ uint32_t u32_at(uint32_t o) const { return u16_at(o) | (u16_at(o + 2) << 16); }
 };
 
-// One decode step.  `caddr` is the shared address of the cursor (linear within a
-// tile thanks to the mirror).  Returns the level-2 entry; its low byte is the symbol.
+// Table lookups and the state update of one decode step, before the refill.
+// Returns the level-2 entry (its low byte is the symbol); x2 is the new state.
+template <uint32_t CFMASK>
+__device__ __forceinline__ uint32_t stream_advance(uint32_t x, uint32_t l1_sa, uint32_t cf_sa, uint32_t &x2)
+{
+    // level 1: the warp's four tables are interleaved word by word, so bucket b of
+    // this group sits 16 * b bytes in -- the slot's bits 4-11, unshifted
+    const uint32_t e1 = lds_u32((x & 0xff0u) | l1_sa);
+    const uint32_t upto = 0xffffffffu >> ((~x) & 15u);                 // bits 0 .. 16 + (slot & 15)
+    const uint32_t pc = __popc(e1 & upto & 0xffff0000u);
+    const uint32_t e = lds_u32(((e1 & CFMASK) | cf_sa) + (pc << 2));
+    // f * (x >> 12) + slot - start  ==  x - (x >> 12) * (4096 - f) - start
+    x2 = x - ((x >> PROB_BITS) * (e >> 20) + ((e >> 8) & 0xfffu));
+    return e;
+}
+
+// One decode step, any lane mix.  `caddr` is the shared address of the cursor
+// (linear within a tile thanks to the mirror).
+template <uint32_t CFMASK>
 __device__ __forceinline__ uint32_t stream_step(uint32_t &x, uint32_t &caddr, uint32_t l1_sa,
                                                 uint32_t cf_sa, uint32_t lt_mask, uint32_t grp_mask,
                                                 bool active)
 {
-    const uint32_t slot = x & (PROB_SCALE - 1);
-    const uint32_t e1 = lds_u32(((x >> 2) & 0x3fcu) | l1_sa);
-    const uint32_t upto = 0xffffffffu >> ((~x) & 15u);                 // bits 0 .. 16 + (slot & 15)
-    const uint32_t pc = __popc(e1 & upto & 0xffff0000u);
-    const uint32_t e = lds_u32(((e1 & 0x3fcu) | cf_sa) + (pc << 2));
-    const uint32_t xs = x >> PROB_BITS;
-    const uint32_t x2 = (e >> 20) * xs + xs + slot - ((e >> 8) & 0xfffu);
+    uint32_t x2;
+    const uint32_t e = stream_advance<CFMASK>(x, l1_sa, cf_sa, x2);
     const bool need = active && x2 < RANS_LOW;
     const uint32_t vote = __ballot_sync(0xffffffffu, need);
     const uint32_t addr = caddr + 2 * __popc(vote & lt_mask);
-    const uint32_t w = lds_u8(addr) | (lds_u8_1(addr) << 8);
-    if (active) x = need ? __byte_perm(w, x2, 0x5410) : x2;
+    const uint32_t lo = lds_u8(addr), hi = lds_u8_1(addr);
+    if (need) x2 = ((x2 << 8) + hi << 8) + lo;
+    if (active) x = x2;
     caddr += 2 * __popc(vote & grp_mask);
     return e;
 }
 
-template <int SINK, bool CRC, int WARPS>
+// One step of a full tile, four to a block.  `hist` collects the group's votes of
+// the block, newest in byte 0 (vsel = 0x6540 + group picks this group's byte of
+// the warp vote and shifts the older ones up); refills consumed before this
+// lane's = bits of the older bytes plus the lanes below it in the newest, so one
+// popcount of hist & below (= 0xffffff00 | lanes below) gives the offset from
+// the block's cursor.  The caller adds 2 * popc(hist) to `cbase` after step 3.
+template <uint32_t CFMASK, bool FIRST>
+__device__ __forceinline__ uint32_t stream_step4(uint32_t &x, uint32_t &hist, uint32_t cbase,
+                                                 uint32_t l1_sa, uint32_t cf_sa, uint32_t below,
+                                                 uint32_t vsel)
+{
+    uint32_t x2;
+    const uint32_t e = stream_advance<CFMASK>(x, l1_sa, cf_sa, x2);
+    const bool need = x2 < RANS_LOW;
+    const uint32_t vote = __ballot_sync(0xffffffffu, need);
+    hist = __byte_perm(vote, FIRST ? 0u : hist, vsel);
+    const uint32_t addr = cbase + 2 * __popc(hist & below);
+    const uint32_t lo = lds_u8(addr), hi = lds_u8_1(addr);
+    if (need) x2 = ((x2 << 8) + hi << 8) + lo;       // two predicated shift-adds, no select
+    x = x2;
+    return e;
+}
+
+__device__ __forceinline__ uint32_t dynamic_smem_bytes()
+{
+    uint32_t v;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(v));
+    return v;
+}
+
+template <int SINK, bool CRC, int WARPS, int CFN>
 __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
 {
     extern __shared__ __align__(16) uint8_t ssm[];
-    constexpr uint32_t G = WARPS * 4, TS = 1024u << F_LOGR;
+    constexpr uint32_t G = WARPS * 4, CFB = 4u * CFN, CFMASK = CFB - 4u;
     constexpr uint32_t LEAD = HDR_BYTES + STATE_BYTES;
+    constexpr uint32_t MAX_LIVE = CFN == 256 ? 256u : F_SMALL_LIVE;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t k = lane & 7u, g = lane >> 3, gi = warp * 4 + g;
     const uint32_t grp_mask = 0xffu << (g * 8), lt_mask = ((1u << k) - 1u) << (g * 8);
+    const uint32_t below = 0xffffff00u | ((1u << k) - 1u), vsel = 0x6540u + g;
+    const uint32_t rot = CFN == 256 ? 0u : 8u * g;
 
     // ---- carve shared memory (addresses are 32-bit shared-space addresses) --------
-    const uint32_t base0 = (smem_addr(ssm) + 4095u) & ~4095u;
-    uint8_t *gen0 = ssm + (base0 - smem_addr(ssm));
-    const uint32_t tab0 = base0;
-    const uint32_t l1_0 = base0 + (CRC ? 8 * TS : 0);
-    const uint32_t cf_0 = l1_0 + G * 1024;
-    const uint32_t ring_0 = cf_0 + G * 1024;
-    const uint32_t stage_0 = ring_0 + G * F_RING_BYTES;
-    const uint32_t bars_0 = stage_0 + G * F_STAGE;
-    const uint32_t l1_sa = l1_0 + gi * 1024, cf_sa = cf_0 + gi * 1024;
+    // small per-stream pieces from the bottom; level-1 tables (4 KiB per warp, the
+    // four streams interleaved) end where the CRC tables begin, or at the top
+    const uint32_t s0 = smem_addr(ssm), top = s0 + dynamic_smem_bytes();
+    const uint32_t adv0 = stream_crc_adv(top), tab0 = stream_crc_slice(top);
+    const uint32_t bars_0 = (s0 + 15u) & ~15u;
+    const uint32_t stage_0 = bars_0 + G * 32;
+    const uint32_t ring_0 = stage_0 + G * F_STAGE;
+    const uint32_t cf_0 = (ring_0 + G * F_RING_BYTES + CFB - 1) & ~(CFB - 1);
+    const uint32_t l1_0 = ((CRC ? tab0 : top) & ~4095u) - WARPS * 4096u;
+    const bool fits = cf_0 + G * CFB <= l1_0;
+    auto gen = [&](uint32_t sa) { return ssm + (sa - s0); };
+    const uint32_t l1_sa = l1_0 + warp * 4096 + g * 4, cf_sa = cf_0 + gi * CFB;
     const uint32_t stage_sa = stage_0 + gi * F_STAGE;
-    const uint32_t tl = tab0 + 4 * (lane & ((1u << F_LOGR) - 1));
+    const uint32_t tls = tab0 + 4 * (lane & ((1u << F_LOGS) - 1));   // this lane's slice-table replica
+    const uint32_t tla = adv0 - 4096u;                              // crc_advance<0> adds 4 .. 7 KiB
 
     MRing ring;
     ring.sa = ring_0 + gi * F_RING_BYTES;
-    ring.bars = reinterpret_cast<uint64_t *>(gen0 + (bars_0 - base0)) + gi * F_NSLOT;
+    ring.bars = reinterpret_cast<uint64_t *>(gen(bars_0)) + gi * F_NSLOT;
 
     // ---- this group's stream ------------------------------------------------------
     const uint32_t job = (blockIdx.x * WARPS + warp) * 4 + g;
@@ -200,6 +276,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
         }
     }
     uint32_t st = ST_OK;
+    if (!fits) { st = ST_BAD_SHAPE; n = 0; }          // the launch gave less shared memory than the layout needs
     if (n != 0 && slen < LEAD) { st = ST_BAD_HEADER; n = 0; }
     if (n == 0) slen = 0;
     const uint8_t *sbase = a.src + soff;
@@ -211,13 +288,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
     if (k == 0)
         for (uint32_t j = 0; j < F_NSLOT; j++) mbar_init(&ring.bars[j], 1);
     mbar_fence_init();
-    if (CRC) {
-        // tables 0..3 = slice-by-4, 4..7 = advance by one row minus one lane unit
-        uint32_t *tw = reinterpret_cast<uint32_t *>(gen0);
-        for (uint32_t i = threadIdx.x; i < (8u * 256u) << F_LOGR; i += WARPS * 32) {
-            uint32_t e = i >> F_LOGR;
-            tw[i] = e < 1024 ? (&a.tabs->slice[0][0])[e] : (&a.tabs->adv_row[0][0])[e - 1024];
-        }
+    if (CRC && fits) {
+        // slice-by-4 tables, each word 8 times; then "advance by one row minus one lane unit"
+        uint32_t *ts = reinterpret_cast<uint32_t *>(gen(tab0)), *ta = reinterpret_cast<uint32_t *>(gen(adv0));
+        for (uint32_t i = threadIdx.x; i < 1024u << F_LOGS; i += WARPS * 32)
+            ts[i] = (&a.tabs->slice[0][0])[i >> F_LOGS];
+        for (uint32_t i = threadIdx.x; i < 1024u; i += WARPS * 32) ta[i] = (&a.tabs->adv_row[0][0])[i];
     }
     __syncthreads();
 
@@ -246,12 +322,15 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
         const uint32_t rsa = ring_0 + (warp * 4 + gg) * F_RING_BYTES;
         auto rd = [&](uint32_t o) { return lds_u8(rsa + o); };     // header sits in the first 548+15 bytes
         Tables tb{};
-        tb.l1 = reinterpret_cast<uint32_t *>(gen0 + (l1_0 - base0) + (warp * 4 + gg) * 1024);
-        tb.cf = reinterpret_cast<uint32_t *>(gen0 + (cf_0 - base0) + (warp * 4 + gg) * 1024);
-        bool ok = build_table<T_COMPACT>(
-            [&](uint32_t s) { return rd(sk + 4 + 2 * s) | (rd(sk + 5 + 2 * s) << 8); }, tb, lane);
+        tb.l1 = reinterpret_cast<uint32_t *>(gen(l1_0 + warp * 4096 + gg * 4));
+        tb.cf = reinterpret_cast<uint32_t *>(gen(cf_0 + (warp * 4 + gg) * CFB));
+        uint32_t nlive = 0;
+        bool ok = build_table<T_COMPACT, 4>(
+            [&](uint32_t s) { return rd(sk + 4 + 2 * s) | (rd(sk + 5 + 2 * s) << 8); }, tb, lane,
+            CFN == 256 ? 0u : 8u * gg, &nlive, MAX_LIVE);
         ok = ok && rd(sk) == 'R' && rd(sk + 1) == '1';
-        if (!ok && g == gg) { st = ST_BAD_HEADER; n = 0; }
+        // an alphabet too large for this instance is the caller's mistake, not the stream's
+        if (!ok && g == gg) { st = nlive > MAX_LIVE ? ST_BAD_SHAPE : ST_BAD_HEADER; n = 0; }
     }
     __syncwarp();
 
@@ -292,26 +371,34 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
         uint32_t caddr = caddr0;
         const bool full = __all_sync(0xffffffffu, rem >= TILE);
         if (full) {
-            if (SINK == SINK_BF16 && CRC && pending) acc = crc_advance<F_LOGR>(tl, acc);
+            if (SINK == SINK_BF16 && CRC && pending) acc = crc_advance<0>(tla, acc);
 #pragma unroll
-            for (uint32_t s = 0; s < TILE / NLANES; s++) {
-                uint32_t e = stream_step(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, true);
-                sts_u8(stage_sa + s * NLANES + k, e);
-                if (SINK == SINK_BF16 && CRC && (s & 1u) && pending)
-                    acc = crc_feed4<F_LOGR>(tl, acc ^ wp[s >> 1]);
+            for (uint32_t s4 = 0; s4 < TILE / NLANES; s4 += 4) {
+                uint32_t hist = 0, e;
+                e = stream_step4<CFMASK, true>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                sts_u8(stage_sa + s4 * NLANES + k, e);
+                e = stream_step4<CFMASK, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                sts_u8(stage_sa + (s4 + 1) * NLANES + k, e);
+                if (SINK == SINK_BF16 && CRC && pending) acc = crc_feed4<F_LOGS>(tls, acc ^ wp[s4 >> 1]);
+                e = stream_step4<CFMASK, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                sts_u8(stage_sa + (s4 + 2) * NLANES + k, e);
+                e = stream_step4<CFMASK, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                sts_u8(stage_sa + (s4 + 3) * NLANES + k, e);
+                if (SINK == SINK_BF16 && CRC && pending) acc = crc_feed4<F_LOGS>(tls, acc ^ wp[(s4 >> 1) + 1]);
+                caddr += 2 * __popc(hist);
             }
             pending = false;
         } else {
             if (SINK == SINK_BF16 && CRC && pending) {
-                acc = crc_advance<F_LOGR>(tl, acc);
+                acc = crc_advance<0>(tla, acc);
 #pragma unroll
-                for (int i = 0; i < 8; i++) acc = crc_feed4<F_LOGR>(tl, acc ^ wp[i]);
+                for (int i = 0; i < 8; i++) acc = crc_feed4<F_LOGS>(tls, acc ^ wp[i]);
                 pending = false;
             }
 #pragma unroll 1
             for (uint32_t s = 0; s < TILE / NLANES; s++) {
                 bool active = s * NLANES + k < rem;
-                uint32_t e = stream_step(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
+                uint32_t e = stream_step<CFMASK>(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
                 if (active) sts_u8(stage_sa + s * NLANES + k, e);
             }
         }
@@ -337,11 +424,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
         const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w};
         uint32_t w[8];
 #pragma unroll
-        for (int h = 0; h < 4; h++) {
-            const uint32_t b = __funnelshift_r(m[h], m[h + 1], msh), e4 = ew[h];
-            w[2 * h] = bf16_pair(__byte_perm(e4, 0, 0x4140), __byte_perm(b, 0, 0x4140));
-            w[2 * h + 1] = bf16_pair(__byte_perm(e4, 0, 0x4342), __byte_perm(b, 0, 0x4342));
-        }
+        for (int h = 0; h < 4; h++)
+            bf16_merge4(ew[h], __funnelshift_r(m[h], m[h + 1], msh), w[2 * h], w[2 * h + 1]);
         if (t + 1 < my_tiles) {                                // next tile's stored bytes
 #pragma unroll
             for (int i = 0; i < 5; i++) m[i] = __ldg(mq + (size_t)(t + 1) * (TILE / 4) + i);
@@ -380,9 +464,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
                 for (int i = 0; i < 8; i++) wp[i] = w[i];
                 pending = true;
             } else {
-                acc = crc_advance<F_LOGR>(tl, acc);
+                acc = crc_advance<0>(tla, acc);
 #pragma unroll
-                for (int i = 0; i < 8; i++) acc = crc_feed4<F_LOGR>(tl, acc ^ w[i]);
+                for (int i = 0; i < 8; i++) acc = crc_feed4<F_LOGS>(tls, acc ^ w[i]);
                 // close the 64 KiB piece: lane units -> row end, XOR over the group
                 uint32_t v = crc_mulmod(a.tabs->lane_mul8[k], acc);
                 v ^= __shfl_xor_sync(grp_mask, v, 1);

@@ -85,18 +85,39 @@ static int launch_rans_mode(const RansArgs &a, cudaStream_t cs)
     return LMZ_GPU_OK;
 }
 
-constexpr int WARPS_STREAM = 16;   // 64 streams per SM, one CTA
+// k_stream takes all the shared memory one CTA may have and lays its tables out from
+// both ends, counting on the window starting F_SMEM_BASE bytes in (what the
+// driver reserves per CTA on this architecture).
+static int stream_smem_ok()
+{
+    static int state[64];                       // 0 unknown, 1 good, -1 bad
+    int dev = 0;
+    CK("cudaGetDevice", cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail_msg(LMZ_GPU_EUNSUPPORTED, "device index out of range");
+    if (state[dev] == 0) {
+        int reserved = 0, optin = 0;
+        CK("cudaDeviceGetAttribute", cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev));
+        CK("cudaDeviceGetAttribute", cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        state[dev] = (reserved == (int)F_SMEM_BASE && optin >= (int)F_SMEM_DYN) ? 1 : -1;
+    }
+    if (state[dev] < 0)
+        return fail_msg(LMZ_GPU_EUNSUPPORTED, "this GPU's shared memory per CTA is not the 1 KiB + 227 KiB k_stream is laid out for");
+    return LMZ_GPU_OK;
+}
 
-template <int SINK, bool CRC>
+// CFN = 128 is for streams the caller knows to have at most F_SMALL_LIVE live symbols.
+template <int SINK, bool CRC, int CFN>
 static int launch_stream(const StreamArgs &a, cudaStream_t cs)
 {
     if (a.njobs == 0) return LMZ_GPU_OK;
+    constexpr int WARPS = stream_warps(CFN, CRC);
     static bool done[64];
-    constexpr uint32_t shm = stream_smem_bytes(WARPS_STREAM, CRC);
-    int rc = opt_in_smem(k_stream<SINK, CRC, WARPS_STREAM>, shm, done);
+    int rc = stream_smem_ok();
     if (rc) return rc;
-    unsigned blocks = (a.njobs + WARPS_STREAM * 4 - 1) / (WARPS_STREAM * 4);
-    k_stream<SINK, CRC, WARPS_STREAM><<<blocks, WARPS_STREAM * 32, shm, cs>>>(a);
+    rc = opt_in_smem(k_stream<SINK, CRC, WARPS, CFN>, F_SMEM_DYN, done);
+    if (rc) return rc;
+    unsigned blocks = (a.njobs + WARPS * 4 - 1) / (WARPS * 4);
+    k_stream<SINK, CRC, WARPS, CFN><<<blocks, WARPS * 32, F_SMEM_DYN, cs>>>(a);
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return fail_cuda("launch k_stream", le);
     return LMZ_GPU_OK;
@@ -115,7 +136,7 @@ static int launch_rans(const RansArgs &a, cudaStream_t cs)
         StreamArgs sa{};
         sa.src = a.src; sa.sjobs = a.jobs; sa.offs = a.offs; sa.plane = a.plane;
         sa.njobs = a.njobs; sa.dst = a.dst; sa.status = a.status; sa.any_bad = a.any_bad;
-        return launch_stream<SINK_BYTES, false>(sa, cs);
+        return launch_stream<SINK_BYTES, false, 256>(sa, cs);
     }
     return launch_rans_mode<T_NARROW, WARPS_NARROW>(a, cs);
 }

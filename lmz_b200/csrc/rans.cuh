@@ -24,10 +24,12 @@ namespace lmz {
 //             (bits 0-9, i.e. its byte offset in level 2) and a bit per in-bucket
 //             position t where another live symbol starts (bit 16+t); a popcount
 //             of the bits at or below the slot's position gives the live-symbol
-//             index exactly, and level 2 holds one wide-style entry per live
-//             symbol.  Two dependent loads and a popcount, at 40 % of the narrow
-//             layout's footprint, so 2.4x as many streams fit an SM.
-// Frequency is stored minus one because a single-symbol stream has f = 4096.
+//             index exactly, and level 2 holds one entry per live symbol,
+//             (4096 - freq) << 20 | start << 8 | symbol.  Two dependent loads and a
+//             popcount, at 40 % of the narrow layout's footprint or less.  Level-1
+//             words may be strided (L1S) so that several streams interleave.
+// Narrow and wide store the frequency minus one because a single-symbol stream has
+// f = 4096; compact stores 4096 - f for the same reason.
 enum : int { T_NARROW = 0, T_WIDE = 1, T_COMPACT = 2 };
 
 struct Tables {
@@ -89,8 +91,15 @@ struct Ring {
 // this; returns false (on all lanes) if the frequencies do not sum to 4096.
 // Lane j owns symbols 8j..8j+7.  Rare symbols are written by their owner,
 // common ones (f >= 64) by the whole warp so the fill stays balanced.
-template <int MODE, class FreqOf>
-__device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, uint32_t lane)
+// Compact layout only: `rot` is added to every live-symbol index, in level 1 and
+// in the position of the level-2 entry (streams that share a warp rotate their
+// level 2 apart so that their popular entries fall in different banks);
+// `nlive_out`, when not NULL, receives the number of live symbols, and a stream
+// with more than `max_live` of them is refused before anything is written.
+template <int MODE, int L1S = 1, class FreqOf>
+__device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, uint32_t lane,
+                                            uint32_t rot = 0, uint32_t *nlive_out = nullptr,
+                                            uint32_t max_live = 256)
 {
     uint32_t f[8], tot = 0, nlive = 0;
 #pragma unroll
@@ -114,10 +123,13 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, ui
     uint32_t lanes_sum = __reduce_add_sync(0xffffffffu, lane_ok ? tot : PROB_SCALE + 1);
     if (!__all_sync(0xffffffffu, lane_ok) || lanes_sum != PROB_SCALE || total != PROB_SCALE)
         return false;
-    uint32_t start = (incl - both) & 0xffffu, live = (incl - both) >> 16;
+    const uint32_t all_live = __shfl_sync(0xffffffffu, incl, 31) >> 16;
+    if (nlive_out) *nlive_out = all_live;
+    if (all_live > max_live) return false;
+    uint32_t start = (incl - both) & 0xffffu, live = ((incl - both) >> 16) + rot;
     if (MODE == T_COMPACT) {
 #pragma unroll
-        for (int i = 0; i < 8; i++) tb.l1[lane * 8 + i] = 0;
+        for (int i = 0; i < 8; i++) tb.l1[(lane * 8 + i) * L1S] = 0;
         __syncwarp();
     }
 #pragma unroll
@@ -125,11 +137,13 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, ui
         uint32_t s = lane * 8 + i, fi = f[i], st = start, li = live;
         start += fi;
         live += fi != 0;
-        uint32_t packed = ((fi ? fi - 1 : 0) << 20) | (st << 8) | s;
+        // wide: freq - 1; compact: 4096 - freq, which turns the state update into
+        // x - (x >> 12) * (4096 - f) - start with no separate slot term
+        uint32_t packed = ((MODE == T_COMPACT ? PROB_SCALE - fi : (fi ? fi - 1 : 0)) << 20) | (st << 8) | s;
         if (MODE == T_NARROW) tb.sf[s] = ((fi ? fi - 1 : 0) << 12) | st;
         if (MODE == T_COMPACT && fi) {
             tb.cf[li] = packed;
-            if (st & 15u) atomicOr(&tb.l1[st >> 4], 1u << (16 + (st & 15u)));
+            if (st & 15u) atomicOr(&tb.l1[(st >> 4) * L1S], 1u << (16 + (st & 15u)));
         }
         // work items of this symbol: slots (narrow/wide) or covered bucket heads (compact)
         uint32_t lo = MODE == T_COMPACT ? (st + 15) >> 4 : st;
@@ -140,7 +154,7 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, ui
             for (uint32_t t = 0; t < cnt; t++) {
                 if (MODE == T_WIDE) tb.wide[lo + t] = packed;
                 else if (MODE == T_NARROW) tb.sym[lo + t] = (uint8_t)s;
-                else atomicOr(&tb.l1[lo + t], li << 2);
+                else atomicOr(&tb.l1[(lo + t) * L1S], li << 2);
             }
         }
         uint32_t m = __ballot_sync(0xffffffffu, big);
@@ -154,7 +168,7 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, ui
             for (uint32_t t = lane; t < bc; t += 32) {
                 if (MODE == T_WIDE) tb.wide[bl + t] = bp;
                 else if (MODE == T_NARROW) tb.sym[bl + t] = (uint8_t)bp;
-                else atomicOr(&tb.l1[bl + t], bi << 2);
+                else atomicOr(&tb.l1[(bl + t) * L1S], bi << 2);
             }
         }
     }
@@ -176,15 +190,8 @@ __device__ __forceinline__ uint32_t rans_step(uint32_t &x, uint32_t &cursor, con
         uint32_t p = tb.sf[sym];
         x2 = ((p >> 12) + 1) * (x >> PROB_BITS) + slot - (p & 0xfffu);
     } else {
-        uint32_t e;
-        if (MODE == T_WIDE) {
-            e = tb.wide[slot];
-        } else {
-            uint32_t e1 = tb.l1[slot >> 4];
-            uint32_t upto = 0xffffffffu >> (15u - (slot & 15u));       // bits 0 .. 16+t
-            uint32_t j4 = (e1 & 0x3fcu) + 4u * __popc(e1 & upto & 0xffff0000u);
-            e = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(tb.cf) + j4);
-        }
+        static_assert(MODE != T_COMPACT, "compact tables are decoded by k_stream");
+        uint32_t e = tb.wide[slot];
         sym = e & 0xffu;
         x2 = ((e >> 20) + 1) * (x >> PROB_BITS) + slot - ((e >> 8) & 0xfffu);
     }

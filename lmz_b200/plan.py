@@ -64,6 +64,7 @@ class Plan:
     cond_jobs: np.ndarray
     cond_pieces: np.ndarray
     fused_jobs: np.ndarray = field(default=None)
+    n_fused_small: int = 0         # leading fused jobs with at most SMALL_LIVE live symbols
     stream_owner: np.ndarray = field(default=None)   # record index of each stream job
     coded_bytes: int = 0           # sum of clen: algorithmic bytes read
     base_bytes: int = 0            # bytes of delta bases read back
@@ -75,6 +76,26 @@ class Plan:
 
 def _gather(blob: np.ndarray, offs: np.ndarray, width: int) -> np.ndarray:
     return blob[offs[:, None] + np.arange(width, dtype=np.int64)[None, :]]
+
+
+SMALL_LIVE = 104       # largest alphabet the denser fused-kernel instance takes (csrc/fused_kernel.cuh)
+
+
+def _alphabet_sizes(blob: np.ndarray, offs: np.ndarray) -> np.ndarray:
+    """Live symbols (non-zero frequencies) of the rANS table at each stream offset."""
+    from . import gpu
+    offs = np.ascontiguousarray(offs, dtype=np.uint64)
+    out = np.zeros(offs.size, dtype=np.uint16)
+    lib = gpu._lib
+    if lib is not None and blob.flags.c_contiguous and offs.size:
+        rc = lib.lmz_host_alphabet_sizes(blob.ctypes.data, offs.ctypes.data, offs.size, out.ctypes.data)
+        if rc == 0:
+            return out
+    cols = np.arange(0, 512, 2, dtype=np.int64)[None, :]
+    for i in range(0, offs.size, 8192):                # the same count, without the library
+        o = offs[i:i + 8192, None].astype(np.int64) + 4 + cols
+        out[i:i + 8192] = ((blob[o] | blob[o + 1]) != 0).sum(1)
+    return out
 
 
 def _align16(x):
@@ -332,7 +353,11 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=No
         cond["piece0"] = piece0[pos_of[ci]]
         chunks["aux"][pos_of[ci]] = np.arange(ci.size)
     cond_pieces = np.nonzero(chunks["kind"][piece_chunk] == K_COND)[0].astype(np.uint32)
-    fpos = np.nonzero(g == 2)[0]                    # fused chunks, in launch order
+    fpos = np.nonzero(g == 2)[0]                    # fused chunks, in launch order ...
+    whole = f_len[corder[fpos]] >= 548              # table + states present (else the kernel rejects it)
+    small = np.zeros(fpos.size, dtype=bool)
+    small[whole] = _alphabet_sizes(blob, f_src[corder[fpos]][whole]) <= SMALL_LIVE
+    fpos = np.concatenate([fpos[small], fpos[~small]])      # ... small alphabets first
     fused_jobs = np.zeros(fpos.size, dtype=FUSED_JOB)
     frec = corder[fpos]
     fused_jobs["src_off"], fused_jobs["src_len"] = f_src[frec], f_len[frec]
@@ -345,6 +370,7 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=No
                 stream_jobs=stream_jobs, seg_jobs=seg_jobs, chunks=chunks,
                 piece_chunk=piece_chunk, piece_split=split, cond_jobs=cond,
                 cond_pieces=cond_pieces, stream_owner=s_owner[order], fused_jobs=fused_jobs,
+                n_fused_small=int(small.sum()),
                 coded_bytes=int(clen.sum()), base_bytes=int(rlen[is_delta].sum()))
 
 
