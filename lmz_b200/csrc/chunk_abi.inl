@@ -211,6 +211,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         rc = launch_rans(a, cs);
         if (rc) return rc;
         k_cond_count<<<p->n_cond_pieces, 256, 0, cs>>>(c);
+        k_cond_scan<<<(p->n_cond * 8 + 127) / 128, 128, 0, cs>>>(c.chunks, c.cond_jobs, c.ncond, c.piece_cnt);
         cudaError_t le = cudaGetLastError();
         if (le != cudaSuccess) return fail_cuda("launch cond kernels", le);
     }

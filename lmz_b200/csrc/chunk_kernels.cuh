@@ -133,7 +133,7 @@ struct FinishArgs {
     const CrcTables *tabs;
     const CondJob *cond_jobs;
     const CondState *cond_state;
-    const uint32_t *piece_cnt;     // 8 bucket populations per piece (K_COND chunks)
+    const uint32_t *piece_cnt;     // per piece of a K_COND chunk: 8 bucket populations, 8 running totals
 };
 
 constexpr uint32_t FINISH_THREADS = 256;   // threads that finish one piece together
@@ -153,12 +153,6 @@ __host__ __device__ constexpr uint32_t finish_smem(int logr, int subs)
     return finish_table_bytes(logr) + (1024u << logr) /*alignment slack*/ + subs * finish_sub_bytes();
 }
 
-__device__ __forceinline__ uint32_t lds_u32(uint32_t saddr)
-{
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
-    return v;
-}
 
 // Replicated-table CRC steps.  `tl` = shared address of this lane's copy of table 0;
 // table j lives j table-sizes further on.

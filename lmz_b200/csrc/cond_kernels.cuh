@@ -14,7 +14,7 @@ struct CondArgs {
     CondState *cond_state;
     uint32_t ncond;
     uint32_t *hist;                // ncond x 256, zeroed by the caller
-    uint32_t *piece_cnt;           // npieces x 8
+    uint32_t *piece_cnt;           // npieces x 16: 8 populations, then 8 running totals (k_cond_scan)
     StreamJob *seg_jobs;           // one slot per rANS-coded segment, sized by k_cond_plan
     const uint8_t *payload;
     const uint8_t *scratch;
@@ -122,18 +122,35 @@ __global__ void k_cond_plan(CondArgs a)
 }
 
 // Bucket populations of one exponent piece, for the stable un-partition's ranks.
+// Every symbol's bucket is looked up as a pair of one-hot words (8 bits per bucket,
+// buckets 0-3 and 4-7), so counting a byte is one 8-byte shared load and two adds;
+// a thread sees at most 128 elements, which an 8-bit field holds.
 __global__ void __launch_bounds__(256) k_cond_count(CondArgs a)
 {
     __shared__ uint32_t cnt[8][COND_BUCKETS];
-    __shared__ uint8_t lut[256];
+    __shared__ __align__(8) uint2 hot[256];
     const uint32_t t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const uint32_t q = a.cond_pieces[blockIdx.x];
     uint32_t ci, ne;
     const uint8_t *exp = cond_exp_piece(a, q, ci, ne);
-    lut[t] = a.cond_state[ci].lut[t];
+    {
+        const uint32_t b = a.cond_state[ci].lut[t];
+        hot[t] = make_uint2(b < 4 ? 1u << (8 * b) : 0u, b < 4 ? 0u : 1u << (8 * (b - 4)));
+    }
     __syncthreads();
-    // one 8-bit field per bucket in a 64-bit word: a thread sees at most 128 elements
-    uint64_t packed = 0;
+    const uint32_t hot_sa = smem_addr(hot);
+    uint32_t lo = 0, hi = 0;
+    auto count4 = [&](uint32_t w, uint32_t valid) {
+        const uint32_t ix[4] = {(w << 3) & 0x7f8u, (w >> 5) & 0x7f8u, (w >> 13) & 0x7f8u, (w >> 21) & 0x7f8u};
+#pragma unroll
+        for (int z = 0; z < 4; z++) {
+            if ((uint32_t)z < valid) {
+                const uint2 h = lds_u64(hot_sa + ix[z]);
+                lo += h.x;
+                hi += h.y;
+            }
+        }
+    };
     for (uint32_t i0 = t * 4; i0 < ne; i0 += 256 * 4 * 8) {
         uint32_t w[8];
 #pragma unroll
@@ -142,29 +159,36 @@ __global__ void __launch_bounds__(256) k_cond_count(CondArgs a)
             if (i < ne) load_words<1>(exp + i, v);
             w[u] = v[0];
         }
+        if (i0 + 7 * 256 * 4 + 4 <= ne) {
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-            uint32_t i = i0 + u * 256 * 4;
+            for (int u = 0; u < 8; u++) count4(w[u], 4);
+        } else {
 #pragma unroll
-            for (int z = 0; z < 4; z++)
-                if (i + z < ne) packed += 1ull << (8 * lut[(w[u] >> (8 * z)) & 0xff]);
+            for (int u = 0; u < 8; u++) {
+                uint32_t i = i0 + u * 256 * 4;
+                count4(w[u], i < ne ? min(ne - i, 4u) : 0u);
+            }
         }
     }
-    uint32_t c[COND_BUCKETS];
+    // 8-bit fields -> 16-bit fields (a warp sees at most 4096 elements), then a butterfly
+    uint32_t f[4] = {lo & 0x00ff00ffu, (lo >> 8) & 0x00ff00ffu, hi & 0x00ff00ffu, (hi >> 8) & 0x00ff00ffu};
 #pragma unroll
-    for (int j = 0; j < COND_BUCKETS; j++) c[j] = (uint32_t)(packed >> (8 * j)) & 0xffu;
+    for (int j = 0; j < 4; j++) {
 #pragma unroll
-    for (int j = 0; j < COND_BUCKETS; j++) {
-        uint32_t v = c[j];
-#pragma unroll
-        for (int d = 16; d; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-        if (lane == 0) cnt[warp][j] = v;
+        for (int d = 16; d; d >>= 1) f[j] += __shfl_xor_sync(0xffffffffu, f[j], d);
+    }
+    if (lane == 0) {
+        // f[0] = buckets 0,2  f[1] = buckets 1,3  f[2] = buckets 4,6  f[3] = buckets 5,7
+        cnt[warp][0] = f[0] & 0xffffu; cnt[warp][2] = f[0] >> 16;
+        cnt[warp][1] = f[1] & 0xffffu; cnt[warp][3] = f[1] >> 16;
+        cnt[warp][4] = f[2] & 0xffffu; cnt[warp][6] = f[2] >> 16;
+        cnt[warp][5] = f[3] & 0xffffu; cnt[warp][7] = f[3] >> 16;
     }
     __syncthreads();
     if (t < COND_BUCKETS) {
         uint32_t s = 0;
         for (int w = 0; w < 8; w++) s += cnt[w][t];
-        a.piece_cnt[(size_t)q * 8 + t] = s;
+        a.piece_cnt[(size_t)q * 16 + t] = s;
     }
 }
 

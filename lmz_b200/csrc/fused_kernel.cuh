@@ -90,29 +90,6 @@ __host__ __device__ constexpr int stream_warps(int cfn, bool crc)
 }
 static_assert(F_LOGS != 3 || (stream_warps(128, true) == 19 && stream_warps(256, true) == 16), "shared memory budget");
 
-__device__ __forceinline__ uint32_t lds_u8(uint32_t a)
-{
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds_u8_1(uint32_t a)
-{
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1+1];" : "=r"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ void sts_u8(uint32_t a, uint32_t v)
-{
-    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint4 lds_u128(uint32_t a)
-{
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-    return v;
-}
 __device__ __forceinline__ void bulk_g2s_sa(uint32_t dst_sa, const void *src, uint32_t bytes,
                                             uint32_t bar_sa)
 {

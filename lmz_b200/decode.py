@@ -97,7 +97,7 @@ class ArchiveDecoder:
             self.d_cond_state = torch.zeros(max(1, ncond * planner.COND_STATE_BYTES),
                                             dtype=torch.uint8, device=d)
             self.d_hist = torch.zeros(max(1, ncond * 256), **u32)
-            self.d_piece_cnt = torch.zeros(max(1, p.n_pieces * 8), **u32)
+            self.d_piece_cnt = torch.zeros(max(1, p.n_pieces * 16), **u32)
             self.d_piece_crc = torch.zeros(max(1, p.n_pieces), **u32)
             self.d_stream_status = torch.zeros(max(1, p.stream_jobs.size), **u32)
             self.d_seg_status = torch.zeros(max(1, p.seg_jobs.size), **u32)
