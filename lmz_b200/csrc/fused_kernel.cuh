@@ -21,6 +21,9 @@
 //   * CFN = 128: level 2 has 128 slots, the four streams of a warp rotated 8
 //     entries apart so their popular symbols sit in different banks; streams with
 //     more than 104 live symbols must be given to the CFN = 256 instance
+//   * CFN = 0: no levels, a 16 KiB slot -> entry table per stream and 13 streams per
+//     CTA: for launches so small that only the length of a symbol's dependent chain
+//     counts (one lookup instead of two and a popcount)
 #pragma once
 #include "chunk_kernels.cuh"
 #include "rans.cuh"
@@ -65,9 +68,11 @@ struct StreamArgs {
     const CrcTables *tabs;
 };
 
+constexpr uint32_t F_WIDE_BYTES = PROB_SCALE * 4;   // CFN = 0: one 16 KiB slot -> entry table per stream
+constexpr int F_WIDE_GROUPS = 13;                   // as many as fit one CTA, each table 16 KiB aligned
 __host__ __device__ constexpr uint32_t stream_group_bytes(int cfn)
 {
-    return 1024 + 4 * cfn + F_RING_BYTES + F_STAGE + 32;     // 3024 / 2512
+    return (cfn ? 1024 + 4 * cfn : F_WIDE_BYTES) + F_RING_BYTES + F_STAGE + 32;     // 3024 / 2512 / 17360
 }
 // Streams are carved from the bottom of the CTA's shared memory and the CRC tables
 // from the top (slice tables 8 KiB aligned, row-advance tables above them), so the
@@ -82,12 +87,14 @@ __host__ __device__ constexpr uint32_t stream_crc_slice(uint32_t top)
 __host__ __device__ constexpr int stream_warps(int cfn, bool crc)
 {
     constexpr uint32_t top = F_SMEM_BASE + F_SMEM_DYN;
+    if (cfn == 0) return (F_WIDE_GROUPS + 3) / 4;
     int w = (int)(((crc ? stream_crc_slice(top) : top) - F_SMEM_BASE) / (4u * stream_group_bytes(cfn)));
 #ifdef LMZ_STREAM_WARPS_MAX
     if (crc && w > LMZ_STREAM_WARPS_MAX) w = LMZ_STREAM_WARPS_MAX;
 #endif
     return w;
 }
+__host__ __device__ constexpr unsigned stream_groups(int cfn, int warps) { return cfn ? warps * 4 : F_WIDE_GROUPS; }
 static_assert(F_LOGS != 3 || (stream_warps(128, true) == 19 && stream_warps(256, true) == 16), "shared memory budget");
 
 __device__ __forceinline__ void bulk_g2s_sa(uint32_t dst_sa, const void *src, uint32_t bytes,
@@ -137,15 +144,21 @@ struct MRing {
 
 // Table lookups and the state update of one decode step, before the refill.
 // Returns the level-2 entry (its low byte is the symbol); x2 is the new state.
-template <uint32_t CFMASK>
+template <int CFN>
 __device__ __forceinline__ uint32_t stream_advance(uint32_t x, uint32_t l1_sa, uint32_t cf_sa, uint32_t &x2)
 {
-    // level 1: the warp's four tables are interleaved word by word, so bucket b of
-    // this group sits 16 * b bytes in -- the slot's bits 4-11, unshifted
-    const uint32_t e1 = lds_u32((x & 0xff0u) | l1_sa);
-    const uint32_t upto = 0xffffffffu >> ((~x) & 15u);                 // bits 0 .. 16 + (slot & 15)
-    const uint32_t pc = __popc(e1 & upto & 0xffff0000u);
-    const uint32_t e = lds_u32(((e1 & CFMASK) | cf_sa) + (pc << 2));
+    uint32_t e;
+    if (CFN == 0) {
+        // per-stream wide table at l1_sa (16 KiB aligned): one lookup
+        e = lds_u32(((x << 2) & 0x3ffcu) | l1_sa);
+    } else {
+        // level 1: the warp's four tables are interleaved word by word, so bucket b of
+        // this group sits 16 * b bytes in -- the slot's bits 4-11, unshifted
+        const uint32_t e1 = lds_u32((x & 0xff0u) | l1_sa);
+        const uint32_t upto = 0xffffffffu >> ((~x) & 15u);             // bits 0 .. 16 + (slot & 15)
+        const uint32_t pc = __popc(e1 & upto & 0xffff0000u);
+        e = lds_u32(((e1 & (4u * CFN - 4u)) | cf_sa) + (pc << 2));
+    }
     // f * (x >> 12) + slot - start  ==  x - (x >> 12) * (4096 - f) - start
     x2 = x - ((x >> PROB_BITS) * (e >> 20) + ((e >> 8) & 0xfffu));
     return e;
@@ -153,13 +166,13 @@ __device__ __forceinline__ uint32_t stream_advance(uint32_t x, uint32_t l1_sa, u
 
 // One decode step, any lane mix.  `caddr` is the shared address of the cursor
 // (linear within a tile thanks to the mirror).
-template <uint32_t CFMASK>
+template <int CFN>
 __device__ __forceinline__ uint32_t stream_step(uint32_t &x, uint32_t &caddr, uint32_t l1_sa,
                                                 uint32_t cf_sa, uint32_t lt_mask, uint32_t grp_mask,
                                                 bool active)
 {
     uint32_t x2;
-    const uint32_t e = stream_advance<CFMASK>(x, l1_sa, cf_sa, x2);
+    const uint32_t e = stream_advance<CFN>(x, l1_sa, cf_sa, x2);
     const bool need = active && x2 < RANS_LOW;
     const uint32_t vote = __ballot_sync(0xffffffffu, need);
     const uint32_t addr = caddr + 2 * __popc(vote & lt_mask);
@@ -176,13 +189,13 @@ __device__ __forceinline__ uint32_t stream_step(uint32_t &x, uint32_t &caddr, ui
 // lane's = bits of the older bytes plus the lanes below it in the newest, so one
 // popcount of hist & below (= 0xffffff00 | lanes below) gives the offset from
 // the block's cursor.  The caller adds 2 * popc(hist) to `cbase` after step 3.
-template <uint32_t CFMASK, bool FIRST>
+template <int CFN, bool FIRST>
 __device__ __forceinline__ uint32_t stream_step4(uint32_t &x, uint32_t &hist, uint32_t cbase,
                                                  uint32_t l1_sa, uint32_t cf_sa, uint32_t below,
                                                  uint32_t vsel)
 {
     uint32_t x2;
-    const uint32_t e = stream_advance<CFMASK>(x, l1_sa, cf_sa, x2);
+    const uint32_t e = stream_advance<CFN>(x, l1_sa, cf_sa, x2);
     const bool need = x2 < RANS_LOW;
     const uint32_t vote = __ballot_sync(0xffffffffu, need);
     hist = __byte_perm(vote, FIRST ? 0u : hist, vsel);
@@ -204,39 +217,48 @@ template <int SINK, bool CRC, int WARPS, int CFN>
 __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
 {
     extern __shared__ __align__(16) uint8_t ssm[];
-    constexpr uint32_t G = WARPS * 4, CFB = 4u * CFN, CFMASK = CFB - 4u;
+    constexpr bool WIDE = CFN == 0;
+    constexpr uint32_t G = stream_groups(CFN, WARPS), CFB = WIDE ? 16u : 4u * CFN;
     constexpr uint32_t LEAD = HDR_BYTES + STATE_BYTES;
-    constexpr uint32_t MAX_LIVE = CFN == 256 ? 256u : F_SMALL_LIVE;
+    constexpr uint32_t MAX_LIVE = CFN == 128 ? F_SMALL_LIVE : 256u;
+    static_assert(!WIDE || !CRC, "the wide instance has no room for CRC tables");
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t k = lane & 7u, g = lane >> 3, gi = warp * 4 + g;
     const uint32_t grp_mask = 0xffu << (g * 8), lt_mask = ((1u << k) - 1u) << (g * 8);
     const uint32_t below = 0xffffff00u | ((1u << k) - 1u), vsel = 0x6540u + g;
-    const uint32_t rot = CFN == 256 ? 0u : 8u * g;
 
     // ---- carve shared memory (addresses are 32-bit shared-space addresses) --------
     // small per-stream pieces from the bottom; level-1 tables (4 KiB per warp, the
     // four streams interleaved) end where the CRC tables begin, or at the top
     const uint32_t s0 = smem_addr(ssm), top = s0 + dynamic_smem_bytes();
     const uint32_t adv0 = stream_crc_adv(top), tab0 = stream_crc_slice(top);
+    // G groups have work; a warp's four lanes-of-eight always exist (GA >= G).  Lanes
+    // without a group get their own staging slot and barrier words (never used) and
+    // read the last group's tables and ring, so whatever they compute stays in bounds.
+    constexpr uint32_t GA = WARPS * 4;
+    const uint32_t gs = gi < G ? gi : G - 1;
     const uint32_t bars_0 = (s0 + 15u) & ~15u;
-    const uint32_t stage_0 = bars_0 + G * 32;
-    const uint32_t ring_0 = stage_0 + G * F_STAGE;
+    const uint32_t stage_0 = bars_0 + GA * 32;
+    const uint32_t ring_0 = stage_0 + GA * F_STAGE;
     const uint32_t cf_0 = (ring_0 + G * F_RING_BYTES + CFB - 1) & ~(CFB - 1);
-    const uint32_t l1_0 = ((CRC ? tab0 : top) & ~4095u) - WARPS * 4096u;
-    const bool fits = cf_0 + G * CFB <= l1_0;
+    // compact: level 1 at the top; wide: 16 KiB tables from the first 16 KiB boundary up
+    const uint32_t l1_0 = WIDE ? (cf_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1)
+                               : ((CRC ? tab0 : top) & ~4095u) - WARPS * 4096u;
+    const bool fits = WIDE ? l1_0 + G * F_WIDE_BYTES <= top : cf_0 + G * CFB <= l1_0;
     auto gen = [&](uint32_t sa) { return ssm + (sa - s0); };
-    const uint32_t l1_sa = l1_0 + warp * 4096 + g * 4, cf_sa = cf_0 + gi * CFB;
+    const uint32_t l1_sa = WIDE ? l1_0 + gs * F_WIDE_BYTES : l1_0 + warp * 4096 + g * 4;
+    const uint32_t cf_sa = cf_0 + gs * CFB;
     const uint32_t stage_sa = stage_0 + gi * F_STAGE;
     const uint32_t tls = tab0 + 4 * (lane & ((1u << F_LOGS) - 1));   // this lane's slice-table replica
     const uint32_t tla = adv0 - 4096u;                              // crc_advance<0> adds 4 .. 7 KiB
 
     MRing ring;
-    ring.sa = ring_0 + gi * F_RING_BYTES;
+    ring.sa = ring_0 + gs * F_RING_BYTES;
     ring.bars = reinterpret_cast<uint64_t *>(gen(bars_0)) + gi * F_NSLOT;
 
     // ---- this group's stream ------------------------------------------------------
-    const uint32_t job = (blockIdx.x * WARPS + warp) * 4 + g;
-    const bool have = job < a.njobs;
+    const uint32_t job = blockIdx.x * G + gi;
+    const bool have = gi < G && job < a.njobs;        // (the wide instance has spare lanes)
     uint64_t soff = 0, doff = 0, moff = 0;
     uint32_t slen = 0, n = 0, piece0 = 0;
     if (have) {
@@ -262,7 +284,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
     ring.valid_slots = n ? (skew + slen + F_SLOT - 1) / F_SLOT : 0;
     ring.issued = 0; ring.ready = 0; ring.dead = false;
 
-    if (k == 0)
+    if (k == 0 && gi < G)
         for (uint32_t j = 0; j < F_NSLOT; j++) mbar_init(&ring.bars[j], 1);
     mbar_fence_init();
     if (CRC && fits) {
@@ -299,12 +321,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
         const uint32_t rsa = ring_0 + (warp * 4 + gg) * F_RING_BYTES;
         auto rd = [&](uint32_t o) { return lds_u8(rsa + o); };     // header sits in the first 548+15 bytes
         Tables tb{};
-        tb.l1 = reinterpret_cast<uint32_t *>(gen(l1_0 + warp * 4096 + gg * 4));
-        tb.cf = reinterpret_cast<uint32_t *>(gen(cf_0 + (warp * 4 + gg) * CFB));
+        auto freq_of = [&](uint32_t s) { return rd(sk + 4 + 2 * s) | (rd(sk + 5 + 2 * s) << 8); };
         uint32_t nlive = 0;
-        bool ok = build_table<T_COMPACT, 4>(
-            [&](uint32_t s) { return rd(sk + 4 + 2 * s) | (rd(sk + 5 + 2 * s) << 8); }, tb, lane,
-            CFN == 256 ? 0u : 8u * gg, &nlive, MAX_LIVE);
+        bool ok;
+        if (WIDE) {
+            tb.wide = reinterpret_cast<uint32_t *>(gen(l1_0 + (warp * 4 + gg) * F_WIDE_BYTES));
+            ok = build_table<T_WIDE1>(freq_of, tb, lane);
+        } else {
+            tb.l1 = reinterpret_cast<uint32_t *>(gen(l1_0 + warp * 4096 + gg * 4));
+            tb.cf = reinterpret_cast<uint32_t *>(gen(cf_0 + (warp * 4 + gg) * CFB));
+            ok = build_table<T_COMPACT, 4>(freq_of, tb, lane, CFN == 128 ? 8u * gg : 0u, &nlive, MAX_LIVE);
+        }
         ok = ok && rd(sk) == 'R' && rd(sk + 1) == '1';
         // an alphabet too large for this instance is the caller's mistake, not the stream's
         if (!ok && g == gg) { st = nlive > MAX_LIVE ? ST_BAD_SHAPE : ST_BAD_HEADER; n = 0; }
@@ -346,20 +373,21 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
         __syncwarp();
         const uint32_t caddr0 = ring.sa + (cursor & (F_RING - 1));
         uint32_t caddr = caddr0;
+        // (lanes that never had a stream run along in full tiles; nothing of theirs is kept)
         const bool full = __all_sync(0xffffffffu, rem >= TILE);
         if (full) {
             if (SINK == SINK_BF16 && CRC && pending) acc = crc_advance<0>(tla, acc);
 #pragma unroll
             for (uint32_t s4 = 0; s4 < TILE / NLANES; s4 += 4) {
                 uint32_t hist = 0, e;
-                e = stream_step4<CFMASK, true>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN, true>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + s4 * NLANES + k, e);
-                e = stream_step4<CFMASK, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + (s4 + 1) * NLANES + k, e);
                 if (SINK == SINK_BF16 && CRC && pending) acc = crc_feed4<F_LOGS>(tls, acc ^ wp[s4 >> 1]);
-                e = stream_step4<CFMASK, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + (s4 + 2) * NLANES + k, e);
-                e = stream_step4<CFMASK, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + (s4 + 3) * NLANES + k, e);
                 if (SINK == SINK_BF16 && CRC && pending) acc = crc_feed4<F_LOGS>(tls, acc ^ wp[(s4 >> 1) + 1]);
                 caddr += 2 * __popc(hist);
@@ -375,7 +403,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
 #pragma unroll 1
             for (uint32_t s = 0; s < TILE / NLANES; s++) {
                 bool active = s * NLANES + k < rem;
-                uint32_t e = stream_step<CFMASK>(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
+                uint32_t e = stream_step<CFN>(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
                 if (active) sts_u8(stage_sa + s * NLANES + k, e);
             }
         }

@@ -105,7 +105,8 @@ static int stream_smem_ok()
     return LMZ_GPU_OK;
 }
 
-// CFN = 128 is for streams the caller knows to have at most F_SMALL_LIVE live symbols.
+// CFN = 128 is for streams the caller knows to have at most F_SMALL_LIVE live symbols;
+// CFN = 0 is the per-stream wide table (13 streams per SM).
 template <int SINK, bool CRC, int CFN>
 static int launch_stream(const StreamArgs &a, cudaStream_t cs)
 {
@@ -116,7 +117,8 @@ static int launch_stream(const StreamArgs &a, cudaStream_t cs)
     if (rc) return rc;
     rc = opt_in_smem(k_stream<SINK, CRC, WARPS, CFN>, F_SMEM_DYN, done);
     if (rc) return rc;
-    unsigned blocks = (a.njobs + WARPS * 4 - 1) / (WARPS * 4);
+    constexpr unsigned groups = stream_groups(CFN, WARPS);
+    unsigned blocks = (a.njobs + groups - 1) / groups;
     k_stream<SINK, CRC, WARPS, CFN><<<blocks, WARPS * 32, F_SMEM_DYN, cs>>>(a);
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return fail_cuda("launch k_stream", le);
@@ -126,18 +128,49 @@ static int launch_stream(const StreamArgs &a, cudaStream_t cs)
 // `force_mode` < 0 picks by batch size.
 static int g_force_table_mode = -1;
 
-static int launch_rans(const RansArgs &a, cudaStream_t cs)
+static int sm_count(int *out);
+
+static StreamArgs as_stream_args(const RansArgs &a)
+{
+    StreamArgs sa{};
+    sa.src = a.src; sa.sjobs = a.jobs; sa.offs = a.offs; sa.plane = a.plane;
+    sa.njobs = a.njobs; sa.dst = a.dst; sa.status = a.status; sa.any_bad = a.any_bad;
+    return sa;
+}
+
+// Launches with at most one CTA of 13 streams per SM are bound by the length of the
+// per-symbol dependent chain alone, and a wide table per stream shortens it by one
+// shared-memory round trip.  With `sorted` jobs (longest first, as the planner lists
+// them) a launch slightly over that size still takes the wide kernel for its head
+// when what is left over is short.
+static int launch_rans(const RansArgs &a, cudaStream_t cs, bool sorted = false)
 {
     if (a.njobs == 0) return LMZ_GPU_OK;
     if (a.shared_hdr) return launch_rans_mode<T_WIDE, WARPS_WIDE>(a, cs);
-    int mode = g_force_table_mode >= 0 ? g_force_table_mode
-                                       : (a.njobs >= COMPACT_MIN_JOBS ? T_COMPACT : T_NARROW);
-    if (mode == T_COMPACT) {
-        StreamArgs sa{};
-        sa.src = a.src; sa.sjobs = a.jobs; sa.offs = a.offs; sa.plane = a.plane;
-        sa.njobs = a.njobs; sa.dst = a.dst; sa.status = a.status; sa.any_bad = a.any_bad;
-        return launch_stream<SINK_BYTES, false, 256>(sa, cs);
+    int mode = g_force_table_mode;
+    if (mode < 0) {
+        int sms = 0;
+        int rc = sm_count(&sms);
+        if (rc) return rc;
+        const unsigned cap = (unsigned)sms * stream_groups(0, 4);
+        if (a.njobs <= cap) {
+            mode = T_WIDE1;
+        } else if (sorted && a.jobs && a.njobs < COMPACT_MIN_JOBS) {
+            // the caller guarantees the order; the kernel reads the lengths itself
+            RansArgs head = a, tail = a;
+            head.njobs = cap;
+            tail.jobs = a.jobs + cap;
+            tail.njobs = a.njobs - cap;
+            if (tail.status) tail.status = a.status + cap;
+            rc = launch_stream<SINK_BYTES, false, 0>(as_stream_args(head), cs);
+            if (rc) return rc;
+            return launch_rans_mode<T_NARROW, WARPS_NARROW>(tail, cs);
+        } else {
+            mode = a.njobs >= COMPACT_MIN_JOBS ? T_COMPACT : T_NARROW;
+        }
     }
+    if (mode == T_WIDE1) return launch_stream<SINK_BYTES, false, 0>(as_stream_args(a), cs);
+    if (mode == T_COMPACT) return launch_stream<SINK_BYTES, false, 256>(as_stream_args(a), cs);
     return launch_rans_mode<T_NARROW, WARPS_NARROW>(a, cs);
 }
 
@@ -265,8 +298,9 @@ done:
 
 API int lmz_gpu_set_table_mode(int mode)
 {
-    if (mode != -1 && mode != T_NARROW && mode != T_COMPACT)
-        return fail_msg(LMZ_GPU_EUNSUPPORTED, "table mode must be -1 (auto), 0 (narrow) or 2 (compact)");
+    if (mode != -1 && mode != T_NARROW && mode != T_COMPACT && mode != T_WIDE1)
+        return fail_msg(LMZ_GPU_EUNSUPPORTED,
+                        "table mode must be -1 (auto), 0 (narrow), 2 (compact) or 3 (wide per stream)");
     g_force_table_mode = mode;
     return LMZ_GPU_OK;
 }

@@ -18,7 +18,9 @@ namespace lmz {
 //   T_NARROW  per stream, 5 KiB: slot -> symbol (4096 x u8), then
 //             symbol -> (freq-1) << 12 | start (256 x u32).  Two dependent loads.
 //   T_WIDE    one per CTA, 16 KiB: slot -> (freq-1) << 20 | start << 8 | symbol.
-//             One dependent load; only affordable when the whole CTA shares a table.
+//             One dependent load; affordable when the whole CTA shares a table, or
+//             (T_WIDE1, one per stream, holding 4096 - freq) when a launch has so few
+//             streams that only the length of the per-symbol chain matters: 13 fit an SM.
 //   T_COMPACT per stream, 2 KiB: level 1 has one word per 16 slots holding four
 //             times the index of the live symbol covering the bucket's first slot
 //             (bits 0-9, i.e. its byte offset in level 2) and a bit per in-bucket
@@ -30,7 +32,7 @@ namespace lmz {
 //             words may be strided (L1S) so that several streams interleave.
 // Narrow and wide store the frequency minus one because a single-symbol stream has
 // f = 4096; compact stores 4096 - f for the same reason.
-enum : int { T_NARROW = 0, T_WIDE = 1, T_COMPACT = 2 };
+enum : int { T_NARROW = 0, T_WIDE = 1, T_COMPACT = 2, T_WIDE1 = 3 };   // T_WIDE1: a wide table per stream
 
 struct Tables {
     uint8_t *sym;        // T_NARROW
@@ -137,9 +139,9 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, ui
         uint32_t s = lane * 8 + i, fi = f[i], st = start, li = live;
         start += fi;
         live += fi != 0;
-        // wide: freq - 1; compact: 4096 - freq, which turns the state update into
+        // wide: freq - 1; compact and per-stream wide: 4096 - freq, which turns the state update into
         // x - (x >> 12) * (4096 - f) - start with no separate slot term
-        uint32_t packed = ((MODE == T_COMPACT ? PROB_SCALE - fi : (fi ? fi - 1 : 0)) << 20) | (st << 8) | s;
+        uint32_t packed = ((MODE == T_COMPACT || MODE == T_WIDE1 ? PROB_SCALE - fi : (fi ? fi - 1 : 0)) << 20) | (st << 8) | s;
         if (MODE == T_NARROW) tb.sf[s] = ((fi ? fi - 1 : 0) << 12) | st;
         if (MODE == T_COMPACT && fi) {
             tb.cf[li] = packed;
@@ -152,7 +154,7 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, ui
         bool big = cnt >= 64;
         if (!big) {
             for (uint32_t t = 0; t < cnt; t++) {
-                if (MODE == T_WIDE) tb.wide[lo + t] = packed;
+                if (MODE == T_WIDE || MODE == T_WIDE1) tb.wide[lo + t] = packed;
                 else if (MODE == T_NARROW) tb.sym[lo + t] = (uint8_t)s;
                 else atomicOr(&tb.l1[(lo + t) * L1S], li << 2);
             }
@@ -166,7 +168,7 @@ __device__ __forceinline__ bool build_table(FreqOf freq_of, const Tables &tb, ui
             uint32_t bp = __shfl_sync(0xffffffffu, packed, src);
             uint32_t bi = __shfl_sync(0xffffffffu, li, src);
             for (uint32_t t = lane; t < bc; t += 32) {
-                if (MODE == T_WIDE) tb.wide[bl + t] = bp;
+                if (MODE == T_WIDE || MODE == T_WIDE1) tb.wide[bl + t] = bp;
                 else if (MODE == T_NARROW) tb.sym[bl + t] = (uint8_t)bp;
                 else atomicOr(&tb.l1[(bl + t) * L1S], bi << 2);
             }
@@ -190,7 +192,7 @@ __device__ __forceinline__ uint32_t rans_step(uint32_t &x, uint32_t &cursor, con
         uint32_t p = tb.sf[sym];
         x2 = ((p >> 12) + 1) * (x >> PROB_BITS) + slot - (p & 0xfffu);
     } else {
-        static_assert(MODE != T_COMPACT, "compact tables are decoded by k_stream");
+        static_assert(MODE != T_COMPACT && MODE != T_WIDE1, "compact and per-stream wide tables are decoded by k_stream");
         uint32_t e = tb.wide[slot];
         sym = e & 0xffu;
         x2 = ((e >> 20) + 1) * (x >> PROB_BITS) + slot - ((e >> 8) & 0xfffu);

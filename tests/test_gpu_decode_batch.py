@@ -8,7 +8,7 @@ from helpers import DISTRIBUTIONS, SHAPES, distribution, pack_streams, shaped
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=[0, 2], ids=["narrow", "compact"])
+@pytest.fixture(autouse=True, params=[0, 2, 3], ids=["narrow", "compact", "wide1"])
 def table_mode(request, gpu):
     """Every test runs with both per-stream table layouts forced."""
     lib = gpu.library()
@@ -112,8 +112,8 @@ def test_stress_extremes_long_streams_and_wide_batches(gpu, orc, dist, table_mod
     """The corners of the decoder stress matrix: 4 MiB streams (batch 1 and 7) and a
     4096-stream batch, per-stream and shared tables.  The wide batch cycles a pool of
     256 distinct streams so the CPU encoder stays out of the way."""
-    if table_mode == 0 and dist != "exponent":
-        pytest.skip("one distribution is enough for the plain narrow kernel")
+    if table_mode in (0, 3) and dist != "exponent":
+        pytest.skip("one distribution is enough for the narrow and wide-per-stream kernels")
     big = [distribution(dist, 4 << 20, 1000 + i) for i in range(7)]
     _check(gpu, orc, big[:1])
     _check(gpu, orc, big)
