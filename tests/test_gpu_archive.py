@@ -45,6 +45,24 @@ def test_bf16_shard_layouts(shard, kw):
         assert (dec.archive.records["codec"] == 5).any(), "default chunking should condition"
 
 
+def test_wide_exponent_alphabets_take_the_large_table_instance():
+    """BF16 whose exponent byte takes ~200 values (a skewed draw, so rANS still pays):
+    the planner must list such chunks after the small-alphabet ones, and the
+    256-entry instance of the fused kernel must decode them."""
+    from lmz_b200 import archive, plan
+    rng = np.random.default_rng(11)
+    n = 600_000
+    e = np.minimum(rng.geometric(0.03, n) - 1, 199).astype(np.uint16)        # ~200 live exponents
+    b = rng.integers(0, 256, n).astype(np.uint16)
+    wide = (((b & 0x80) << 8) | (e << 7) | (b & 0x7F)).astype("<u2").view(np.uint8)
+    narrow = synth.normal_bf16(300_000, 5)
+    src = synth.safetensors_bytes([("wide", "BF16", (n,), wide), ("narrow", "BF16", (300_000,), narrow)])
+    blob = oa.write_archive([("m.safetensors", src)], mapped=True)
+    p = plan.build_plan(archive.Archive(blob))
+    assert 0 < p.n_fused_small < p.fused_jobs.size, (p.n_fused_small, p.fused_jobs.size)
+    _roundtrip(blob, src)
+
+
 def test_without_checksums(shard):
     blob = oa.write_archive([("m.safetensors", shard)], mapped=True)
     _roundtrip(blob, shard, checksum=False)

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol(lib_path):
     """Loads without a GPU and exports everything include/lmz_b200.h declares."""
     with open(os.path.join(ROOT, "include", "lmz_b200.h")) as f:
         text = re.sub(r"/\*.*?\*/", "", f.read(), flags=re.S)
-    names = set(re.findall(r"\b(lmz_gpu_\w+)\s*\(", text))
+    names = set(re.findall(r"\b(lmz_(?:gpu|host)_\w+)\s*\(", text))
     assert len(names) >= 13, names
     lib = ctypes.CDLL(lib_path)
     for n in names:
@@ -42,6 +42,27 @@ def test_library_exports_every_declared_symbol(lib_path):
     assert tuple(sizes) == (plan.STREAM_JOB.itemsize, plan.CHUNK_JOB.itemsize,
                             plan.COND_JOB.itemsize, plan.COND_STATE_BYTES, plan.FUSED_JOB.itemsize)
     assert lib.lmz_gpu_piece_bytes() == plan.PIECE
+
+
+def test_alphabet_sizes_helper_matches_the_planner_fallback(lib_path, orc):
+    """lmz_host_alphabet_sizes (host code of the library) and the planner's numpy
+    count agree on streams with 1 ... 256 live symbols."""
+    from lmz_b200 import plan
+    rng = np.random.default_rng(3)
+    streams, want = [], []
+    for live in (1, 2, 24, 104, 105, 200, 256):
+        syms = rng.choice(256, live, replace=False).astype(np.uint8)
+        data = np.concatenate([syms, syms[rng.integers(0, live, 4000)]])
+        streams.append(orc.rans_encode(data))
+        want.append(live)
+    blob = np.frombuffer(b"".join(streams), dtype=np.uint8)
+    offs = np.cumsum([0] + [len(s) for s in streams[:-1]]).astype(np.uint64)
+    assert plan._alphabet_sizes(blob, offs).tolist() == want          # numpy path (no library loaded here)
+    lib = ctypes.CDLL(lib_path)
+    lib.lmz_host_alphabet_sizes.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+    out = np.zeros(len(streams), dtype=np.uint16)
+    assert lib.lmz_host_alphabet_sizes(blob.ctypes.data, offs.ctypes.data, offs.size, out.ctypes.data) == 0
+    assert out.tolist() == want
 
 
 def test_validate_is_host_side(lib_path, orc):
