@@ -328,8 +328,9 @@ def main():
             traffic = None
     if world == 1:
         cpu_base = cpu_baseline_subprocess(a)
+        batch = batch_decode_compare(dec, p)
     else:
-        cpu_base = None        # timed at N=1 only
+        cpu_base = batch = None        # timed at N=1 only
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": round(ms / a.steps, 3),
@@ -352,10 +353,61 @@ def main():
                                       "bytes": coded + plain + p.base_bytes}},
         "phase_ms": {k: round(v, 3) for k, v in phase_ms.items()},
         "cpu_baseline": cpu_base,
+        "batch_decode": batch,
     }
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def batch_decode_compare(dec, p):
+    """`lmz_gpu_decode_batch_dev` on the archive's own exponent streams (device resident,
+    per-stream tables, 32768 symbols each): this library, and the reference's CUDA decoder
+    on the same inputs when oracle/_ref/liblmzgpu.so exists (its lmz/gpu/lmzgpu.cu compiled
+    for sm_100 by oracle/Makefile).  Symbols per second, best of 5, CUDA events."""
+    import ctypes
+    import torch
+    from lmz_b200 import gpu
+    fj = p.fused_jobs
+    sel = np.nonzero(fj["n"] == 32768)[0][:65536]
+    if sel.size < 1024:
+        return None
+    offs = np.empty(2 * sel.size, dtype=np.uint64)
+    offs[0::2], offs[1::2] = fj["src_off"][sel], fj["src_len"][sel]
+    d_off = torch.from_numpy(offs.view(np.int64)).cuda()
+    nstr, plane = int(sel.size), 32768
+    cs = torch.cuda.current_stream().cuda_stream
+
+    def run(lib):
+        fn = lib.lmz_gpu_decode_batch_dev
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_uint, ctypes.c_uint, ctypes.c_void_p,
+                                               ctypes.c_void_p, ctypes.c_uint]
+        out = torch.zeros(nstr * plane, dtype=torch.uint8, device="cuda")
+        best = None
+        for i in range(8):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = fn(None, dec.d_payload.data_ptr(), d_off.data_ptr(), nstr, plane, out.data_ptr(), cs, 0)
+            e1.record()
+            torch.cuda.synchronize()
+            if rc != 0:
+                return None, None
+            if i >= 3:
+                best = e0.elapsed_time(e1) if best is None else min(best, e0.elapsed_time(e1))
+        return nstr * plane / (best / 1e3) / 1e9, out
+
+    ours, out = run(gpu.library())
+    res = {"streams": nstr, "plane": plane, "unit": "GB/s of symbols", "value": round(ours, 1),
+           "reference_gpu": None}
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "liblmzgpu.so")
+    if os.path.exists(ref_path):
+        ref, ref_out = run(ctypes.CDLL(ref_path))
+        if ref is not None:
+            if not torch.equal(out, ref_out):
+                raise SystemExit("batch decode differs from the reference's CUDA decoder")
+            res["reference_gpu"] = round(ref, 1)
+    return res
 
 
 def cpu_baseline_subprocess(a):
