@@ -269,6 +269,57 @@ class PipelinedDecoder:
             dec.check()
 
 
+def decode_tensors(ar, names, device=None, checksum: bool = True):
+    """Decode only what the named tensors need.  `names`: (member path, tensor name)
+    keys of `Archive.tensor_index()`, or bare tensor names when they are unambiguous.
+    Uploads the payload bytes of the chunks that overlap those tensors (and of the
+    sources of any ref or delta among them), decodes them into a buffer that spans
+    just their part of the output space, verifies, and returns {key: device tensor}."""
+    import torch
+    from . import multi
+
+    ar = ar if isinstance(ar, fmt.Archive) else fmt.Archive(ar)
+    index = ar.tensor_index()
+    by_name = {}
+    for key in index:
+        by_name.setdefault(key[1], []).append(key)
+    keys = []
+    for n in names:
+        if isinstance(n, tuple):
+            if n not in index:
+                raise KeyError(n)
+            keys.append(n)
+        else:
+            hits = by_name.get(n, [])
+            if len(hits) != 1:
+                raise KeyError(f"{n!r} names {len(hits)} tensors; give (member path, name)")
+            keys.append(hits[0])
+    if not keys:
+        return {}
+    select = multi.cover(ar, [(index[k][2], index[k][3]) for k in keys])
+    r = ar.records[select]
+    out_lo = int(r["dst"].min()) & ~15                     # keep the output's 16-byte phase
+    out_hi = int((r["dst"].astype(np.int64) + r["rlen"]).max())
+    pay_lo = int(r["off"].min()) & ~15
+    pay_hi = int((r["off"].astype(np.int64) + r["clen"]).max())
+    p = planner.build_plan(ar, select=select, payload_range=(pay_lo, pay_hi), out_range=(out_lo, out_hi))
+    dec = ArchiveDecoder(ar, device=device, checksum=checksum, plan=p)
+    dec.run()
+    dec.check()
+    out = {}
+    for k in keys:
+        dt, shape, s, e = index[k]
+        raw = dec.d_out[s - out_lo:e - out_lo]
+        name = _TORCH_DTYPES.get(dt)
+        if name is not None and (s - out_lo) % 2 == 0:
+            try:
+                raw = raw.view(getattr(torch, name)).reshape(shape)
+            except RuntimeError:
+                pass
+        out[k] = raw
+    return out
+
+
 def decode_archive(ar, device=None, checksum: bool = True):
     """Decode a whole archive to a device tensor and verify it (the reference's
     `decompress` + `verify`, lmz/api.py:889, :1061, without the files)."""

@@ -29,6 +29,26 @@ def sources(ar: fmt.Archive) -> np.ndarray:
     return src
 
 
+def cover(ar: fmt.Archive, ranges) -> np.ndarray:
+    """Record indices needed to produce the bytes [lo, hi) of the output space for
+    every (lo, hi) in `ranges`: the chunks that overlap them, plus the plain chunks
+    that cover the sources of any ref or delta among those (one hop)."""
+    r = ar.records
+    order = np.argsort(r["dst"], kind="stable")
+    dst_sorted = r["dst"][order].astype(np.int64)
+
+    def overlapping(pairs):
+        got = [order[max(int(np.searchsorted(dst_sorted, lo, "right")) - 1, 0):
+                     int(np.searchsorted(dst_sorted, hi, "left"))] for lo, hi in pairs if hi > lo]
+        return np.unique(np.concatenate(got)) if got else np.zeros(0, dtype=np.int64)
+
+    mine = overlapping(ranges)
+    src = sources(ar)
+    need = mine[src[mine] >= 0]
+    extra = overlapping([(int(src[i]), int(src[i]) + int(r["rlen"][i])) for i in need])
+    return np.union1d(mine, extra).astype(np.int64)
+
+
 def shard(ar: fmt.Archive, rank: int, world: int):
     """(select, (lo, hi)): record indices rank `rank` must decode, and the byte
     range of the output space it owns.  The owned ranges of all ranks tile the

@@ -102,13 +102,17 @@ def _align16(x):
     return (x + 15) & ~15
 
 
-def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=None) -> Plan:
+def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=None,
+               out_range=None) -> Plan:
     """`fuse` routes BF16 chunks whose exponent plane is rANS and whose sign/mantissa
     plane is stored to the fused decode+merge+checksum kernel (no scratch plane).
     `select` (record indices) plans only those chunks -- one rank's share of a
     partitioned decode, sources of its refs and deltas included by the caller.
     `payload_range` = (lo, hi) uploads only those archive bytes (every selected chunk's
-    payload must lie inside); offsets in the plan are then relative to `lo`."""
+    payload must lie inside); offsets in the plan are then relative to `lo`.
+    `out_range` = (lo, hi) decodes into a buffer that holds only those bytes of the
+    output space (every selected chunk, and the sources of selected refs and deltas,
+    must lie inside); `Plan.total` is then hi - lo."""
     ar.check_coverage()
     r = ar.records if select is None else ar.records[np.asarray(select, dtype=np.int64)]
     lo, hi = (0, int(ar.table_off)) if payload_range is None else map(int, payload_range)
@@ -120,7 +124,10 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=No
     if r.size and ((off < 0).any() or (off + clen > hi - lo).any()):
         raise FormatError("a selected chunk's payload lies outside the payload range")
     rlen = r["rlen"].astype(np.int64)
-    dst = r["dst"].astype(np.int64)
+    out_lo, out_hi = (0, int(ar.total)) if out_range is None else map(int, out_range)
+    dst = r["dst"].astype(np.int64) - out_lo
+    if r.size and ((dst < 0).any() or (dst + rlen > out_hi - out_lo).any()):
+        raise FormatError("a selected chunk lies outside the output range")
     flags = r["flags"].astype(np.int64)
     esize = r["esize"].astype(np.int64)
 
@@ -134,7 +141,7 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=No
         if (clen[di] < 9).any():
             raise CorruptArchive("delta chunk is truncated")           # lmz/codec.py:1036
         h = _gather(blob, off[di], 9)
-        base[di] = np.ascontiguousarray(h[:, :8]).view("<u8")[:, 0].astype(np.int64)
+        base[di] = np.ascontiguousarray(h[:, :8]).view("<u8")[:, 0].astype(np.int64) - out_lo
         inner = h[:, 8].astype(np.int64)
         if np.isin(inner, (fmt.CODEC_REF, fmt.CODEC_DELTA)).any():
             raise CorruptArchive("delta chunk names a ref or delta for its own difference")
@@ -143,13 +150,13 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=No
     if ri.size:
         if (clen[ri] != 8).any():
             raise CorruptArchive("ref chunk payload must be 8 bytes")  # lmz/api.py:873
-        ref_src[ri] = np.ascontiguousarray(_gather(blob, off[ri], 8)).view("<u8")[:, 0].astype(np.int64)
+        ref_src[ri] = np.ascontiguousarray(_gather(blob, off[ri], 8)).view("<u8")[:, 0].astype(np.int64) - out_lo
     pass2 = is_delta | is_ref
     src = np.where(is_ref, ref_src, base)
     si = np.nonzero(pass2)[0]
     if si.size:
         s, e = src[si], src[si] + rlen[si]
-        if (s < 0).any() or (e > ar.total).any():
+        if (s < 0).any() or (e > out_hi - out_lo).any():
             raise CorruptArchive("a ref or delta source lies outside the output")
         o2 = si[np.argsort(dst[si], kind="stable")]
         d2, e2 = dst[o2], dst[o2] + rlen[o2]
@@ -366,7 +373,7 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=No
 
     payload = blob[:hi - lo]
     extra = np.concatenate(extras) if extras else np.zeros(0, dtype=np.uint8)
-    return Plan(payload=payload, extras=extra, total=ar.total, scratch_bytes=scratch_pos + 64,
+    return Plan(payload=payload, extras=extra, total=out_hi - out_lo, scratch_bytes=scratch_pos + 64,
                 stream_jobs=stream_jobs, seg_jobs=seg_jobs, chunks=chunks,
                 piece_chunk=piece_chunk, piece_split=split, cond_jobs=cond,
                 cond_pieces=cond_pieces, stream_owner=s_owner[order], fused_jobs=fused_jobs,

@@ -159,6 +159,41 @@ def test_tensor_views(shard):
         assert t.contiguous().view(torch.uint8).reshape(-1).cpu().numpy().tobytes() == shard[s:e].tobytes()
 
 
+def test_tensor_addressed_decode():
+    """decode_tensors uploads and decodes only the chunks a tensor needs - through every
+    layout, and through deltas and refs, whose sources it must bring along."""
+    import torch
+    from lmz_b200 import archive, decode, multi
+    c0 = synth.llama_shard([0, 1], 9, scale=0.25)
+    info = oa.parse_safetensors(c0)[1]
+    c1 = c0.copy()
+    names = list(info)
+    for i, name in enumerate(names):
+        s, e = info[name]["offsets"]
+        if i % 3 and e - s > 100000:
+            c1[s:e] = synth.perturbed_bf16(c0[s:e], 300 + i)
+    members = [("ck/0.safetensors", c0), ("ck/1.safetensors", c1)]
+    hdr = c0.size - max(t["offsets"][1] for t in info.values())       # safetensors header bytes
+    for kw in (dict(), dict(mapped=True), dict(chunk_size=1 << 20)):
+        blob = oa.write_archive(members, **kw)
+        ar = archive.Archive(blob)
+        pick = [("ck/1.safetensors", names[1]), ("ck/1.safetensors", names[-2]), ("ck/0.safetensors", names[3])]
+        got = decode.decode_tensors(ar, pick)
+        assert set(got) == set(pick)
+        for (member, name), t in got.items():
+            src = c0 if member.endswith("0.safetensors") else c1
+            s, e = info[name]["offsets"]
+            assert t.dtype == torch.bfloat16 and list(t.shape) == info[name]["shape"]
+            assert t.contiguous().view(torch.uint8).reshape(-1).cpu().numpy().tobytes() == \
+                src[hdr + s:hdr + e].tobytes(), (kw, member, name)
+        # a small tensor needs a small part of the archive
+        key = ("ck/1.safetensors", "model.norm.weight") if "model.norm.weight" in info else pick[0]
+        sel = multi.cover(ar, [ar.tensor_index()[key][2:4]])
+        assert sel.size < ar.records.size / 4, (sel.size, ar.records.size)
+    with pytest.raises(KeyError):
+        decode.decode_tensors(ar, [names[0]])             # in both members: ambiguous
+
+
 def test_reference_written_archives_decode_to_the_reference_plaintext():
     """The committed archives were written by the reference's own `lmz compress`;
     the recorded digest is of what its `decompress` restored."""
