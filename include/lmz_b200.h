@@ -125,6 +125,23 @@ int lmz_gpu_decode_batch_dev_noalloc(const void *d_hdr, const void *d_streams, c
                                      unsigned nstr, unsigned plane, void *d_out,
                                      void *cuda_stream, uint32_t *h_status);
 
+/* ---- batch encode -----------------------------------------------------------
+ * No counterpart in the reference's GPU library (its encoder is CPU code,
+ * lmz/native/lmzcore.c:882-937 and :958-979, :1318-1383).  Stream i is byte-identical
+ * to what that encoder writes for plane i with the plane's own histogram.
+ *
+ * d_planes: nstr planes of `plane` bytes back to back.  d_slots: nstr slots of
+ * lmz_gpu_encode_slot_bytes(plane) bytes, 512-byte aligned; stream i is written so
+ * that it ENDS at the end of slot i.  d_lengths: nstr uint32, the stream lengths
+ * (0 = that plane could not be coded).  Asynchronous on cuda_stream. */
+int lmz_gpu_encode_slot_bytes(unsigned plane);
+int lmz_gpu_encode_batch_dev(const void *d_planes, unsigned nstr, unsigned plane, void *d_slots,
+                             void *d_lengths, void *cuda_stream);
+/* Copy the streams out of their slots into one buffer: d_offsets = 2*nstr uint64
+ * (byte offset in d_out, length) - the layout lmz_gpu_decode_batch_dev reads. */
+int lmz_gpu_pack_streams_dev(const void *d_slots, unsigned plane, const void *d_offsets, unsigned nstr,
+                             void *d_out, void *cuda_stream);
+
 /* ---- whole-archive decode ---------------------------------------------------
  * The reference has no GPU counterpart for anything below: its chunk framing,
  * plane merge, exponent conditioning, delta undo and checksum run on the CPU

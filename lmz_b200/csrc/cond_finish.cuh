@@ -270,6 +270,9 @@ __global__ void __launch_bounds__(CF_THREADS, 3) k_cond_finish(FinishArgs a)
         const CondJob &cj = a.cond_jobs[c.aux];
         const CondState &cs = a.cond_state[c.aux];
         __syncthreads();                                   // the previous piece is done with shared memory
+        // A chunk whose bucket sizes contradict its stored segment lengths (k_cond_plan's
+        // verdict) is reported, not decoded: its counts would index past its segments.
+        if (cs.status != ST_OK) continue;
         if (have_lut != c.aux) {                           // bucket tables of this chunk
             const uint32_t b = cs.lut[t];
             s_hot[t] = make_uint2(b < 4 ? 1u << (8 * b) : 0u, b < 4 ? 0u : 1u << (8 * (b - 4)));

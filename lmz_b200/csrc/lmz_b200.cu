@@ -14,6 +14,7 @@
 #include "chunk_kernels.cuh"
 #include "cond_kernels.cuh"
 #include "fused_kernel.cuh"
+#include "encode_kernel.cuh"
 
 using namespace lmz;
 
@@ -302,6 +303,50 @@ API int lmz_gpu_set_table_mode(int mode)
         return fail_msg(LMZ_GPU_EUNSUPPORTED,
                         "table mode must be -1 (auto), 0 (narrow), 2 (compact) or 3 (wide per stream)");
     g_force_table_mode = mode;
+    return LMZ_GPU_OK;
+}
+
+// ---- batch encode (no counterpart in the reference's GPU library) -------------------
+
+API int lmz_gpu_encode_slot_bytes(unsigned plane) { return (int)encode_slot_bytes(plane); }
+
+API int lmz_gpu_encode_batch_dev(const void *d_planes, unsigned nstr, unsigned plane, void *d_slots,
+                                 void *d_lengths, void *cuda_stream)
+{
+    int rc = device_ready();
+    if (rc) return rc;
+    if (nstr == 0) return LMZ_GPU_OK;
+    if (!d_planes || !d_slots || !d_lengths) return fail_msg(LMZ_GPU_EUNSUPPORTED, "null argument");
+    if (plane == 0 || plane > (1u << 30)) return fail_msg(LMZ_GPU_EUNSUPPORTED, "plane must be 1 .. 2^30 bytes");
+    if ((uintptr_t)d_slots & 511u) return fail_msg(LMZ_GPU_EUNSUPPORTED, "the slot buffer must be 512-byte aligned");
+    constexpr int WARPS = 8;
+    static bool done[64];
+    constexpr uint32_t shm = encode_smem_bytes(WARPS);
+    rc = opt_in_smem(k_encode<WARPS>, shm, done);
+    if (rc) return rc;
+    EncodeArgs a{};
+    a.src = (const uint8_t *)d_planes;
+    a.plane = plane;
+    a.nstr = nstr;
+    a.slots = (uint8_t *)d_slots;
+    a.slot_bytes = encode_slot_bytes(plane);
+    a.lengths = (uint32_t *)d_lengths;
+    k_encode<WARPS><<<(nstr + WARPS * 4 - 1) / (WARPS * 4), WARPS * 32, shm, (cudaStream_t)cuda_stream>>>(a);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch k_encode", le);
+    return LMZ_GPU_OK;
+}
+
+API int lmz_gpu_pack_streams_dev(const void *d_slots, unsigned plane, const void *d_offsets, unsigned nstr,
+                                 void *d_out, void *cuda_stream)
+{
+    int rc = device_ready();
+    if (rc) return rc;
+    if (nstr == 0) return LMZ_GPU_OK;
+    k_pack_streams<<<nstr, 128, 0, (cudaStream_t)cuda_stream>>>((const uint8_t *)d_slots, encode_slot_bytes(plane),
+                                                              (const uint64_t *)d_offsets, nstr, (uint8_t *)d_out);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch k_pack_streams", le);
     return LMZ_GPU_OK;
 }
 

@@ -97,6 +97,12 @@ def _bind(lib) -> None:
     lib.lmz_gpu_set_table_mode.argtypes = [c_int]
     lib.lmz_gpu_decode_streams_dev.restype = c_int
     lib.lmz_gpu_decode_streams_dev.argtypes = [v, c_uint, v, v, v, v, v, v]
+    lib.lmz_gpu_encode_slot_bytes.restype = c_int
+    lib.lmz_gpu_encode_slot_bytes.argtypes = [c_uint]
+    lib.lmz_gpu_encode_batch_dev.restype = c_int
+    lib.lmz_gpu_encode_batch_dev.argtypes = [v, c_uint, c_uint, v, v, v]
+    lib.lmz_gpu_pack_streams_dev.restype = c_int
+    lib.lmz_gpu_pack_streams_dev.argtypes = [v, c_uint, v, c_uint, v, v]
     from . import _chunks
     _chunks.bind(lib)
 
@@ -284,6 +290,56 @@ def decode_batch(streams, offsets, nstr: int, plane: int, out=None, header=None)
     if rc == EBADSTREAM:
         raise ValueError("malformed rANS stream")
     return None
+
+
+def encode_batch(planes, nstr: int, plane: int):
+    """The inverse of `decode_batch` (the reference has no GPU encoder; its CPU one is
+    lmz/kernels.py rans_encode over lmz/native/lmzcore.c:1318-1383): code `nstr` planes
+    of `plane` bytes, each with its own histogram.  Returns (streams, offsets) in the
+    layout `decode_batch` takes - the streams back to back and 2*nstr little-endian
+    uint64 (byte offset, byte length) - and every stream is byte-identical to what the
+    reference's encoder writes for that plane.  Host bytes in, bytes out; a CUDA uint8
+    tensor in, CUDA tensors out (uint8 streams with pad_bytes() of zeroed slack after
+    them, int64 offsets).  None if there is no usable GPU library."""
+    lib = _load()
+    if lib is None:
+        return None
+    if nstr < 0 or plane < 1:
+        raise ValueError("nstr must not be negative and plane must be at least 1")
+    import torch
+
+    on_device = _is_cuda_tensor(planes)
+    if not on_device and len(planes) < nstr * plane:
+        raise ValueError(f"planes holds {len(planes)} bytes, need {nstr * plane}")
+    if nstr == 0:
+        return (torch.empty(0, dtype=torch.uint8, device=planes.device),
+                torch.empty(0, dtype=torch.int64, device=planes.device)) if on_device else (b"", b"")
+    dev = planes.device if on_device else torch.device(f"cuda:{torch.cuda.current_device()}")
+    with torch.cuda.device(dev):
+        src = planes.reshape(-1) if on_device else \
+            torch.frombuffer(bytearray(planes[:nstr * plane]), dtype=torch.uint8).to(dev)
+        if src.numel() < nstr * plane:
+            raise ValueError("planes is too short")
+        slot = lib.lmz_gpu_encode_slot_bytes(plane)
+        slots = torch.empty(nstr * slot, dtype=torch.uint8, device=dev)       # the allocator aligns to 512
+        lens = torch.zeros(nstr, dtype=torch.int32, device=dev)
+        cs = torch.cuda.current_stream(dev).cuda_stream
+        rc = lib.lmz_gpu_encode_batch_dev(src.data_ptr(), nstr, plane, slots.data_ptr(), lens.data_ptr(), cs)
+        if rc != OK:
+            return None
+        lens64 = lens.to(torch.int64)
+        if bool((lens64 == 0).any()):
+            raise ValueError("a plane could not be coded")
+        offs = torch.stack((torch.cumsum(lens64, 0) - lens64, lens64), dim=1).reshape(-1).contiguous()
+        total = int(lens64.sum())
+        out = torch.zeros(total + pad_bytes(), dtype=torch.uint8, device=dev)
+        rc = lib.lmz_gpu_pack_streams_dev(slots.data_ptr(), plane, offs.data_ptr(), nstr, out.data_ptr(), cs)
+        if rc != OK:
+            return None
+        torch.cuda.current_stream(dev).synchronize()
+        if on_device:
+            return out[:total], offs
+        return out[:total].cpu().numpy().tobytes(), offs.cpu().numpy().astype("<u8").tobytes()
 
 
 def _decode_batch_cuda(lib, streams, offsets, nstr, plane, out, header):

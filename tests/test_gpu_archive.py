@@ -143,6 +143,36 @@ def test_corruption_is_reported(shard):
         decode.ArchiveDecoder(bytes(blob[:-1]))
 
 
+def test_corrupt_conditioned_chunks_are_reported(shard):
+    """Default chunking: damage to the exponent stream of a conditioned chunk changes its
+    histogram, so its bucket sizes no longer match the stored segments - the chunk is
+    reported and its segments are not indexed with the wrong counts."""
+    import struct
+    from lmz_b200 import decode
+    from lmz_b200.archive import CorruptArchive
+    blob = oa.write_archive([("m.safetensors", shard)])
+    ar = oa.Archive(bytes(blob))
+    i = int(np.nonzero(ar.records["codec"] == 5)[0][0])
+    rec = ar.records[i]
+    for where in (46 + 548 + 4000, 46 + 548 + 9):                   # inside the exponent stream
+        hit = bytearray(blob)
+        hit[int(rec["off"]) + where] ^= 0x81
+        dec = decode.ArchiveDecoder(bytes(hit))
+        dec.run()
+        with pytest.raises(CorruptArchive):
+            dec.check()
+    # a segment length that disagrees with the bucket population (header field, lmz/codec.py:50)
+    hit = bytearray(blob)
+    pos = int(rec["off"]) + 1 + 1 + 8 + 4                            # k, exp_m, sm_m[8], exp_len -> seg_len[0]
+    n0 = struct.unpack_from("<I", hit, pos)[0]
+    struct.pack_into("<I", hit, pos, n0 - 16)
+    struct.pack_into("<I", hit, pos + 4, struct.unpack_from("<I", hit, pos + 4)[0] + 16)
+    dec = decode.ArchiveDecoder(bytes(hit))
+    dec.run()
+    with pytest.raises(CorruptArchive):
+        dec.check()
+
+
 def test_tensor_views(shard):
     import torch
     from lmz_b200 import decode
