@@ -61,7 +61,32 @@ __global__ void __launch_bounds__(WARPS * 32) k_encode(EncodeArgs a)
     // ---- 1. histogram ------------------------------------------------------------------
     for (uint32_t i = k; i < 256; i += 8) tab[i] = 0;
     __syncwarp();
-    for (uint32_t i = k; i < n; i += 8) atomicAdd(&tab[src[i]], 1u);
+    {
+        // bytes up to the first 16-byte boundary, whole 16-byte units (two per lane in
+        // flight), then the tail
+        const uint32_t head = min(n, (uint32_t)((16u - (reinterpret_cast<uintptr_t>(src) & 15u)) & 15u));
+        const uint32_t units = (n - head) / 16;
+        for (uint32_t i = k; i < head; i += 8) atomicAdd(&tab[src[i]], 1u);
+        const uint4 *u4 = reinterpret_cast<const uint4 *>(src + head);
+        auto count16 = [&](const uint4 &v) {
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                atomicAdd(&tab[w[j] & 0xffu], 1u);
+                atomicAdd(&tab[(w[j] >> 8) & 0xffu], 1u);
+                atomicAdd(&tab[(w[j] >> 16) & 0xffu], 1u);
+                atomicAdd(&tab[w[j] >> 24], 1u);
+            }
+        };
+        uint32_t u = k;
+        for (; u + 8 < units; u += 16) {
+            const uint4 v0 = __ldg(u4 + u), v1 = __ldg(u4 + u + 8);
+            count16(v0);
+            count16(v1);
+        }
+        for (; u < units; u += 8) count16(__ldg(u4 + u));
+        for (uint32_t i = head + units * 16 + k; i < n; i += 8) atomicAdd(&tab[src[i]], 1u);
+    }
     __syncwarp();
 
     // ---- 2. frequencies, one stream at a time by the whole warp ---------------------------
@@ -159,10 +184,15 @@ __global__ void __launch_bounds__(WARPS * 32) k_encode(EncodeArgs a)
         // this tile's 128 symbols into shared memory (lane k: bytes 16 k .. 16 k + 15)
         __syncwarp();
         if (mine_tile) {
+            const uint8_t *tp = src + tt * 128 + 16 * k;
+            if ((reinterpret_cast<uintptr_t>(tp) & 15u) == 0 && tt * 128 + 16 * k + 16 <= n) {
+                *reinterpret_cast<uint4 *>(tile + 16 * k) = __ldg(reinterpret_cast<const uint4 *>(tp));
+            } else {
 #pragma unroll
-            for (uint32_t j = 0; j < 16; j++) {
-                const uint32_t i = tt * 128 + 16 * k + j;
-                tile[16 * k + j] = i < n ? src[i] : 0;
+                for (uint32_t j = 0; j < 16; j++) {
+                    const uint32_t i = tt * 128 + 16 * k + j;
+                    tile[16 * k + j] = i < n ? src[i] : 0;
+                }
             }
         }
         __syncwarp();
