@@ -364,7 +364,8 @@ def batch_decode_compare(dec, p):
     """`lmz_gpu_decode_batch_dev` on the archive's own exponent streams (device resident,
     per-stream tables, 32768 symbols each): this library, and the reference's CUDA decoder
     on the same inputs when oracle/_ref/liblmzgpu.so exists (its lmz/gpu/lmzgpu.cu compiled
-    for sm_100 by oracle/Makefile).  Symbols per second, best of 5, CUDA events."""
+    for sm_100 by oracle/Makefile).  Symbols per second, best of 5, CUDA events.  `encode` is
+    `lmz_gpu_encode_batch_dev` on the decoded planes, checked against the archive's streams."""
     import ctypes
     import torch
     from lmz_b200 import gpu
@@ -399,7 +400,32 @@ def batch_decode_compare(dec, p):
 
     ours, out = run(gpu.library())
     res = {"streams": nstr, "plane": plane, "unit": "GB/s of symbols", "value": round(ours, 1),
-           "reference_gpu": None}
+           "reference_gpu": None, "encode": None}
+    # and back: the GPU encoder must reproduce the archive's streams (written by the
+    # reference-exact CPU encoder) from the decoded planes, length for length, byte for byte
+    lib = gpu.library()
+    slot = lib.lmz_gpu_encode_slot_bytes(plane)
+    slots = torch.empty(nstr * slot, dtype=torch.uint8, device="cuda")
+    lens = torch.zeros(nstr, dtype=torch.int32, device="cuda")
+    best = None
+    for i in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = lib.lmz_gpu_encode_batch_dev(out.data_ptr(), nstr, plane, slots.data_ptr(), lens.data_ptr(), cs)
+        e1.record()
+        torch.cuda.synchronize()
+        if rc != 0:
+            raise SystemExit("batch encode failed: " + gpu.last_error())
+        if i >= 2:
+            best = e0.elapsed_time(e1) if best is None else min(best, e0.elapsed_time(e1))
+    if not np.array_equal(lens.cpu().numpy().astype(np.int64), fj["src_len"][sel].astype(np.int64)):
+        raise SystemExit("re-encoded stream lengths differ from the archive's")
+    for i in np.linspace(0, nstr - 1, 64).astype(np.int64):
+        n, o = int(fj["src_len"][sel[i]]), int(fj["src_off"][sel[i]])
+        if not torch.equal(slots[(i + 1) * slot - n:(i + 1) * slot], dec.d_payload[o:o + n]):
+            raise SystemExit(f"re-encoded stream {i} differs from the archive's bytes")
+    res["encode"] = round(nstr * plane / (best / 1e3) / 1e9, 1)
+    del slots
     ref_path = os.path.join(ROOT, "oracle", "_ref", "liblmzgpu.so")
     if os.path.exists(ref_path):
         ref, ref_out = run(ctypes.CDLL(ref_path))
