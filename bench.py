@@ -32,7 +32,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 MODELS = {
-    # BASELINE configuration 3: 32 layers, hidden 4096, FFN 14336, 8 KV heads of 128, vocab 128256
+    # the headline configuration: 32 layers, hidden 4096, FFN 14336, 8 KV heads of 128, vocab 128256
     "llama-3.1-8b": dict(layers=32, hidden=4096, ffn=14336, kv=1024, vocab=128256, shards=4),
     "llama-8layer": dict(layers=8, hidden=4096, ffn=14336, kv=1024, vocab=1024, shards=1),
     "llama-2layer": dict(layers=2, hidden=4096, ffn=14336, kv=1024, vocab=1024, shards=1),
