@@ -24,6 +24,8 @@
 //   * CFN = 0: no levels, a 16 KiB slot -> entry table per stream and 13 streams per
 //     CTA: for launches so small that only the length of a symbol's dependent chain
 //     counts (one lookup instead of two and a popcount)
+//   * CFN = -1: the same wide table once per CTA, for batches whose streams share one
+//     516-byte table (lmz_gpu_decode_batch's d_hdr); a stream is then states + words
 #pragma once
 #include "chunk_kernels.cuh"
 #include "rans.cuh"
@@ -66,14 +68,16 @@ struct StreamArgs {
     uint32_t *any_bad;
     uint32_t *piece_crc;        // SINK_BF16 with checksums: R() per 64 KiB piece
     const CrcTables *tabs;
+    const uint8_t *shared_hdr;  // CFN = -1: the 516-byte table every stream of the launch shares
 };
 
 constexpr uint32_t F_WIDE_BYTES = PROB_SCALE * 4;   // CFN = 0: one 16 KiB slot -> entry table per stream
 constexpr int F_WIDE_GROUPS = 13;                   // as many as fit one CTA, each table 16 KiB aligned
 __host__ __device__ constexpr uint32_t stream_group_bytes(int cfn)
 {
-    return (cfn ? 1024 + 4 * cfn : F_WIDE_BYTES) + F_RING_BYTES + F_STAGE + 32;     // 3024 / 2512 / 17360
+    return (cfn > 0 ? 1024 + 4 * cfn : cfn == 0 ? F_WIDE_BYTES : 0) + F_RING_BYTES + F_STAGE + 32;   // 3024 / 2512 / 17360 / 976
 }
+constexpr int F_SHARED_WARPS = 16;                  // CFN = -1: one table per CTA, two CTAs per SM (64 registers a thread)
 // Streams are carved from the bottom of the CTA's shared memory and the CRC tables
 // from the top (slice tables 8 KiB aligned, row-advance tables above them), so the
 // launch asks for everything the device lets one CTA have: 227 KiB that start
@@ -88,6 +92,7 @@ __host__ __device__ constexpr int stream_warps(int cfn, bool crc)
 {
     constexpr uint32_t top = F_SMEM_BASE + F_SMEM_DYN;
     if (cfn == 0) return (F_WIDE_GROUPS + 3) / 4;
+    if (cfn < 0) return F_SHARED_WARPS;
     int w = (int)(((crc ? stream_crc_slice(top) : top) - F_SMEM_BASE) / (4u * stream_group_bytes(cfn)));
 #ifdef LMZ_STREAM_WARPS_MAX
     if (crc && w > LMZ_STREAM_WARPS_MAX) w = LMZ_STREAM_WARPS_MAX;
@@ -148,8 +153,8 @@ template <int CFN>
 __device__ __forceinline__ uint32_t stream_advance(uint32_t x, uint32_t l1_sa, uint32_t cf_sa, uint32_t &x2)
 {
     uint32_t e;
-    if (CFN == 0) {
-        // per-stream wide table at l1_sa (16 KiB aligned): one lookup
+    if (CFN <= 0) {
+        // wide table at l1_sa (16 KiB aligned; the stream's own, or the CTA's shared one): one lookup
         e = lds_u32(((x << 2) & 0x3ffcu) | l1_sa);
     } else {
         // level 1: the warp's four tables are interleaved word by word, so bucket b of
@@ -214,12 +219,12 @@ __device__ __forceinline__ uint32_t dynamic_smem_bytes()
 }
 
 template <int SINK, bool CRC, int WARPS, int CFN>
-__global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
+__global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamArgs a)
 {
     extern __shared__ __align__(16) uint8_t ssm[];
-    constexpr bool WIDE = CFN == 0;
+    constexpr bool WIDE = CFN <= 0, SHARED = CFN < 0;
     constexpr uint32_t G = stream_groups(CFN, WARPS), CFB = WIDE ? 16u : 4u * CFN;
-    constexpr uint32_t LEAD = HDR_BYTES + STATE_BYTES;
+    constexpr uint32_t LEAD = (SHARED ? 0u : HDR_BYTES) + STATE_BYTES;
     constexpr uint32_t MAX_LIVE = CFN == 128 ? F_SMALL_LIVE : 256u;
     static_assert(!WIDE || !CRC, "the wide instance has no room for CRC tables");
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -244,9 +249,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
     // compact: level 1 at the top; wide: 16 KiB tables from the first 16 KiB boundary up
     const uint32_t l1_0 = WIDE ? (cf_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1)
                                : ((CRC ? tab0 : top) & ~4095u) - WARPS * 4096u;
-    const bool fits = WIDE ? l1_0 + G * F_WIDE_BYTES <= top : cf_0 + G * CFB <= l1_0;
+    const bool fits = WIDE ? l1_0 + (SHARED ? 1u : G) * F_WIDE_BYTES <= top : cf_0 + G * CFB <= l1_0;
     auto gen = [&](uint32_t sa) { return ssm + (sa - s0); };
-    const uint32_t l1_sa = WIDE ? l1_0 + gs * F_WIDE_BYTES : l1_0 + warp * 4096 + g * 4;
+    const uint32_t l1_sa = SHARED ? l1_0 : WIDE ? l1_0 + gs * F_WIDE_BYTES : l1_0 + warp * 4096 + g * 4;
     const uint32_t cf_sa = cf_0 + gs * CFB;
     const uint32_t stage_sa = stage_0 + gi * F_STAGE;
     const uint32_t tls = tab0 + 4 * (lane & ((1u << F_LOGS) - 1));   // this lane's slice-table replica
@@ -296,25 +301,49 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
     }
     __syncthreads();
 
+    if (SHARED) {
+        // one table for the CTA, built by its first warp; a table that does not validate
+        // fails every stream of the CTA
+        uint32_t *poison = reinterpret_cast<uint32_t *>(gen(cf_0));
+        if (warp == 0) {
+            const uint8_t *h = a.shared_hdr;
+            Tables tb{};
+            tb.wide = reinterpret_cast<uint32_t *>(gen(l1_0));
+            bool ok = fits && build_table<T_WIDE1>(
+                [&](uint32_t s) { return (uint32_t)h[4 + 2 * s] | ((uint32_t)h[5 + 2 * s] << 8); }, tb, lane);
+            if (lane == 0) *poison = (ok && h[0] == 'R' && h[1] == '1') ? 0u : 1u;
+        }
+        __syncthreads();
+        if (*poison && n) { st = ST_BAD_HEADER; n = 0; }
+        // the ring starts cold: slots 0..3 are requested the ordinary way
+        ring.valid_slots = n ? ring.valid_slots : 0;
+        __syncwarp();
+        if (n) {
+            ring.issue(0, k == 0);
+            ring.require(skew + LEAD);
+        }
+    }
     // The stream's first 576 bytes (table + states, wherever the 16-byte boundary
     // falls) land linearly across ring + mirror: four 144-byte copies, one per
     // slot barrier, so every barrier has completed one phase -- as if ring slots
     // 0..3 had been filled and consumed -- when normal ring operation takes over.
-    if (k == 0 && n) {
+    if (!SHARED && k == 0 && n) {
         for (uint32_t j = 0; j < F_NSLOT; j++) {
             mbar_expect_tx(&ring.bars[j], 144);
             bulk_g2s_sa(ring.sa + 144 * j, ring.abase + 144 * j, 144, smem_addr(&ring.bars[j]));
         }
     }
     __syncwarp();
-    if (n)
-        for (uint32_t j = 0; j < F_NSLOT; j++)
-            if (!ring.dead && !mbar_wait(&ring.bars[j], 0)) ring.dead = true;
-    ring.issued = ring.ready = F_NSLOT;
+    if (!SHARED) {
+        if (n)
+            for (uint32_t j = 0; j < F_NSLOT; j++)
+                if (!ring.dead && !mbar_wait(&ring.bars[j], 0)) ring.dead = true;
+        ring.issued = ring.ready = F_NSLOT;
+    }
 
     // ---- per-stream tables, built by the whole warp one stream at a time ------------
 #pragma unroll 1
-    for (uint32_t gg = 0; gg < 4; gg++) {
+    for (uint32_t gg = 0; !SHARED && gg < 4; gg++) {
         uint32_t on = __shfl_sync(0xffffffffu, n, gg * 8);
         if (!on) continue;
         uint32_t sk = __shfl_sync(0xffffffffu, skew, gg * 8);
@@ -338,7 +367,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_stream(StreamArgs a)
     }
     __syncwarp();
 
-    const uint32_t xo = ring.sa + skew + HDR_BYTES + 4 * k;
+    const uint32_t xo = ring.sa + skew + (SHARED ? 0u : HDR_BYTES) + 4 * k;
     uint32_t x = lds_u8(xo) | (lds_u8(xo + 1) << 8) | (lds_u8(xo + 2) << 16) | (lds_u8(xo + 3) << 24);
     uint32_t cursor = skew + LEAD;
     uint8_t *out = a.dst + doff;

@@ -116,11 +116,13 @@ static int launch_stream(const StreamArgs &a, cudaStream_t cs)
     static bool done[64];
     int rc = stream_smem_ok();
     if (rc) return rc;
-    rc = opt_in_smem(k_stream<SINK, CRC, WARPS, CFN>, F_SMEM_DYN, done);
+    // the shared-table instance needs little shared memory and runs two CTAs per SM
+    constexpr uint32_t shm = CFN < 0 ? 2u * F_WIDE_BYTES + WARPS * 4 * stream_group_bytes(CFN) : F_SMEM_DYN;
+    rc = opt_in_smem(k_stream<SINK, CRC, WARPS, CFN>, shm, done);
     if (rc) return rc;
     constexpr unsigned groups = stream_groups(CFN, WARPS);
     unsigned blocks = (a.njobs + groups - 1) / groups;
-    k_stream<SINK, CRC, WARPS, CFN><<<blocks, WARPS * 32, F_SMEM_DYN, cs>>>(a);
+    k_stream<SINK, CRC, WARPS, CFN><<<blocks, WARPS * 32, shm, cs>>>(a);
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return fail_cuda("launch k_stream", le);
     return LMZ_GPU_OK;
@@ -136,6 +138,7 @@ static StreamArgs as_stream_args(const RansArgs &a)
     StreamArgs sa{};
     sa.src = a.src; sa.sjobs = a.jobs; sa.offs = a.offs; sa.plane = a.plane;
     sa.njobs = a.njobs; sa.dst = a.dst; sa.status = a.status; sa.any_bad = a.any_bad;
+    sa.shared_hdr = a.shared_hdr;
     return sa;
 }
 
@@ -147,7 +150,17 @@ static StreamArgs as_stream_args(const RansArgs &a)
 static int launch_rans(const RansArgs &a, cudaStream_t cs, bool sorted = false)
 {
     if (a.njobs == 0) return LMZ_GPU_OK;
-    if (a.shared_hdr) return launch_rans_mode<T_WIDE, WARPS_WIDE>(a, cs);
+    if (a.shared_hdr) {
+        // one table for the whole launch: the k_stream instance (128 streams per SM, leaner
+        // steps) once every SM is full, the plain kernel (shorter chain on a lone warp) below
+        int sms = 0;
+        int rc = sm_count(&sms);
+        if (rc) return rc;
+        const bool plain = g_force_table_mode == T_NARROW ||
+                           (g_force_table_mode < 0 && a.njobs < (unsigned)sms * 128u);
+        return plain ? launch_rans_mode<T_WIDE, WARPS_WIDE>(a, cs)
+                     : launch_stream<SINK_BYTES, false, -1>(as_stream_args(a), cs);
+    }
     int mode = g_force_table_mode;
     if (mode < 0) {
         int sms = 0;
