@@ -258,7 +258,7 @@ def main():
     # ---- end to end: pinned host archive -> device, decode, verdicts back ---------------
     # The public host-to-HBM call: the upload is cut into slices so slice i decodes
     # while slice i+1 is still crossing PCIe.
-    pd = decode.PipelinedDecoder(dec.archive, nslices=8, checksum=not a.no_crc)
+    pd = decode.PipelinedDecoder(dec.archive, checksum=not a.no_crc)
     pinned = pin_host(np.asarray(blob[:int(dec.archive.table_off)]))
     nres = sum(s.plan.chunks.size + 1 for s in pd.slices)
     host_res = torch.empty(nres, dtype=torch.int32).pin_memory()
@@ -343,7 +343,7 @@ def main():
         "clocks": clk.summary(),
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s",
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": int(host_res.numel() * 4),
-                "api": "lmz_b200.decode.PipelinedDecoder.run_from_host, 8 slices"},
+                "api": f"lmz_b200.decode.PipelinedDecoder.run_from_host, {len(pd.slices)} slices"},
         "gpu_launches": int(dec.launches_per_run * a.steps),
         "roofline": {"bound": "hbm", "kernel": kname[dom],
                      "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",

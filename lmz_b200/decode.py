@@ -221,12 +221,19 @@ class PipelinedDecoder:
     into `nslices` runs of consecutive payload bytes, each with its own plan, and
     slice i decodes on the compute stream while slice i+1 is still crossing PCIe on
     the copy stream.  All slices write into one output buffer.  Archives with refs
-    or deltas (which read other chunks' output) use a single slice."""
+    or deltas (which read other chunks' output) use a single slice.
 
-    def __init__(self, ar, nslices: int = 8, device=None, checksum: bool = True):
+    `nslices=None` chooses: 8 for archives of small chunks; for chunks of a megabyte or
+    more, whose decode time is the latency of one long stream whatever their number,
+    one slice per ~1900 such chunks (a slice of fewer costs as much as a full one)."""
+
+    def __init__(self, ar, nslices=None, device=None, checksum: bool = True):
         import torch
         self.archive = ar if isinstance(ar, fmt.Archive) else fmt.Archive(ar)
         r = self.archive.records
+        if nslices is None:
+            big = int((r["rlen"] >= (1 << 20)).sum())
+            nslices = 8 if big == 0 else max(1, min(8, big // 1900))
         sourced = np.isin(r["codec"], (fmt.CODEC_REF, fmt.CODEC_DELTA)).any()
         order = np.argsort(r["off"], kind="stable")
         nslices = 1 if sourced or r.size < nslices else nslices
