@@ -36,6 +36,19 @@ constexpr uint32_t F_SLOT = 128, F_NSLOT = 4, F_RING = F_SLOT * F_NSLOT;
 constexpr uint32_t F_MIRROR = 272;                 // a tile reads at most 256 + 2 bytes ahead
 constexpr uint32_t F_RING_BYTES = F_RING + F_MIRROR + 16;   // 800
 constexpr uint32_t F_STAGE = 144;                  // 128 + 16: groups land 4 banks apart
+// The per-stream wide instance (CFN = 0) runs one warp per scheduler, where every
+// instruction of tile bookkeeping is paid in full.  With 12 streams per CTA (3 warps) it
+// has shared memory to spare: its tiles are then twice as long (256 symbols) and its ring
+// twice as deep.  With 13 streams the tables leave no room for that.
+__host__ __device__ constexpr bool stream_long_tiles(int cfn, int warps) { return cfn == 0 && warps == 3; }
+__host__ __device__ constexpr uint32_t stream_tile(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 256u : 128u; }
+__host__ __device__ constexpr uint32_t stream_nslot(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 8u : F_NSLOT; }
+__host__ __device__ constexpr uint32_t stream_mirror(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 528u : F_MIRROR; }
+__host__ __device__ constexpr uint32_t stream_ring_bytes(int cfn, int warps)
+{
+    return F_SLOT * stream_nslot(cfn, warps) + stream_mirror(cfn, warps) + 16;
+}
+__host__ __device__ constexpr uint32_t stream_stage(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 272u : F_STAGE; }
 #ifndef LMZ_CRC_LOGS
 #define LMZ_CRC_LOGS 3
 #endif
@@ -99,7 +112,12 @@ __host__ __device__ constexpr int stream_warps(int cfn, bool crc)
 #endif
     return w;
 }
-__host__ __device__ constexpr unsigned stream_groups(int cfn, int warps) { return cfn ? warps * 4 : F_WIDE_GROUPS; }
+// (the wide instance runs as 3 warps = 12 streams, all on the full-tile path, when the
+// launch fits that way, else as 4 warps = 13 streams, the thirteenth alone in its warp)
+__host__ __device__ constexpr unsigned stream_groups(int cfn, int warps)
+{
+    return cfn ? warps * 4 : (warps * 4 < F_WIDE_GROUPS ? warps * 4 : F_WIDE_GROUPS);
+}
 static_assert(F_LOGS != 3 || (stream_warps(128, true) == 19 && stream_warps(256, true) == 16), "shared memory budget");
 
 __device__ __forceinline__ void bulk_g2s_sa(uint32_t dst_sa, const void *src, uint32_t bytes,
@@ -111,7 +129,9 @@ __device__ __forceinline__ void bulk_g2s_sa(uint32_t dst_sa, const void *src, ui
 }
 
 // Input ring with a mirror of its head behind it.  Offsets are bytes from `abase`.
-struct MRing {
+template <uint32_t NSLOT_, uint32_t MIRROR_>
+struct MRingT {
+    static constexpr uint32_t F_NSLOT = NSLOT_, F_RING = F_SLOT * NSLOT_, F_MIRROR = MIRROR_;
     uint32_t sa;           // shared address of the ring
     uint64_t *bars;
     const uint8_t *abase;
@@ -226,6 +246,9 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     constexpr uint32_t G = stream_groups(CFN, WARPS), CFB = WIDE ? 16u : 4u * CFN;
     constexpr uint32_t LEAD = (SHARED ? 0u : HDR_BYTES) + STATE_BYTES;
     constexpr uint32_t MAX_LIVE = CFN == 128 ? F_SMALL_LIVE : 256u;
+    constexpr uint32_t TS = stream_tile(CFN, WARPS), NSL = stream_nslot(CFN, WARPS), RB = stream_ring_bytes(CFN, WARPS);
+    constexpr uint32_t STG = stream_stage(CFN, WARPS), RINGB = F_SLOT * NSL;
+    constexpr uint32_t HS = NSL == 8 ? 160u : 144u;     // header staging copy: four of them cover 548 + 15 bytes
     static_assert(!WIDE || !CRC, "the wide instance has no room for CRC tables");
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t k = lane & 7u, g = lane >> 3, gi = warp * 4 + g;
@@ -243,9 +266,9 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     constexpr uint32_t GA = WARPS * 4;
     const uint32_t gs = gi < G ? gi : G - 1;
     const uint32_t bars_0 = (s0 + 15u) & ~15u;
-    const uint32_t stage_0 = bars_0 + GA * 32;
-    const uint32_t ring_0 = stage_0 + GA * F_STAGE;
-    const uint32_t cf_0 = (ring_0 + G * F_RING_BYTES + CFB - 1) & ~(CFB - 1);
+    const uint32_t stage_0 = bars_0 + GA * 8 * NSL;
+    const uint32_t ring_0 = stage_0 + GA * STG;
+    const uint32_t cf_0 = (ring_0 + G * RB + CFB - 1) & ~(CFB - 1);
     // compact: level 1 at the top; wide: 16 KiB tables from the first 16 KiB boundary up
     const uint32_t l1_0 = WIDE ? (cf_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1)
                                : ((CRC ? tab0 : top) & ~4095u) - WARPS * 4096u;
@@ -253,13 +276,13 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     auto gen = [&](uint32_t sa) { return ssm + (sa - s0); };
     const uint32_t l1_sa = SHARED ? l1_0 : WIDE ? l1_0 + gs * F_WIDE_BYTES : l1_0 + warp * 4096 + g * 4;
     const uint32_t cf_sa = cf_0 + gs * CFB;
-    const uint32_t stage_sa = stage_0 + gi * F_STAGE;
+    const uint32_t stage_sa = stage_0 + gi * STG;
     const uint32_t tls = tab0 + 4 * (lane & ((1u << F_LOGS) - 1));   // this lane's slice-table replica
     const uint32_t tla = adv0 - 4096u;                              // crc_advance<0> adds 4 .. 7 KiB
 
-    MRing ring;
-    ring.sa = ring_0 + gs * F_RING_BYTES;
-    ring.bars = reinterpret_cast<uint64_t *>(gen(bars_0)) + gi * F_NSLOT;
+    MRingT<NSL, stream_mirror(CFN, WARPS)> ring;
+    ring.sa = ring_0 + gs * RB;
+    ring.bars = reinterpret_cast<uint64_t *>(gen(bars_0)) + gi * NSL;
 
     // ---- this group's stream ------------------------------------------------------
     const uint32_t job = blockIdx.x * G + gi;
@@ -290,7 +313,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     ring.issued = 0; ring.ready = 0; ring.dead = false;
 
     if (k == 0 && gi < G)
-        for (uint32_t j = 0; j < F_NSLOT; j++) mbar_init(&ring.bars[j], 1);
+        for (uint32_t j = 0; j < NSL; j++) mbar_init(&ring.bars[j], 1);
     mbar_fence_init();
     if (CRC && fits) {
         // slice-by-4 tables, each word 8 times; then "advance by one row minus one lane unit"
@@ -323,22 +346,24 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
             ring.require(skew + LEAD);
         }
     }
-    // The stream's first 576 bytes (table + states, wherever the 16-byte boundary
-    // falls) land linearly across ring + mirror: four 144-byte copies, one per
-    // slot barrier, so every barrier has completed one phase -- as if ring slots
-    // 0..3 had been filled and consumed -- when normal ring operation takes over.
+    // The stream's first 576 bytes or more (table + states, wherever the 16-byte
+    // boundary falls) land linearly from the ring's start: four copies, one on each of
+    // the first four slot barriers, which have then completed one phase -- as if ring
+    // slots 0..3 had been filled and consumed -- when normal ring operation takes over.
     if (!SHARED && k == 0 && n) {
-        for (uint32_t j = 0; j < F_NSLOT; j++) {
-            mbar_expect_tx(&ring.bars[j], 144);
-            bulk_g2s_sa(ring.sa + 144 * j, ring.abase + 144 * j, 144, smem_addr(&ring.bars[j]));
+        for (uint32_t j = 0; j < 4; j++) {
+            mbar_expect_tx(&ring.bars[j], HS);
+            bulk_g2s_sa(ring.sa + HS * j, ring.abase + HS * j, HS, smem_addr(&ring.bars[j]));
         }
     }
     __syncwarp();
     if (!SHARED) {
         if (n)
-            for (uint32_t j = 0; j < F_NSLOT; j++)
+            for (uint32_t j = 0; j < 4; j++)
                 if (!ring.dead && !mbar_wait(&ring.bars[j], 0)) ring.dead = true;
-        ring.issued = ring.ready = F_NSLOT;
+        // the bytes of ring slots 0..3 are in place and their barriers are one phase on; a
+        // deeper ring's other slots and barriers are untouched
+        ring.issued = ring.ready = 4;
     }
 
     // ---- per-stream tables, built by the whole warp one stream at a time ------------
@@ -347,7 +372,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         uint32_t on = __shfl_sync(0xffffffffu, n, gg * 8);
         if (!on) continue;
         uint32_t sk = __shfl_sync(0xffffffffu, skew, gg * 8);
-        const uint32_t rsa = ring_0 + (warp * 4 + gg) * F_RING_BYTES;
+        const uint32_t rsa = ring_0 + (warp * 4 + gg) * RB;
         auto rd = [&](uint32_t o) { return lds_u8(rsa + o); };     // header sits in the first 548+15 bytes
         Tables tb{};
         auto freq_of = [&](uint32_t s) { return rd(sk + 4 + 2 * s) | (rd(sk + 5 + 2 * s) << 8); };
@@ -378,7 +403,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     const uint32_t msh = (uint32_t)(reinterpret_cast<uintptr_t>(mant) & 3u) * 8u;
     const uint32_t *mq = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(mant) & ~uintptr_t(3));
     uint32_t m[5] = {0, 0, 0, 0, 0};
-    const uint32_t my_tiles = (n + TILE - 1) / TILE;
+    const uint32_t my_tiles = (n + TS - 1) / TS;
     if (SINK == SINK_BF16 && my_tiles) {
 #pragma unroll
         for (int i = 0; i < 5; i++) m[i] = __ldg(mq + i);
@@ -392,22 +417,22 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     const uint32_t warp_tiles = __reduce_max_sync(0xffffffffu, my_tiles);
 #pragma unroll 1
     for (uint32_t t = 0; t < warp_tiles; t++) {
-        const uint32_t done = t * TILE;
+        const uint32_t done = t * TS;
         const uint32_t rem = n > done ? n - done : 0;
         __syncwarp();
         if (rem) {
             ring.issue(cursor, k == 0);
-            ring.require(cursor + 2 * TILE);
+            ring.require(cursor + 2 * TS);
         }
         __syncwarp();
-        const uint32_t caddr0 = ring.sa + (cursor & (F_RING - 1));
+        const uint32_t caddr0 = ring.sa + (cursor & (RINGB - 1));
         uint32_t caddr = caddr0;
         // (lanes that never had a stream run along in full tiles; nothing of theirs is kept)
-        const bool full = __all_sync(0xffffffffu, rem >= TILE);
+        const bool full = __all_sync(0xffffffffu, rem >= TS);
         if (full) {
             if (SINK == SINK_BF16 && CRC && pending) acc = crc_advance<0>(tla, acc);
 #pragma unroll
-            for (uint32_t s4 = 0; s4 < TILE / NLANES; s4 += 4) {
+            for (uint32_t s4 = 0; s4 < TS / NLANES; s4 += 4) {
                 uint32_t hist = 0, e;
                 e = stream_step4<CFN, true>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + s4 * NLANES + k, e);
@@ -430,7 +455,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
                 pending = false;
             }
 #pragma unroll 1
-            for (uint32_t s = 0; s < TILE / NLANES; s++) {
+            for (uint32_t s = 0; s < TS / NLANES; s++) {
                 bool active = s * NLANES + k < rem;
                 uint32_t e = stream_step<CFN>(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
                 if (active) sts_u8(stage_sa + s * NLANES + k, e);
@@ -439,17 +464,27 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         cursor += caddr - caddr0;
         __syncwarp();
         if (!rem) continue;
-        const uint4 ev = lds_u128(stage_sa + 16 * k);        // this lane's 16 symbols
+        constexpr uint32_t PER = TS / NLANES;                  // this lane's symbols of the tile: 16 or 32
+        uint4 evs[PER / 16];
+#pragma unroll
+        for (uint32_t q = 0; q < PER / 16; q++) evs[q] = lds_u128(stage_sa + PER * k + 16 * q);
+        const uint4 ev = evs[0];
 
         if (SINK == SINK_BYTES) {
-            if (rem >= TILE && al == 0) {
-                *reinterpret_cast<uint4 *>(out + done + k * 16) = ev;
-            } else {
-                const uint32_t cnt = rem < TILE ? rem : TILE;
-                const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w};
+            if (rem >= TS && al == 0) {
 #pragma unroll
-                for (uint32_t i = 0; i < 16; i++)
-                    if (k * 16 + i < cnt) out[done + k * 16 + i] = (uint8_t)(ew[i >> 2] >> (8 * (i & 3)));
+                for (uint32_t q = 0; q < PER / 16; q++)
+                    *reinterpret_cast<uint4 *>(out + done + k * PER + 16 * q) = evs[q];
+            } else {
+                const uint32_t cnt = rem < TS ? rem : TS;
+#pragma unroll
+                for (uint32_t q = 0; q < PER / 16; q++) {
+                    const uint32_t ew[4] = {evs[q].x, evs[q].y, evs[q].z, evs[q].w};
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; i++)
+                        if (k * PER + 16 * q + i < cnt)
+                            out[done + k * PER + 16 * q + i] = (uint8_t)(ew[i >> 2] >> (8 * (i & 3)));
+                }
             }
             continue;
         }

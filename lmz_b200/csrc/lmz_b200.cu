@@ -108,11 +108,11 @@ static int stream_smem_ok()
 
 // CFN = 128 is for streams the caller knows to have at most F_SMALL_LIVE live symbols;
 // CFN = 0 is the per-stream wide table (13 streams per SM).
-template <int SINK, bool CRC, int CFN>
+template <int SINK, bool CRC, int CFN, int WARPS_AS = 0>
 static int launch_stream(const StreamArgs &a, cudaStream_t cs)
 {
     if (a.njobs == 0) return LMZ_GPU_OK;
-    constexpr int WARPS = stream_warps(CFN, CRC);
+    constexpr int WARPS = WARPS_AS ? WARPS_AS : stream_warps(CFN, CRC);
     static bool done[64];
     int rc = stream_smem_ok();
     if (rc) return rc;
@@ -132,6 +132,16 @@ static int launch_stream(const StreamArgs &a, cudaStream_t cs)
 static int g_force_table_mode = -1;
 
 static int sm_count(int *out);
+
+static StreamArgs as_stream_args(const RansArgs &a);
+
+// The per-stream wide instance: 12 streams per CTA when that still gives every stream
+// an SM slot at once, else 13.
+static int launch_wide1(const RansArgs &a, int sms, cudaStream_t cs)
+{
+    if (a.njobs <= (unsigned)sms * 12u) return launch_stream<SINK_BYTES, false, 0, 3>(as_stream_args(a), cs);
+    return launch_stream<SINK_BYTES, false, 0>(as_stream_args(a), cs);
+}
 
 static StreamArgs as_stream_args(const RansArgs &a)
 {
@@ -176,14 +186,18 @@ static int launch_rans(const RansArgs &a, cudaStream_t cs, bool sorted = false)
             tail.jobs = a.jobs + cap;
             tail.njobs = a.njobs - cap;
             if (tail.status) tail.status = a.status + cap;
-            rc = launch_stream<SINK_BYTES, false, 0>(as_stream_args(head), cs);
+            rc = launch_wide1(head, sms, cs);
             if (rc) return rc;
             return launch_rans_mode<T_NARROW, WARPS_NARROW>(tail, cs);
         } else {
             mode = a.njobs >= COMPACT_MIN_JOBS ? T_COMPACT : T_NARROW;
         }
     }
-    if (mode == T_WIDE1) return launch_stream<SINK_BYTES, false, 0>(as_stream_args(a), cs);
+    if (mode == T_WIDE1) {
+        int sms = 0;
+        int rc = sm_count(&sms);
+        return rc ? rc : launch_wide1(a, sms, cs);
+    }
     if (mode == T_COMPACT) return launch_stream<SINK_BYTES, false, 256>(as_stream_args(a), cs);
     return launch_rans_mode<T_NARROW, WARPS_NARROW>(a, cs);
 }
