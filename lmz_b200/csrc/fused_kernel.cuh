@@ -138,18 +138,21 @@ struct MRingT {
     uint32_t valid_slots, issued, ready;
     bool dead;
 
+    // Every lane of the group keeps `issued` (so the usual "nothing to request" costs no
+    // divergent branch); only the leader touches the barrier and starts the copies.
     __device__ __forceinline__ void issue(uint32_t cursor, bool leader)
     {
-        if (!leader) return;
         uint32_t lim = cursor / F_SLOT + F_NSLOT;
         if (lim > valid_slots) lim = valid_slots;
         while (issued < lim) {
-            uint32_t j = issued % F_NSLOT;
-            uint32_t m = j * F_SLOT < F_MIRROR ? min(F_SLOT, F_MIRROR - j * F_SLOT) : 0u;
-            const uint8_t *g = abase + (size_t)issued * F_SLOT;
-            mbar_expect_tx(&bars[j], F_SLOT + m);
-            bulk_g2s_sa(sa + j * F_SLOT, g, F_SLOT, smem_addr(&bars[j]));
-            if (m) bulk_g2s_sa(sa + F_RING + j * F_SLOT, g, m, smem_addr(&bars[j]));
+            if (leader) {
+                uint32_t j = issued % F_NSLOT;
+                uint32_t m = j * F_SLOT < F_MIRROR ? min(F_SLOT, F_MIRROR - j * F_SLOT) : 0u;
+                const uint8_t *g = abase + (size_t)issued * F_SLOT;
+                mbar_expect_tx(&bars[j], F_SLOT + m);
+                bulk_g2s_sa(sa + j * F_SLOT, g, F_SLOT, smem_addr(&bars[j]));
+                if (m) bulk_g2s_sa(sa + F_RING + j * F_SLOT, g, m, smem_addr(&bars[j]));
+            }
             issued++;
         }
     }
@@ -422,9 +425,8 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         __syncwarp();
         if (rem) {
             ring.issue(cursor, k == 0);
-            ring.require(cursor + 2 * TS);
+            ring.require(cursor + 2 * TS);         // every lane sees the completion itself
         }
-        __syncwarp();
         const uint32_t caddr0 = ring.sa + (cursor & (RINGB - 1));
         uint32_t caddr = caddr0;
         // (lanes that never had a stream run along in full tiles; nothing of theirs is kept)
