@@ -61,7 +61,10 @@ int lmz_gpu_validate(const void *streams, const void *off, unsigned nstr);
  * shared by all streams (each stream then starts at its 8 states) or NULL.
  * d_streams must be 16-byte aligned with lmz_gpu_pad_bytes() of slack after
  * the last stream.  Asynchronous on cuda_stream (NULL = default); `tpb` is
- * accepted and ignored. */
+ * accepted and ignored.  Unlike the reference's, a batch of 9472 streams or more
+ * with per-stream tables takes (nstr + 2) * 4 bytes of stream-ordered memory from
+ * a pool this library keeps per device, for an index list that sorts the streams
+ * by alphabet size; lmz_gpu_decode_batch_dev_noalloc never does. */
 int lmz_gpu_decode_batch_dev(const void *d_hdr, const void *d_streams, const void *d_off,
                              unsigned nstr, unsigned plane, void *d_out, void *cuda_stream,
                              unsigned tpb);

@@ -82,6 +82,12 @@ struct StreamArgs {
     uint32_t *piece_crc;        // SINK_BF16 with checksums: R() per 64 KiB piece
     const CrcTables *tabs;
     const uint8_t *shared_hdr;  // CFN = -1: the 516-byte table every stream of the launch shares
+    // Optional indirection, filled on the device by k_classify: the launch covers the
+    // first *count entries of `order` (read from its end backwards when order_from_back),
+    // each the index of a job; CTAs past the count leave at once.
+    const uint32_t *order;
+    const uint32_t *count;
+    uint32_t order_from_back;
 };
 
 constexpr uint32_t F_WIDE_BYTES = PROB_SCALE * 4;   // CFN = 0: one 16 KiB slot -> entry table per stream
@@ -288,8 +294,14 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     ring.bars = reinterpret_cast<uint64_t *>(gen(bars_0)) + gi * NSL;
 
     // ---- this group's stream ------------------------------------------------------
-    const uint32_t job = blockIdx.x * G + gi;
-    const bool have = gi < G && job < a.njobs;        // (the wide instance has spare lanes)
+    const uint32_t idx = blockIdx.x * G + gi;
+    uint32_t limit = a.njobs;
+    if (a.count) {
+        limit = *a.count;
+        if (blockIdx.x * G >= limit) return;          // the whole CTA: nothing of this class is left
+    }
+    const bool have = gi < G && idx < limit;          // (the wide instance has spare lanes)
+    const uint32_t job = (have && a.order) ? a.order[a.order_from_back ? a.njobs - 1 - idx : idx] : idx;
     uint64_t soff = 0, doff = 0, moff = 0;
     uint32_t slen = 0, n = 0, piece0 = 0;
     if (have) {
@@ -565,6 +577,33 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         }
         if (a.status) a.status[job] = st;
         if (a.any_bad && st != ST_OK && st != ST_SLACK) atomicOr(a.any_bad, 1u);
+    }
+}
+
+// Sort a launch's streams by alphabet size, on the device: one warp per stream counts the
+// non-zero frequencies of its table; streams with at most `small_live` go to the front of
+// `order` (counts[0] of them), the others to its back (counts[1]).
+__global__ void k_classify(StreamArgs a, uint32_t small_live, uint32_t *order, uint32_t *counts)
+{
+    const uint32_t job = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (job >= a.njobs) return;
+    uint64_t soff;
+    uint32_t slen;
+    if (a.sjobs) { soff = a.sjobs[job].src_off; slen = a.sjobs[job].src_len; }
+    else { soff = a.offs[2 * job]; slen = (uint32_t)a.offs[2 * job + 1]; }
+    uint32_t live = 0;
+    if (slen >= HDR_BYTES + STATE_BYTES) {
+        const uint8_t *h = a.src + soff + 4 + 16 * lane;
+#pragma unroll
+        for (int i = 0; i < 8; i++) live += (h[2 * i] | h[2 * i + 1]) != 0;
+        live = __reduce_add_sync(0xffffffffu, live);
+    } else {
+        live = 257;                                    // too short: the large instance reports it
+    }
+    if (lane == 0) {
+        const bool small = live <= small_live;
+        const uint32_t pos = atomicAdd(&counts[small ? 0 : 1], 1u);
+        order[small ? pos : a.njobs - 1 - pos] = job;
     }
 }
 

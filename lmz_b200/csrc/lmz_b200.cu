@@ -157,7 +157,71 @@ static StreamArgs as_stream_args(const RansArgs &a)
 // shared-memory round trip.  With `sorted` jobs (longest first, as the planner lists
 // them) a launch slightly over that size still takes the wide kernel for its head
 // when what is left over is short.
-static int launch_rans(const RansArgs &a, cudaStream_t cs, bool sorted = false)
+// A large batch whose tables the host cannot see: sort the streams by alphabet size on the
+// device and give the small ones to the denser 128-entry instance.  The index list lives in
+// stream-ordered memory for the duration of the two launches.  Returns 1 when that memory
+// is not to be had (the caller then runs everything on the 256-entry instance).
+// A memory pool of this library's own per device, which keeps what is freed into it: the
+// default pool hands memory back to the driver at every synchronisation, and getting it
+// again costs more than the index list's kernels.
+static cudaMemPool_t scratch_pool()
+{
+    static cudaMemPool_t pools[64];
+    static bool tried[64];
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!tried[dev]) {
+        tried[dev] = true;
+        cudaMemPoolProps props{};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        cudaMemPool_t pool = nullptr;
+        if (cudaMemPoolCreate(&pool, &props) == cudaSuccess) {
+            uint64_t keep = ~0ull;
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+            pools[dev] = pool;
+        } else {
+            cudaGetLastError();
+        }
+    }
+    return pools[dev];
+}
+
+static int launch_compact_sorted(const RansArgs &a, cudaStream_t cs)
+{
+    uint32_t *buf = nullptr;
+    const size_t bytes = ((size_t)a.njobs + 2) * sizeof(uint32_t);
+    cudaMemPool_t pool = scratch_pool();
+    if (!pool || cudaMallocFromPoolAsync((void **)&buf, bytes, pool, cs) != cudaSuccess) {
+        cudaGetLastError();
+        return 1;
+    }
+    uint32_t *counts = buf, *order = buf + 2;
+    StreamArgs sa = as_stream_args(a);
+    int rc = LMZ_GPU_OK;
+    do {
+        if (cudaMemsetAsync(counts, 0, 8, cs) != cudaSuccess) { rc = fail_msg(LMZ_GPU_ECUDA, "cudaMemsetAsync failed"); break; }
+        k_classify<<<(a.njobs + 7) / 8, 256, 0, cs>>>(sa, F_SMALL_LIVE, order, counts);
+        cudaError_t le = cudaGetLastError();
+        if (le != cudaSuccess) { rc = fail_cuda("launch k_classify", le); break; }
+        sa.order = order;
+        sa.count = counts;
+        sa.order_from_back = 0;
+        rc = launch_stream<SINK_BYTES, false, 128>(sa, cs);
+        if (rc) break;
+        sa.count = counts + 1;
+        sa.order_from_back = 1;
+        rc = launch_stream<SINK_BYTES, false, 256>(sa, cs);
+    } while (0);
+    cudaFreeAsync(buf, cs);
+    return rc;
+}
+
+static int launch_rans(const RansArgs &a, cudaStream_t cs, bool sorted = false, bool may_alloc = true)
 {
     if (a.njobs == 0) return LMZ_GPU_OK;
     if (a.shared_hdr) {
@@ -198,7 +262,13 @@ static int launch_rans(const RansArgs &a, cudaStream_t cs, bool sorted = false)
         int rc = sm_count(&sms);
         return rc ? rc : launch_wide1(a, sms, cs);
     }
-    if (mode == T_COMPACT) return launch_stream<SINK_BYTES, false, 256>(as_stream_args(a), cs);
+    if (mode == T_COMPACT) {
+        if (may_alloc && g_force_table_mode < 0) {
+            int rc = launch_compact_sorted(a, cs);
+            if (rc != 1) return rc;
+        }
+        return launch_stream<SINK_BYTES, false, 256>(as_stream_args(a), cs);
+    }
     return launch_rans_mode<T_NARROW, WARPS_NARROW>(a, cs);
 }
 
@@ -469,7 +539,7 @@ API int lmz_gpu_decode_batch_dev_noalloc(const void *d_hdr, const void *d_stream
     a.shared_hdr = (const uint8_t *)d_hdr;
     a.status = scratch + 64;                 // every job writes its own word
     a.any_bad = scratch;
-    rc = launch_rans(a, cs);
+    rc = launch_rans(a, cs, /*sorted=*/false, /*may_alloc=*/false);
     if (rc) return rc;
     uint32_t bad = 0;
     CK("cudaMemcpyAsync(verdict summary)",

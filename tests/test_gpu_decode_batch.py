@@ -8,7 +8,7 @@ from helpers import DISTRIBUTIONS, SHAPES, distribution, pack_streams, shaped
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=[0, 2, 3], ids=["narrow", "compact", "wide1"])
+@pytest.fixture(autouse=True, params=[0, 2, 3, -1], ids=["narrow", "compact", "wide1", "auto"])
 def table_mode(request, gpu):
     """Every test runs with both per-stream table layouts forced."""
     lib = gpu.library()
@@ -58,6 +58,24 @@ def test_stress_distributions_per_stream_and_shared(gpu, orc, dist, n):
     freqs = orc.rans_freqs(counts)
     header = b"R1\0\0" + freqs.astype("<u2").tobytes()
     _check(gpu, orc, plains, header=header, freqs=freqs)
+
+
+def test_large_batches_are_sorted_by_alphabet_on_the_device(gpu, orc, table_mode):
+    """12 000 short streams, every seventh with more live symbols than the dense instance
+    of the throughput kernel holds: in automatic mode the library counts alphabets on the
+    device and splits the launch; results must not depend on it."""
+    if table_mode not in (-1, 2):
+        pytest.skip("only the throughput kernel takes batches this large")
+    pool = [distribution("uniform" if i % 7 == 0 else "exponent", 640, 900 + i) for i in range(70)]
+    streams = [orc.rans_encode(p) for p in pool]
+    n = 12000
+    blob, offs = pack_streams([streams[i % 70] for i in range(n)])
+    out = np.frombuffer(gpu.decode_batch(blob, offs, n, 640), dtype=np.uint8).reshape(n, 640)
+    assert (out == np.stack([pool[i % 70] for i in range(n)])).all()
+    bad = bytearray(blob)
+    bad[int(np.frombuffer(offs, dtype="<u8")[2 * 777])] = ord("X")      # one stream's magic
+    with pytest.raises(ValueError):
+        gpu.decode_batch(bytes(bad), offs, n, 640)
 
 
 def test_declines_and_errors(gpu, orc):
@@ -112,7 +130,7 @@ def test_stress_extremes_long_streams_and_wide_batches(gpu, orc, dist, table_mod
     """The corners of the decoder stress matrix: 4 MiB streams (batch 1 and 7) and a
     4096-stream batch, per-stream and shared tables.  The wide batch cycles a pool of
     256 distinct streams so the CPU encoder stays out of the way."""
-    if table_mode in (0, 3) and dist != "exponent":
+    if table_mode in (0, 3, -1) and dist != "exponent":
         pytest.skip("one distribution is enough for the narrow and wide-per-stream kernels")
     big = [distribution(dist, 4 << 20, 1000 + i) for i in range(7)]
     _check(gpu, orc, big[:1])
