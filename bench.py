@@ -329,8 +329,9 @@ def main():
     if world == 1:
         cpu_base = cpu_baseline_subprocess(a)
         batch = batch_decode_compare(dec, p)
+        other = default_layout_side(a, barrier) if a.layout == "mapped" and a.model == "llama-3.1-8b" else None
     else:
-        cpu_base = batch = None        # timed at N=1 only
+        cpu_base = batch = other = None        # timed at N=1 only
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": round(ms / a.steps, 3),
@@ -354,6 +355,7 @@ def main():
         "phase_ms": {k: round(v, 3) for k, v in phase_ms.items()},
         "cpu_baseline": cpu_base,
         "batch_decode": batch,
+        "default_layout": other,
     }
     print(json.dumps(line))
     if world > 1:
@@ -434,6 +436,41 @@ def batch_decode_compare(dec, p):
                 raise SystemExit("batch decode differs from the reference's CUDA decoder")
             res["reference_gpu"] = round(ref, 1)
     return res
+
+
+def default_layout_side(a, barrier):
+    """The reference's default 8 MiB chunking (exponent-conditioned BF16), which a GPU
+    decodes at the latency of one 4 Mi-symbol stream per chunk: measured beside the
+    headline on the 8-layer model so that the run stays short."""
+    import argparse as _ap
+    import torch
+    from lmz_b200 import decode
+    b = _ap.Namespace(**vars(a))
+    b.model, b.layout, b.chunk_size = "llama-8layer", "default", 0
+    blob = get_archive(b, 0, barrier)
+    dec = decode.ArchiveDecoder(blob, checksum=not a.no_crc)
+    for _ in range(2):
+        dec.run()
+    dec.check()
+    verify_sample(dec, blob, nsample=6)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        dec.run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 3
+    phase = {}
+    for name, mask in (("stream_decode", 1), ("cond", 2), ("finish", 4)):
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(); dec.run(phases=mask); s1.record()
+        torch.cuda.synchronize()
+        phase[name] = round(s0.elapsed_time(s1), 3)
+    p = dec.plan
+    return {"workload": workload_name(b), "plaintext_bytes": int(p.total), "chunks": int(p.chunks.size),
+            "value": round(p.total / (ms / 1e3) / 1e9, 2), "unit": "GB/s", "ms_per_step": round(ms, 3),
+            "phase_ms": phase}
 
 
 def cpu_baseline_subprocess(a):
