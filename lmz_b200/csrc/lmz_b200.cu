@@ -416,7 +416,7 @@ API int lmz_gpu_encode_batch_dev(const void *d_planes, unsigned nstr, unsigned p
     if (!d_planes || !d_slots || !d_lengths) return fail_msg(LMZ_GPU_EUNSUPPORTED, "null argument");
     if (plane == 0 || plane > (1u << 30)) return fail_msg(LMZ_GPU_EUNSUPPORTED, "plane must be 1 .. 2^30 bytes");
     if ((uintptr_t)d_slots & 511u) return fail_msg(LMZ_GPU_EUNSUPPORTED, "the slot buffer must be 512-byte aligned");
-    constexpr int WARPS = 8;
+    constexpr int WARPS = 4;      // 43 KiB of shared memory a CTA: five CTAs (80 streams) per SM
     static bool done[64];
     constexpr uint32_t shm = encode_smem_bytes(WARPS);
     rc = opt_in_smem(k_encode<WARPS>, shm, done);
