@@ -136,7 +136,8 @@ int lmz_gpu_decode_batch_dev_noalloc(const void *d_hdr, const void *d_streams, c
  * d_planes: nstr planes of `plane` bytes back to back.  d_slots: nstr slots of
  * lmz_gpu_encode_slot_bytes(plane) bytes, 512-byte aligned; stream i is written so
  * that it ENDS at the end of slot i.  d_lengths: nstr uint32, the stream lengths
- * (0 = that plane could not be coded).  Asynchronous on cuda_stream. */
+ * (0 = that plane could not be coded).  plane is 1 .. 2^29; lmz_gpu_encode_slot_bytes
+ * returns 0 outside that range.  Asynchronous on cuda_stream. */
 int lmz_gpu_encode_slot_bytes(unsigned plane);
 int lmz_gpu_encode_batch_dev(const void *d_planes, unsigned nstr, unsigned plane, void *d_slots,
                              void *d_lengths, void *cuda_stream);

@@ -405,7 +405,12 @@ API int lmz_gpu_set_table_mode(int mode)
 
 // ---- batch encode (no counterpart in the reference's GPU library) -------------------
 
-API int lmz_gpu_encode_slot_bytes(unsigned plane) { return (int)encode_slot_bytes(plane); }
+constexpr unsigned ENCODE_MAX_PLANE = 1u << 29;      // slot sizes stay below 2^31
+
+API int lmz_gpu_encode_slot_bytes(unsigned plane)
+{
+    return plane == 0 || plane > ENCODE_MAX_PLANE ? 0 : (int)encode_slot_bytes(plane);
+}
 
 API int lmz_gpu_encode_batch_dev(const void *d_planes, unsigned nstr, unsigned plane, void *d_slots,
                                  void *d_lengths, void *cuda_stream)
@@ -414,7 +419,7 @@ API int lmz_gpu_encode_batch_dev(const void *d_planes, unsigned nstr, unsigned p
     if (rc) return rc;
     if (nstr == 0) return LMZ_GPU_OK;
     if (!d_planes || !d_slots || !d_lengths) return fail_msg(LMZ_GPU_EUNSUPPORTED, "null argument");
-    if (plane == 0 || plane > (1u << 30)) return fail_msg(LMZ_GPU_EUNSUPPORTED, "plane must be 1 .. 2^30 bytes");
+    if (plane == 0 || plane > ENCODE_MAX_PLANE) return fail_msg(LMZ_GPU_EUNSUPPORTED, "plane must be 1 .. 2^29 bytes");
     if ((uintptr_t)d_slots & 511u) return fail_msg(LMZ_GPU_EUNSUPPORTED, "the slot buffer must be 512-byte aligned");
     constexpr int WARPS = 4;      // 43 KiB of shared memory a CTA: five CTAs (80 streams) per SM
     static bool done[64];

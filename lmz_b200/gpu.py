@@ -321,6 +321,8 @@ def encode_batch(planes, nstr: int, plane: int):
         if src.numel() < nstr * plane:
             raise ValueError("planes is too short")
         slot = lib.lmz_gpu_encode_slot_bytes(plane)
+        if slot <= 0:
+            raise ValueError("plane must be at most 2^29 bytes")
         slots = torch.empty(nstr * slot, dtype=torch.uint8, device=dev)       # the allocator aligns to 512
         lens = torch.zeros(nstr, dtype=torch.int32, device=dev)
         cs = torch.cuda.current_stream(dev).cuda_stream
