@@ -264,6 +264,10 @@ def test_pipelined_upload_decodes_the_same_bytes(shard):
         out = pd.run_from_host(pinned)
         pd.check()
         assert (out.cpu().numpy() == shard).all()
+        auto = decode.PipelinedDecoder(blob)                 # slice count chosen by chunk size
+        assert len(auto.slices) == (8 if kw else 1)
+        assert (auto.run_from_host(pinned).cpu().numpy() == shard).all()
+        auto.check()
 
 
 def test_pythia_shaped_delta_chain():

@@ -63,3 +63,27 @@ def test_arguments(gpu):
         gpu.encode_batch(b"abc", 2, 16)
     with pytest.raises(ValueError):
         gpu.encode_batch(b"abc", 1, 0)
+
+
+def test_random_round_trips(gpu, orc):
+    """Seeded random planes - alphabet size, skew, length and batch size all drawn - through
+    encode_batch and back through decode_batch in every table mode; the first stream of
+    every batch is also held to the oracle's encoder."""
+    rng = np.random.default_rng(20261125)
+    lib = gpu.library()
+    try:
+        for trial in range(60):
+            plane = int(rng.choice([1, 3, 64, 129, 1000, 4096, 20000, 70001]))
+            nstr = int(rng.choice([1, 2, 9, 33, 130])) if plane <= 4096 else int(rng.choice([1, 3, 7]))
+            live = int(rng.integers(1, 257))
+            syms = rng.choice(256, live, replace=False)
+            weights = rng.random(live) ** rng.integers(1, 8)
+            weights /= weights.sum()
+            data = syms[rng.choice(live, size=nstr * plane, p=weights)].astype(np.uint8)
+            streams, offsets = gpu.encode_batch(data.tobytes(), nstr, plane)
+            o = np.frombuffer(offsets, dtype="<u8").reshape(nstr, 2)
+            assert streams[:int(o[0, 1])] == orc.rans_encode(data[:plane])
+            lib.lmz_gpu_set_table_mode([0, 2, 3, -1][trial % 4])
+            assert bytes(gpu.decode_batch(streams, offsets, nstr, plane)) == data.tobytes(), (trial, plane, nstr, live)
+    finally:
+        lib.lmz_gpu_set_table_mode(-1)
