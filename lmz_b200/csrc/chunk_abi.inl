@@ -179,7 +179,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         a.dst = (uint8_t *)p->d_scratch;
         a.status = (uint32_t *)p->d_stream_status;
         a.any_bad = (uint32_t *)p->d_any_bad;
-        rc = launch_rans(a, cs, /*sorted=*/true);       // the planner lists long streams first
+        rc = launch_rans(a, cs);
         if (rc) return rc;
     }
 

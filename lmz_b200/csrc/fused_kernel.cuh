@@ -21,9 +21,9 @@
 //   * CFN = 128: level 2 has 128 slots, the four streams of a warp rotated 8
 //     entries apart so their popular symbols sit in different banks; streams with
 //     more than 104 live symbols must be given to the CFN = 256 instance
-//   * CFN = 0: no levels, a 16 KiB slot -> entry table per stream and 13 streams per
-//     CTA: for launches so small that only the length of a symbol's dependent chain
-//     counts (one lookup instead of two and a popcount)
+//   * CFN = 0: no levels, a 16 KiB slot -> entry table per stream and 12 streams per
+//     CTA, 256-symbol tiles: for launches so small that only the length of a symbol's
+//     dependent chain counts (one lookup instead of two and a popcount)
 //   * CFN = -1: the same wide table once per CTA, for batches whose streams share one
 //     516-byte table (lmz_gpu_decode_batch's d_hdr); a stream is then states + words
 #pragma once
@@ -37,9 +37,8 @@ constexpr uint32_t F_MIRROR = 272;                 // a tile reads at most 256 +
 constexpr uint32_t F_RING_BYTES = F_RING + F_MIRROR + 16;   // 800
 constexpr uint32_t F_STAGE = 144;                  // 128 + 16: groups land 4 banks apart
 // The per-stream wide instance (CFN = 0) runs one warp per scheduler, where every
-// instruction of tile bookkeeping is paid in full.  With 12 streams per CTA (3 warps) it
-// has shared memory to spare: its tiles are then twice as long (256 symbols) and its ring
-// twice as deep.  With 13 streams the tables leave no room for that.
+// instruction of tile bookkeeping is paid in full, and has shared memory to spare beside
+// its 12 tables: its tiles are twice as long (256 symbols) and its ring twice as deep.
 __host__ __device__ constexpr bool stream_long_tiles(int cfn, int warps) { return cfn == 0 && warps == 3; }
 __host__ __device__ constexpr uint32_t stream_tile(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 256u : 128u; }
 __host__ __device__ constexpr uint32_t stream_nslot(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 8u : F_NSLOT; }
@@ -91,7 +90,7 @@ struct StreamArgs {
 };
 
 constexpr uint32_t F_WIDE_BYTES = PROB_SCALE * 4;   // CFN = 0: one 16 KiB slot -> entry table per stream
-constexpr int F_WIDE_GROUPS = 13;                   // as many as fit one CTA, each table 16 KiB aligned
+constexpr int F_WIDE_GROUPS = 12;                   // three full warps; 13 tables would fit, but not their rings
 __host__ __device__ constexpr uint32_t stream_group_bytes(int cfn)
 {
     return (cfn > 0 ? 1024 + 4 * cfn : cfn == 0 ? F_WIDE_BYTES : 0) + F_RING_BYTES + F_STAGE + 32;   // 3024 / 2512 / 17360 / 976
@@ -110,7 +109,7 @@ __host__ __device__ constexpr uint32_t stream_crc_slice(uint32_t top)
 __host__ __device__ constexpr int stream_warps(int cfn, bool crc)
 {
     constexpr uint32_t top = F_SMEM_BASE + F_SMEM_DYN;
-    if (cfn == 0) return (F_WIDE_GROUPS + 3) / 4;
+    if (cfn == 0) return F_WIDE_GROUPS / 4;
     if (cfn < 0) return F_SHARED_WARPS;
     int w = (int)(((crc ? stream_crc_slice(top) : top) - F_SMEM_BASE) / (4u * stream_group_bytes(cfn)));
 #ifdef LMZ_STREAM_WARPS_MAX
@@ -118,12 +117,7 @@ __host__ __device__ constexpr int stream_warps(int cfn, bool crc)
 #endif
     return w;
 }
-// (the wide instance runs as 3 warps = 12 streams, all on the full-tile path, when the
-// launch fits that way, else as 4 warps = 13 streams, the thirteenth alone in its warp)
-__host__ __device__ constexpr unsigned stream_groups(int cfn, int warps)
-{
-    return cfn ? warps * 4 : (warps * 4 < F_WIDE_GROUPS ? warps * 4 : F_WIDE_GROUPS);
-}
+__host__ __device__ constexpr unsigned stream_groups(int cfn, int warps) { return warps * 4; }
 static_assert(F_LOGS != 3 || (stream_warps(128, true) == 19 && stream_warps(256, true) == 16), "shared memory budget");
 
 __device__ __forceinline__ void bulk_g2s_sa(uint32_t dst_sa, const void *src, uint32_t bytes,
@@ -269,28 +263,23 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     // four streams interleaved) end where the CRC tables begin, or at the top
     const uint32_t s0 = smem_addr(ssm), top = s0 + dynamic_smem_bytes();
     const uint32_t adv0 = stream_crc_adv(top), tab0 = stream_crc_slice(top);
-    // G groups have work; a warp's four lanes-of-eight always exist (GA >= G).  Lanes
-    // without a group get their own staging slot and barrier words (never used) and
-    // read the last group's tables and ring, so whatever they compute stays in bounds.
-    constexpr uint32_t GA = WARPS * 4;
-    const uint32_t gs = gi < G ? gi : G - 1;
     const uint32_t bars_0 = (s0 + 15u) & ~15u;
-    const uint32_t stage_0 = bars_0 + GA * 8 * NSL;
-    const uint32_t ring_0 = stage_0 + GA * STG;
+    const uint32_t stage_0 = bars_0 + G * 8 * NSL;
+    const uint32_t ring_0 = stage_0 + G * STG;
     const uint32_t cf_0 = (ring_0 + G * RB + CFB - 1) & ~(CFB - 1);
     // compact: level 1 at the top; wide: 16 KiB tables from the first 16 KiB boundary up
     const uint32_t l1_0 = WIDE ? (cf_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1)
                                : ((CRC ? tab0 : top) & ~4095u) - WARPS * 4096u;
     const bool fits = WIDE ? l1_0 + (SHARED ? 1u : G) * F_WIDE_BYTES <= top : cf_0 + G * CFB <= l1_0;
     auto gen = [&](uint32_t sa) { return ssm + (sa - s0); };
-    const uint32_t l1_sa = SHARED ? l1_0 : WIDE ? l1_0 + gs * F_WIDE_BYTES : l1_0 + warp * 4096 + g * 4;
-    const uint32_t cf_sa = cf_0 + gs * CFB;
+    const uint32_t l1_sa = SHARED ? l1_0 : WIDE ? l1_0 + gi * F_WIDE_BYTES : l1_0 + warp * 4096 + g * 4;
+    const uint32_t cf_sa = cf_0 + gi * CFB;
     const uint32_t stage_sa = stage_0 + gi * STG;
     const uint32_t tls = tab0 + 4 * (lane & ((1u << F_LOGS) - 1));   // this lane's slice-table replica
     const uint32_t tla = adv0 - 4096u;                              // crc_advance<0> adds 4 .. 7 KiB
 
     MRingT<NSL, stream_mirror(CFN, WARPS)> ring;
-    ring.sa = ring_0 + gs * RB;
+    ring.sa = ring_0 + gi * RB;
     ring.bars = reinterpret_cast<uint64_t *>(gen(bars_0)) + gi * NSL;
 
     // ---- this group's stream ------------------------------------------------------
@@ -300,7 +289,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         limit = *a.count;
         if (blockIdx.x * G >= limit) return;          // the whole CTA: nothing of this class is left
     }
-    const bool have = gi < G && idx < limit;          // (the wide instance has spare lanes)
+    const bool have = idx < limit;
     const uint32_t job = (have && a.order) ? a.order[a.order_from_back ? a.njobs - 1 - idx : idx] : idx;
     uint64_t soff = 0, doff = 0, moff = 0;
     uint32_t slen = 0, n = 0, piece0 = 0;
@@ -327,7 +316,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     ring.valid_slots = n ? (skew + slen + F_SLOT - 1) / F_SLOT : 0;
     ring.issued = 0; ring.ready = 0; ring.dead = false;
 
-    if (k == 0 && gi < G)
+    if (k == 0)
         for (uint32_t j = 0; j < NSL; j++) mbar_init(&ring.bars[j], 1);
     mbar_fence_init();
     if (CRC && fits) {

@@ -108,11 +108,11 @@ static int stream_smem_ok()
 
 // CFN = 128 is for streams the caller knows to have at most F_SMALL_LIVE live symbols;
 // CFN = 0 is the per-stream wide table (13 streams per SM).
-template <int SINK, bool CRC, int CFN, int WARPS_AS = 0>
+template <int SINK, bool CRC, int CFN>
 static int launch_stream(const StreamArgs &a, cudaStream_t cs)
 {
     if (a.njobs == 0) return LMZ_GPU_OK;
-    constexpr int WARPS = WARPS_AS ? WARPS_AS : stream_warps(CFN, CRC);
+    constexpr int WARPS = stream_warps(CFN, CRC);
     static bool done[64];
     int rc = stream_smem_ok();
     if (rc) return rc;
@@ -133,16 +133,6 @@ static int g_force_table_mode = -1;
 
 static int sm_count(int *out);
 
-static StreamArgs as_stream_args(const RansArgs &a);
-
-// The per-stream wide instance: 12 streams per CTA when that still gives every stream
-// an SM slot at once, else 13.
-static int launch_wide1(const RansArgs &a, int sms, cudaStream_t cs)
-{
-    if (a.njobs <= (unsigned)sms * 12u) return launch_stream<SINK_BYTES, false, 0, 3>(as_stream_args(a), cs);
-    return launch_stream<SINK_BYTES, false, 0>(as_stream_args(a), cs);
-}
-
 static StreamArgs as_stream_args(const RansArgs &a)
 {
     StreamArgs sa{};
@@ -152,11 +142,6 @@ static StreamArgs as_stream_args(const RansArgs &a)
     return sa;
 }
 
-// Launches with at most one CTA of 13 streams per SM are bound by the length of the
-// per-symbol dependent chain alone, and a wide table per stream shortens it by one
-// shared-memory round trip.  With `sorted` jobs (longest first, as the planner lists
-// them) a launch slightly over that size still takes the wide kernel for its head
-// when what is left over is short.
 // A large batch whose tables the host cannot see: sort the streams by alphabet size on the
 // device and give the small ones to the denser 128-entry instance.  The index list lives in
 // stream-ordered memory for the duration of the two launches.  Returns 1 when that memory
@@ -221,47 +206,29 @@ static int launch_compact_sorted(const RansArgs &a, cudaStream_t cs)
     return rc;
 }
 
-static int launch_rans(const RansArgs &a, cudaStream_t cs, bool sorted = false, bool may_alloc = true)
+// A launch that gives every stream an SM slot at once with 12 streams per SM is bound by
+// the length of the per-symbol dependent chain alone, and a wide table per stream shortens
+// it by one shared-memory round trip.  (13 such tables fit an SM too, but then not the long
+// tiles that pay for the instance: above 12 per SM the narrow tables are faster.)
+static int launch_rans(const RansArgs &a, cudaStream_t cs, bool may_alloc = true)
 {
     if (a.njobs == 0) return LMZ_GPU_OK;
+    int sms = 0;
+    int rc = sm_count(&sms);
+    if (rc) return rc;
     if (a.shared_hdr) {
         // one table for the whole launch: the k_stream instance (128 streams per SM, leaner
         // steps) once every SM is full, the plain kernel (shorter chain on a lone warp) below
-        int sms = 0;
-        int rc = sm_count(&sms);
-        if (rc) return rc;
         const bool plain = g_force_table_mode == T_NARROW ||
                            (g_force_table_mode < 0 && a.njobs < (unsigned)sms * 128u);
         return plain ? launch_rans_mode<T_WIDE, WARPS_WIDE>(a, cs)
                      : launch_stream<SINK_BYTES, false, -1>(as_stream_args(a), cs);
     }
     int mode = g_force_table_mode;
-    if (mode < 0) {
-        int sms = 0;
-        int rc = sm_count(&sms);
-        if (rc) return rc;
-        const unsigned cap = (unsigned)sms * stream_groups(0, 4);
-        if (a.njobs <= cap) {
-            mode = T_WIDE1;
-        } else if (sorted && a.jobs && a.njobs < COMPACT_MIN_JOBS) {
-            // the caller guarantees the order; the kernel reads the lengths itself
-            RansArgs head = a, tail = a;
-            head.njobs = cap;
-            tail.jobs = a.jobs + cap;
-            tail.njobs = a.njobs - cap;
-            if (tail.status) tail.status = a.status + cap;
-            rc = launch_wide1(head, sms, cs);
-            if (rc) return rc;
-            return launch_rans_mode<T_NARROW, WARPS_NARROW>(tail, cs);
-        } else {
-            mode = a.njobs >= COMPACT_MIN_JOBS ? T_COMPACT : T_NARROW;
-        }
-    }
-    if (mode == T_WIDE1) {
-        int sms = 0;
-        int rc = sm_count(&sms);
-        return rc ? rc : launch_wide1(a, sms, cs);
-    }
+    if (mode < 0)
+        mode = a.njobs <= (unsigned)sms * F_WIDE_GROUPS ? T_WIDE1
+             : a.njobs >= COMPACT_MIN_JOBS ? T_COMPACT : T_NARROW;
+    if (mode == T_WIDE1) return launch_stream<SINK_BYTES, false, 0>(as_stream_args(a), cs);
     if (mode == T_COMPACT) {
         if (may_alloc && g_force_table_mode < 0) {
             int rc = launch_compact_sorted(a, cs);
@@ -544,7 +511,7 @@ API int lmz_gpu_decode_batch_dev_noalloc(const void *d_hdr, const void *d_stream
     a.shared_hdr = (const uint8_t *)d_hdr;
     a.status = scratch + 64;                 // every job writes its own word
     a.any_bad = scratch;
-    rc = launch_rans(a, cs, /*sorted=*/false, /*may_alloc=*/false);
+    rc = launch_rans(a, cs, /*may_alloc=*/false);
     if (rc) return rc;
     uint32_t bad = 0;
     CK("cudaMemcpyAsync(verdict summary)",
