@@ -85,7 +85,7 @@ int lmz_gpu_set_device(int device);
 /* No counterpart in the reference: choose the per-stream decode-table layout for
  * streams that carry their own table.  -1 = by batch size (default), 0 = narrow
  * (5 KiB per stream), 2 = compact (2 KiB, the most streams per SM), 3 = a wide
- * 16 KiB table per stream (one lookup per symbol; 13 streams per SM, for launches
+ * 16 KiB table per stream (one lookup per symbol; 12 streams per SM, for launches
  * small enough to be bound by per-symbol latency).  A tuning and testing knob;
  * results are identical. */
 int lmz_gpu_set_table_mode(int mode);
