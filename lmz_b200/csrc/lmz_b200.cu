@@ -107,7 +107,7 @@ static int stream_smem_ok()
 }
 
 // CFN = 128 is for streams the caller knows to have at most F_SMALL_LIVE live symbols;
-// CFN = 0 is the per-stream wide table (13 streams per SM).
+// CFN = 0 is the per-stream wide table (12 streams per SM), CFN = -1 one wide table per CTA.
 template <int SINK, bool CRC, int CFN>
 static int launch_stream(const StreamArgs &a, cudaStream_t cs)
 {
