@@ -48,10 +48,7 @@ __host__ __device__ constexpr uint32_t stream_ring_bytes(int cfn, int warps)
     return F_SLOT * stream_nslot(cfn, warps) + stream_mirror(cfn, warps) + 16;
 }
 __host__ __device__ constexpr uint32_t stream_stage(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 272u : F_STAGE; }
-#ifndef LMZ_CRC_LOGS
-#define LMZ_CRC_LOGS 3
-#endif
-constexpr uint32_t F_LOGS = LMZ_CRC_LOGS;          // CRC slice tables replicated 2^F_LOGS times (32 KiB at 8x)
+constexpr uint32_t F_LOGS = 3;                     // CRC slice tables replicated 8x (32 KiB): 4x and 16x measured slower
 constexpr uint32_t F_CRC_BYTES = (4096u << F_LOGS) + 4096u;   // + the row-advance tables, once
 constexpr uint32_t F_ROW = 256, F_UNIT = 32;       // bytes of BF16 one group / one lane emits per tile
 constexpr uint32_t F_SMALL_LIVE = 104;             // largest alphabet the CFN = 128 instance takes
@@ -111,14 +108,11 @@ __host__ __device__ constexpr int stream_warps(int cfn, bool crc)
     constexpr uint32_t top = F_SMEM_BASE + F_SMEM_DYN;
     if (cfn == 0) return F_WIDE_GROUPS / 4;
     if (cfn < 0) return F_SHARED_WARPS;
-    int w = (int)(((crc ? stream_crc_slice(top) : top) - F_SMEM_BASE) / (4u * stream_group_bytes(cfn)));
-#ifdef LMZ_STREAM_WARPS_MAX
-    if (crc && w > LMZ_STREAM_WARPS_MAX) w = LMZ_STREAM_WARPS_MAX;
-#endif
-    return w;
+    return (int)(((crc ? stream_crc_slice(top) : top) - F_SMEM_BASE) / (4u * stream_group_bytes(cfn)));
 }
 __host__ __device__ constexpr unsigned stream_groups(int cfn, int warps) { return warps * 4; }
-static_assert(F_LOGS != 3 || (stream_warps(128, true) == 19 && stream_warps(256, true) == 16), "shared memory budget");
+static_assert(stream_warps(128, true) == 19 && stream_warps(256, true) == 16 &&
+              stream_warps(128, false) == 23 && stream_warps(256, false) == 19, "shared memory budget");
 
 __device__ __forceinline__ void bulk_g2s_sa(uint32_t dst_sa, const void *src, uint32_t bytes,
                                             uint32_t bar_sa)

@@ -25,15 +25,14 @@ constexpr uint32_t WIDE_TAB_BYTES = PROB_SCALE * 4;
 // Bytes of per-stream tables, and the whole per-group footprint, by table layout.
 __host__ __device__ constexpr uint32_t table_bytes(int mode)
 {
-    return mode == T_NARROW ? PROB_SCALE + 1024 : mode == T_COMPACT ? 2048 : 0;
+    return mode == T_NARROW ? PROB_SCALE + 1024 : 0;
 }
 __host__ __device__ constexpr uint32_t group_bytes(int mode)
 {
     // ring | tables | staging | mbarriers | pad (stride = 8 banks mod 32)
     return RING + table_bytes(mode) + STAGE_BYTES + 32 + (mode == T_WIDE ? 32 : 96);
 }
-static_assert(group_bytes(T_NARROW) == 6432 && group_bytes(T_WIDE) == 1248 &&
-              group_bytes(T_COMPACT) == 3360, "per-group shared memory layout");
+static_assert(group_bytes(T_NARROW) == 6432 && group_bytes(T_WIDE) == 1248, "per-group shared memory layout");
 
 template <int MODE>
 __host__ __device__ constexpr uint32_t rans_smem_bytes(int warps)
@@ -49,10 +48,8 @@ __device__ __forceinline__ Tables group_tables(uint8_t *gp, uint32_t *wide_tab)
     if (MODE == T_NARROW) {
         tb.sym = gp + RING;
         tb.sf = reinterpret_cast<uint32_t *>(gp + RING + PROB_SCALE);
-    } else if (MODE == T_COMPACT) {
-        tb.l1 = reinterpret_cast<uint32_t *>(gp + RING);
-        tb.cf = reinterpret_cast<uint32_t *>(gp + RING + 1024);
     } else {
+        static_assert(MODE == T_NARROW || MODE == T_WIDE, "the other table layouts are decoded by k_stream");
         tb.wide = wide_tab;
     }
     return tb;
