@@ -295,6 +295,29 @@ def main():
     e2e_value = world * plain * a.steps / e2e_s / 1e9
     h2d_bytes = int(pd.h2d_bytes)
 
+    # ---- N > 1: the one archive partitioned over the ranks (no collective on the data path) ----
+    part = None
+    if world > 1:
+        from lmz_b200 import multi
+        sd = multi.ShardedDecoder(dec.archive, rank, world, checksum=not a.no_crc)
+        for _ in range(3):
+            sd.run()
+        sd.check()
+        barrier()
+        torch.cuda.synchronize()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        for _ in range(a.steps):
+            sd.run()
+        p1.record()
+        torch.cuda.synchronize()
+        t_all = torch.tensor([p0.elapsed_time(p1)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+        pms = float(t_all.item()) / a.steps
+        part = {"value": round(plain / (pms / 1e3) / 1e9, 2), "unit": "GB/s", "ms_per_step": round(pms, 3),
+                "what": f"one archive, chunks partitioned over {world} GPUs by output range, each into its own HBM"}
+        del sd
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -356,6 +379,7 @@ def main():
         "cpu_baseline": cpu_base,
         "batch_decode": batch,
         "default_layout": other,
+        "partitioned": part,
     }
     print(json.dumps(line))
     if world > 1:

@@ -90,9 +90,13 @@ class ShardedDecoder:
         self.archive = ar if isinstance(ar, fmt.Archive) else fmt.Archive(ar)
         self.rank, self.world = rank, world
         self.select, self.range = shard(self.archive, rank, world)
-        p = plan.build_plan(self.archive, select=self.select)
-        self.decoder = decode.ArchiveDecoder(self.archive, device=device, checksum=checksum, plan=p)
         r = self.archive.records
+        pay = None
+        if self.select.size:                 # upload only the stretch of the payload this rank reads
+            off = r["off"][self.select].astype(np.int64)
+            pay = (int(off.min()) & ~15, int((off + r["clen"][self.select]).max()))
+        p = plan.build_plan(self.archive, select=self.select, payload_range=pay)
+        self.decoder = decode.ArchiveDecoder(self.archive, device=device, checksum=checksum, plan=p)
         own = self.select[(r["dst"][self.select] >= self.range[0]) &
                           (r["dst"][self.select] < max(self.range[1], self.range[0] + 1))]
         self.owned_plain = int(r["rlen"][own].sum())
