@@ -179,7 +179,8 @@ __device__ __forceinline__ uint32_t stream_advance(uint32_t x, uint32_t l1_sa, u
         const uint32_t e1 = lds_u32((x & 0xff0u) | l1_sa);
         const uint32_t upto = 0xffffffffu >> ((~x) & 15u);             // bits 0 .. 16 + (slot & 15)
         const uint32_t pc = __popc(e1 & upto & 0xffff0000u);
-        e = lds_u32(((e1 & (4u * CFN - 4u)) | cf_sa) + (pc << 2));
+        constexpr uint32_t IDX = 4u * (uint32_t)(CFN > 0 ? CFN : 1) - 4u;   // byte offset field of level 1
+        e = lds_u32(((e1 & IDX) | cf_sa) + (pc << 2));
     }
     // f * (x >> 12) + slot - start  ==  x - (x >> 12) * (4096 - f) - start
     x2 = x - ((x >> PROB_BITS) * (e >> 20) + ((e >> 8) & 0xfffu));
