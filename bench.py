@@ -37,6 +37,13 @@ MODELS = {
     "llama-8layer": dict(layers=8, hidden=4096, ffn=14336, kv=1024, vocab=1024, shards=1),
     "llama-2layer": dict(layers=2, hidden=4096, ffn=14336, kv=1024, vocab=1024, shards=1),
     "llama-tiny": dict(layers=2, hidden=1024, ffn=3584, kv=256, vocab=8000, shards=2),
+    # other configurations (not the headline): each rank's own 1/8 tensor-parallel slice of a
+    # 70B BF16 model (17.6 GB) or of an FP32 XLM-R-large container, and a 3-checkpoint BF16
+    # delta chain on the Pythia-160m shapes
+    "llama-3-70b-tp8": dict(layers=80, hidden=8192, ffn=28672, kv=1024, vocab=128256, shards=4, tp=8),
+    "xlmr-large-f32-tp8": dict(kind="xlmr", layers=24, hidden=1024, ffn=4096, vocab=250002, tp=8),
+    "xlmr-large-f32": dict(kind="xlmr", layers=24, hidden=1024, ffn=4096, vocab=250002),
+    "pythia-160m-chain": dict(kind="chain", layers=12, hidden=768, ffn=3072, vocab=50304),
 }
 METRIC = "decoded plaintext GB/s per B200 & per box (1/2/4/8 GPU), byte-exact vs CPU"
 
@@ -62,20 +69,38 @@ def parse_args():
 
 def workload_name(a) -> str:
     cs = a.chunk_size or ((64 << 10) if a.layout == "mapped" else (8 << 20))
-    return f"{a.model} bf16 N(0,0.02) seed {a.seed}, lmz archive, {cs >> 10} KiB chunks"
+    dt = "f32" if MODELS[a.model].get("kind") == "xlmr" else "bf16"
+    return f"{a.model} {dt} N(0,0.02) seed {a.seed}, lmz archive, {cs >> 10} KiB chunks"
+
+
+def per_rank_archives(a) -> bool:
+    """Tensor-parallel configurations: every rank decodes an archive of its own."""
+    return MODELS[a.model].get("tp", 1) > 1
 
 
 def get_archive(a, rank: int, barrier) -> np.ndarray:
     """The benchmark archive as a numpy byte array, generated once per box and
     cached in /dev/shm (ranks other than 0 wait for rank 0)."""
     cs = a.chunk_size or None
-    key = f"lmzb200-{a.model}-{a.layout}-{a.chunk_size}-{a.seed}.lmz"
+    own = per_rank_archives(a)
+    seed = a.seed * 64 + rank if own else a.seed
+    key = f"lmzb200-{a.model}-{a.layout}-{a.chunk_size}-{seed}.lmz"
     cache = os.path.join("/dev/shm" if os.path.isdir("/dev/shm") else "/tmp", key)
-    if rank == 0 and (a.no_cache or not os.path.exists(cache)):
-        from oracle import bigwrite, synth
+    if (own or rank == 0) and (a.no_cache or not os.path.exists(cache)):
+        from oracle import archive as oa, bigwrite, synth
         t = time.time()
-        blob, _ = bigwrite.write_model_archive(synth.llama_spec(**MODELS[a.model]), seed=a.seed,
-                                               chunk_size=cs, mapped=a.layout == "mapped")
+        m = dict(MODELS[a.model])
+        kind = m.pop("kind", "llama")
+        mapped = a.layout == "mapped"
+        if kind == "chain":
+            files = synth.delta_chain_files(**m)
+            blob = np.frombuffer(oa.write_archive(
+                [(f"step{i}/model.safetensors", f) for i, f in enumerate(files)],
+                chunk_size=cs, mapped=mapped), dtype=np.uint8)
+        else:
+            spec = synth.xlmr_spec(**m) if kind == "xlmr" else synth.llama_spec(**m)
+            nproc = max(1, (os.cpu_count() or 1) // int(os.environ.get("LOCAL_WORLD_SIZE", "1"))) if own else None
+            blob, _ = bigwrite.write_model_archive(spec, seed=seed, chunk_size=cs, mapped=mapped, nproc=nproc)
         tmp = cache + f".{os.getpid()}"
         blob.tofile(tmp)
         os.replace(tmp, cache)
@@ -297,7 +322,7 @@ def main():
 
     # ---- N > 1: the one archive partitioned over the ranks (no collective on the data path) ----
     part = None
-    if world > 1:
+    if world > 1 and not per_rank_archives(a):
         from lmz_b200 import multi
         sd = multi.ShardedDecoder(dec.archive, rank, world, checksum=not a.no_crc)
         for _ in range(3):
@@ -362,7 +387,8 @@ def main():
         "data": "synthetic",
         "config": {"workload": workload_name(a), "plaintext_bytes": plain, "coded_bytes": coded,
                    "chunks": int(p.chunks.size), "rans_streams": int(p.stream_jobs.size + p.seg_jobs.size),
-                   "crc32": not a.no_crc, "per_gpu": "full replica",
+                   "crc32": not a.no_crc,
+                   "per_gpu": "its own tensor-parallel slice" if per_rank_archives(a) else "full replica",
                    "l2": f"no flush: each step streams {coded / 1e9:.1f} GB in and {plain / 1e9:.1f} GB out, far beyond the 126 MB L2"},
         "clocks": clk.summary(),
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s",

@@ -93,9 +93,22 @@ def perturbed_bf16(prev: np.ndarray, seed: int, frac: float = 0.3, sigma: float 
 BLOCK = 8 << 20
 
 
-def llama_spec(layers=32, hidden=4096, ffn=14336, kv=1024, vocab=128256, shards=4):
+def _tp_shape(name: str, shape, tp: int):
+    """One rank's slice of a weight under `tp`-way tensor parallelism: projections
+    into the hidden size (o_proj, down_proj, the encoder's output dense layers) are
+    cut along their input columns, every other matrix along its output rows (the
+    vocabulary padded up to a multiple of tp), 1-D tensors are replicated."""
+    if tp == 1 or len(shape) == 1:
+        return tuple(shape)
+    rows, cols = shape
+    if any(k in name for k in ("o_proj", "down_proj", "output.dense")):
+        return (rows, cols // tp)
+    return (-(-rows // tp), cols)
+
+
+def llama_spec(layers=32, hidden=4096, ffn=14336, kv=1024, vocab=128256, shards=4, tp=1):
     """Llama-architecture tensor list (BF16, untied embeddings) cut into `shards`
-    safetensors files by layer range."""
+    safetensors files by layer range; with tp > 1, one rank's tensor-parallel slice."""
     per = -(-layers // shards)
     out = []
     for s in range(shards):
@@ -108,8 +121,53 @@ def llama_spec(layers=32, hidden=4096, ffn=14336, kv=1024, vocab=128256, shards=
         if s == shards - 1:
             t.append(("model.norm.weight", "BF16", (hidden,)))
             t.append(("lm_head.weight", "BF16", (vocab, hidden)))
-        out.append(t)
+        out.append([(n, d, _tp_shape(n, sh, tp)) for n, d, sh in t])
     return out
+
+
+def xlmr_spec(layers=24, hidden=1024, ffn=4096, vocab=250002, tp=1):
+    """XLM-R-large-shaped FP32 encoder as one safetensors file (biases and layer
+    norms included); with tp > 1, one rank's tensor-parallel slice."""
+    t = [("embeddings.word_embeddings.weight", "F32", (vocab, hidden)),
+         ("embeddings.position_embeddings.weight", "F32", (514, hidden)),
+         ("embeddings.LayerNorm.weight", "F32", (hidden,))]
+    for li in range(layers):
+        pre = f"encoder.layer.{li}."
+        for nm, shape in (("attention.self.query", (hidden, hidden)), ("attention.self.key", (hidden, hidden)),
+                          ("attention.self.value", (hidden, hidden)), ("attention.output.dense", (hidden, hidden)),
+                          ("intermediate.dense", (ffn, hidden)), ("output.dense", (hidden, ffn))):
+            t.append((pre + nm + ".weight", "F32", shape))
+            t.append((pre + nm + ".bias", "F32", (shape[0],)))
+        t.append((pre + "attention.output.LayerNorm.weight", "F32", (hidden,)))
+        t.append((pre + "output.LayerNorm.weight", "F32", (hidden,)))
+    return [[(n, d, _tp_shape(n, sh, tp)) for n, d, sh in t]]
+
+
+def delta_chain_files(hidden=768, ffn=3072, vocab=50304, layers=12, checkpoints=3, seed=7000):
+    """Safetensors files of a Pythia-shaped BF16 checkpoint chain: checkpoint 0 from
+    N(0, 0.02); each later one is the previous plus N(0, 1e-4) noise on a random 30 %
+    of elements, rounded to BF16."""
+    h, f, v = hidden, ffn, vocab
+    names = [("embed.weight", (v, h))]
+    for li in range(layers):
+        names += [(f"l{li}.attn.qkv.weight", (3 * h, h)), (f"l{li}.attn.o.weight", (h, h)),
+                  (f"l{li}.mlp.up.weight", (f, h)), (f"l{li}.mlp.down.weight", (h, f)),
+                  (f"l{li}.ln.weight", (h,))]
+    names.append(("embed_out.weight", (v, h)))
+    files, prev = [], None
+    for ck in range(checkpoints):
+        tensors = []
+        for i, (name, shape) in enumerate(names):
+            if len(shape) == 1:
+                data = bf16_bytes(np.ones(shape, np.float32))
+            elif ck == 0:
+                data = normal_bf16(shape, seed + i)
+            else:
+                data = perturbed_bf16(prev[i], 100 * ck + i, frac=0.3, sigma=1e-4)
+            tensors.append((name, "BF16", shape, data))
+        prev = [t[3] for t in tensors]
+        files.append(safetensors_bytes(tensors))
+    return files
 
 
 _ESZ = {"BF16": 2, "F32": 4}

@@ -275,25 +275,7 @@ def test_pythia_shaped_delta_chain():
     FFN 3072, vocab 50304) at half width: checkpoint 0 from N(0, 0.02), each later one
     the previous plus N(0, 1e-4) on a random 30 % of elements; both later checkpoints
     are coded as deltas against checkpoint 0 (the earliest member holding the tensor)."""
-    h, f, v, layers = 384, 1536, 25152, 12
-    names = [("embed.weight", (v, h))]
-    for li in range(layers):
-        names += [(f"l{li}.attn.qkv.weight", (3 * h, h)), (f"l{li}.attn.o.weight", (h, h)),
-                  (f"l{li}.mlp.up.weight", (f, h)), (f"l{li}.mlp.down.weight", (h, f)),
-                  (f"l{li}.ln.weight", (h,))]
-    files, prev = [], None
-    for ck in range(3):
-        tensors = []
-        for i, (name, shape) in enumerate(names):
-            if len(shape) == 1:
-                data = synth.bf16_bytes(np.ones(shape, np.float32))
-            elif ck == 0:
-                data = synth.normal_bf16(shape, 7000 + i)
-            else:
-                data = synth.perturbed_bf16(prev[i], 100 * ck + i, frac=0.3, sigma=1e-4)
-            tensors.append((name, "BF16", shape, data))
-        prev = [t[3] for t in tensors]
-        files.append(synth.safetensors_bytes(tensors))
+    files = synth.delta_chain_files(hidden=384, ffn=1536, vocab=25152, layers=12)
     blob = oa.write_archive([(f"step{i}/model.safetensors", f) for i, f in enumerate(files)])
     dec = _roundtrip(blob, np.concatenate(files))
     recs = dec.archive.records
