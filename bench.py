@@ -351,20 +351,25 @@ def main():
     # dominant kernel: the one with the largest device time
     # algorithmic bytes of each kernel: what it must read plus what it must write
     fj = p.fused_jobs
-    fused_bytes = int(fj["src_len"].sum()) + 3 * int(fj["n"].sum())       # stream + plane in, 2n out
+    # element size of each fused job: BF16 chunks first, 4-byte-element chunks last
+    fes = np.full(fj.size, 2, dtype=np.int64)
+    fes[fj.size - p.n_fused_f32:] = 4
+    f_stored = int(((fes - 1) * fj["n"]).sum())        # stored planes read by the fused kernel
+    f_plain = int((fes * fj["n"]).sum())
+    fused_bytes = int(fj["src_len"].sum()) + f_stored + f_plain           # stream + planes in, plaintext out
     stream_bytes = int(p.stream_jobs["src_len"].sum() + p.stream_jobs["n"].sum())
-    fin_plain = plain - 2 * int(fj["n"].sum())
-    finish_bytes = int(coded - fj["src_len"].sum() - fj["n"].sum() - p.stream_jobs["src_len"].sum()
+    fin_plain = plain - f_plain
+    finish_bytes = int(coded - fj["src_len"].sum() - f_stored - p.stream_jobs["src_len"].sum()
                        + p.stream_jobs["n"].sum() + fin_plain + p.base_bytes)
     kbytes = {"stream_decode": stream_bytes, "finish": finish_bytes, "fused": fused_bytes}
     kname = {"stream_decode": "k_rans / k_stream<bytes>", "finish": "k_finish",
-             "fused": "k_stream<bf16>"}
+             "fused": "k_stream<f32>" if p.n_fused_f32 * 2 > fj.size else "k_stream<bf16>"}
     dom = max(kbytes, key=lambda k: phase_ms[k])
     dom_bytes = kbytes[dom]
     achieved = dom_bytes / (phase_ms[dom] / 1e3) / 1e9
     whole = (coded + plain + p.base_bytes) / (ms / a.steps / 1e3) / 1e9
     traffic = None
-    if dom == "fused":
+    if dom == "fused" and not p.n_fused_f32:
         # DRAM bytes of one launch, scaled from the committed ncu capture of a smaller
         # archive of the same chunks (traffic is proportional to the chunks processed)
         try:

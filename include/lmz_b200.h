@@ -183,8 +183,11 @@ typedef struct lmz_decode_plan {
     void *d_seg_jobs;           /* 8 per conditioned chunk, sized on the device */
     void *d_stream_status;      /* uint32 per stream job */
     void *d_seg_status;         /* uint32 per segment job */
-    const void *d_fused_jobs;   /* BF16 chunks decoded, merged and checksummed by one kernel; the
-                                 * first n_fused_small have at most 104 live symbols */
+    const void *d_fused_jobs;   /* chunks decoded, merged and checksummed by one kernel: BF16 chunks
+                                 * (coded exponent plane, stored mantissa plane), the first
+                                 * n_fused_small of them with at most 104 live symbols; then the
+                                 * n_fused_f32 chunks of 4-byte elements (coded top byte plane, three
+                                 * stored planes), the first n_fused_f32_small of them small likewise */
     void *d_fused_status;       /* uint32 per fused job */
     const void *d_chunks;       /* chunk jobs, ordered: pass 1 cond, pass 1 plain, fused, pass 2 cond, pass 2 plain */
     const void *d_piece_chunk;  /* uint32 per piece: its chunk */
@@ -201,9 +204,11 @@ typedef struct lmz_decode_plan {
     uint32_t n_stream_jobs, n_seg_jobs, n_chunks, n_pieces, n_cond, n_cond_pieces, n_fused;
     uint32_t n_fused_small;     /* leading fused jobs whose streams have small alphabets (see
                                  * lmz_host_alphabet_sizes); they take the denser kernel instance */
+    uint32_t n_fused_f32;       /* trailing fused jobs that are 4-byte-element chunks (counted in n_fused) */
+    uint32_t n_fused_f32_small; /* the first of those, with small alphabets */
     uint32_t piece_split[6];    /* piece-id boundaries of the five chunk groups */
     uint32_t phases;            /* 0 = everything; else bit 0 stream decode, bit 1 conditioned-chunk
-                                 * kernels, bit 2 finish, bit 3 verdicts, bit 4 fused BF16 chunks
+                                 * kernels, bit 2 finish, bit 3 verdicts, bit 4 fused chunks
                                  * (to time one phase alone) */
 } lmz_decode_plan;
 

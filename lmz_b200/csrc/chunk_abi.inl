@@ -126,7 +126,8 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
 
     if (p->d_any_bad && (ph & 1u)) CK("memset any_bad", cudaMemsetAsync(p->d_any_bad, 0, 4, cs));
 
-    // 0. BF16 chunks with a coded exponent plane and a stored sign/mantissa plane:
+    // 0. BF16 chunks with a coded exponent plane and a stored sign/mantissa plane, and
+    //     4-byte-element chunks with a coded top plane and three stored planes:
     //     decode, merge, write and checksum in one kernel
     SideStream *side = nullptr;
     const bool other_work = p->n_stream_jobs || p->n_cond || p->piece_split[2] > p->piece_split[0] ||
@@ -155,17 +156,28 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         sa.any_bad = (uint32_t *)p->d_any_bad;
         sa.piece_crc = (uint32_t *)p->d_piece_crc;
         sa.tabs = (const CrcTables *)p->d_crc_tables;
-        // small alphabets first (denser instance), then the rest
-        const uint32_t nsmall = p->n_fused_small < p->n_fused ? p->n_fused_small : p->n_fused;
+        // BF16 chunks, then chunks of 4-byte elements; in each, small alphabets first
+        // (denser instance), then the rest
+        if (p->n_fused_f32 > p->n_fused) return fail_msg(LMZ_GPU_EUNSUPPORTED, "n_fused_f32 exceeds n_fused");
+        const uint32_t nbf = p->n_fused - p->n_fused_f32;
+        const uint32_t nsmall = p->n_fused_small < nbf ? p->n_fused_small : nbf;
+        const uint32_t nsmall4 = p->n_fused_f32_small < p->n_fused_f32 ? p->n_fused_f32_small : p->n_fused_f32;
+        auto part = [&](uint32_t cnt) { sa.jobs += sa.njobs; sa.status += sa.njobs; sa.njobs = cnt; };
         sa.njobs = nsmall;
         rc = p->d_piece_crc ? launch_stream<SINK_BF16, true, 128>(sa, fs)
                             : launch_stream<SINK_BF16, false, 128>(sa, fs);
         if (rc) return rc;
-        sa.jobs += nsmall;
-        sa.status += nsmall;
-        sa.njobs = p->n_fused - nsmall;
+        part(nbf - nsmall);
         rc = p->d_piece_crc ? launch_stream<SINK_BF16, true, 256>(sa, fs)
                             : launch_stream<SINK_BF16, false, 256>(sa, fs);
+        if (rc) return rc;
+        part(nsmall4);
+        rc = p->d_piece_crc ? launch_stream<SINK_F32, true, 128>(sa, fs)
+                            : launch_stream<SINK_F32, false, 128>(sa, fs);
+        if (rc) return rc;
+        part(p->n_fused_f32 - nsmall4);
+        rc = p->d_piece_crc ? launch_stream<SINK_F32, true, 256>(sa, fs)
+                            : launch_stream<SINK_F32, false, 256>(sa, fs);
         if (rc) return rc;
         if (side) CK("cudaEventRecord", cudaEventRecord(side->join, side->stream));
     }

@@ -39,6 +39,8 @@ struct CrcTables {
     uint32_t adv_row[4][256]; // advance by a 256-byte group row minus one 32-byte lane unit
     uint32_t lane_mul8[8];    // x^(8 * 32 * (7 - k)): lane k's unit to the group row's end
     uint32_t run_mul[256];    // x^(8 * 256 * (255 - t)): thread t's 256-byte run to the piece's end
+    uint32_t adv_row4[4][256];// advance by a 512-byte group row minus one 64-byte lane unit (4-byte elements)
+    uint32_t lane_mul8_4[8];  // x^(8 * 64 * (7 - k))
 };
 
 // Rows of the piece layout: 256 threads x 16 bytes.
@@ -91,6 +93,10 @@ inline void crc_build_tables(CrcTables &t)
         for (uint32_t i = 0; i < 256; i++) t.adv_row[j][i] = crc_mulmod(adv2, i << (8 * j));
     for (uint32_t k = 0; k < 8; k++) t.lane_mul8[k] = crc_xpow(t.x2, 8ull * 32 * (7 - k));
     for (uint32_t th = 0; th < 256; th++) t.run_mul[th] = crc_xpow(t.x2, 8ull * 256 * (255 - th));
+    uint32_t adv4 = crc_xpow(t.x2, 8ull * (512 - 64));
+    for (int j = 0; j < 4; j++)
+        for (uint32_t i = 0; i < 256; i++) t.adv_row4[j][i] = crc_mulmod(adv4, i << (8 * j));
+    for (uint32_t k = 0; k < 8; k++) t.lane_mul8_4[k] = crc_xpow(t.x2, 8ull * 64 * (7 - k));
 }
 
 // Feed one little-endian 32-bit word: four table lookups.

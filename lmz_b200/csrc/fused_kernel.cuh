@@ -7,6 +7,10 @@
 //               128 stored bytes (lmz/native/lmzcore.c:439-447), written once as
 //               256 bytes of BF16, and folded into the chunk's CRC-32 -- no
 //               scratch plane, no second pass
+//   SINK_F32    a CODEC_SPLIT chunk of 4-byte elements whose top byte plane is rANS
+//               and whose three lower planes are stored back to back: each tile is
+//               interleaved with 3 x 128 stored bytes (lmz/native/lmzcore.c:289-347),
+//               written once as 512 bytes and folded into the chunk's CRC-32
 //
 // Differences from k_rans that buy instructions and occupancy:
 //   * shared memory is laid out by kind (all level-1 tables, all level-2 tables,
@@ -52,15 +56,16 @@ constexpr uint32_t F_LOGS = 3;                     // CRC slice tables replicate
 constexpr uint32_t F_CRC_BYTES = (4096u << F_LOGS) + 4096u;   // + the row-advance tables, once
 constexpr uint32_t F_ROW = 256, F_UNIT = 32;       // bytes of BF16 one group / one lane emits per tile
 constexpr uint32_t F_SMALL_LIVE = 104;             // largest alphabet the CFN = 128 instance takes
-enum : int { SINK_BYTES = 0, SINK_BF16 = 1 };
+enum : int { SINK_BYTES = 0, SINK_BF16 = 1, SINK_F32 = 2 };
 
 struct FusedJob {
     uint64_t src_off;    // rANS stream, bytes from the source base
-    uint64_t mant_off;   // SINK_BF16: the stored sign/mantissa plane, bytes from the source base
+    uint64_t mant_off;   // SINK_BF16: the stored sign/mantissa plane, bytes from the source base;
+                         // SINK_F32: stored plane 0, planes 1 and 2 follow at n and 2n
     uint64_t dst_off;    // first output byte
     uint32_t src_len;
-    uint32_t n;          // symbols (= BF16 elements)
-    uint32_t piece0;     // SINK_BF16: first piece id of the chunk (for piece_crc)
+    uint32_t n;          // symbols (= elements)
+    uint32_t piece0;     // first piece id of the chunk (for piece_crc)
     uint32_t flags;
 };
 static_assert(sizeof(FusedJob) == 40, "FusedJob layout is shared with the host");
@@ -84,6 +89,11 @@ struct StreamArgs {
     const uint32_t *order;
     const uint32_t *count;
     uint32_t order_from_back;
+    // Streams per CTA (a multiple of 4, at most the instance's capacity; 0 = the capacity):
+    // the launcher spreads a launch evenly over its waves of CTAs, so that a launch of 3.03
+    // waves runs as four waves of three quarters the streams instead of three full waves
+    // and one nearly empty one, and a small launch uses every SM.
+    uint32_t per_cta;
 };
 
 constexpr uint32_t F_WIDE_BYTES = PROB_SCALE * 4;   // CFN = 0: one 16 KiB slot -> entry table per stream
@@ -278,13 +288,14 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     ring.bars = reinterpret_cast<uint64_t *>(gen(bars_0)) + gi * NSL;
 
     // ---- this group's stream ------------------------------------------------------
-    const uint32_t idx = blockIdx.x * G + gi;
+    const uint32_t per_cta = a.per_cta ? a.per_cta : G;
+    const uint32_t idx = blockIdx.x * per_cta + gi;
     uint32_t limit = a.njobs;
     if (a.count) {
         limit = *a.count;
-        if (blockIdx.x * G >= limit) return;          // the whole CTA: nothing of this class is left
+        if (blockIdx.x * per_cta >= limit) return;    // the whole CTA: nothing of this class is left
     }
-    const bool have = idx < limit;
+    const bool have = gi < per_cta && idx < limit;
     const uint32_t job = (have && a.order) ? a.order[a.order_from_back ? a.njobs - 1 - idx : idx] : idx;
     uint64_t soff = 0, doff = 0, moff = 0;
     uint32_t slen = 0, n = 0, piece0 = 0;
@@ -319,7 +330,8 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         uint32_t *ts = reinterpret_cast<uint32_t *>(gen(tab0)), *ta = reinterpret_cast<uint32_t *>(gen(adv0));
         for (uint32_t i = threadIdx.x; i < 1024u << F_LOGS; i += WARPS * 32)
             ts[i] = (&a.tabs->slice[0][0])[i >> F_LOGS];
-        for (uint32_t i = threadIdx.x; i < 1024u; i += WARPS * 32) ta[i] = (&a.tabs->adv_row[0][0])[i];
+        const uint32_t *row_adv = SINK == SINK_F32 ? &a.tabs->adv_row4[0][0] : &a.tabs->adv_row[0][0];
+        for (uint32_t i = threadIdx.x; i < 1024u; i += WARPS * 32) ta[i] = row_adv[i];
     }
     __syncthreads();
 
@@ -423,6 +435,19 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
             ring.issue(cursor, k == 0);
             ring.require(cursor + 2 * TS);         // every lane sees the completion itself
         }
+        // SINK_F32: the tile's stored bytes are requested before the decode, which hides
+        // their latency (lane k: elements 16k .. 16k+15 of each of the three planes)
+        uint32_t pr[SINK == SINK_F32 ? 3 : 1][5];
+        if (SINK == SINK_F32) {
+            const bool mine = rem > 16 * k;
+#pragma unroll
+            for (int j = 0; j < 3; j++) {
+                const uint8_t *pp = a.src + moff + (size_t)j * n + done + 16 * k;
+                const uint32_t *pq = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(pp) & ~uintptr_t(3));
+#pragma unroll
+                for (int i = 0; i < 5; i++) pr[j][i] = mine ? __ldg(pq + i) : 0u;
+            }
+        }
         const uint32_t caddr0 = ring.sa + (cursor & (RINGB - 1));
         uint32_t caddr = caddr0;
         // (lanes that never had a stream run along in full tiles; nothing of theirs is kept)
@@ -487,8 +512,77 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
             continue;
         }
 
-        // ---- SINK_BF16: merge with the stored plane, write, checksum ------------------
         const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w};
+        if (SINK == SINK_F32) {
+            // ---- interleave with the three stored planes, write, checksum ------------
+            const uint32_t ve = rem > 16 * k ? min(rem - 16 * k, 16u) : 0u;   // valid elements of this lane
+            uint32_t pw[3][4];
+#pragma unroll
+            for (int j = 0; j < 3; j++) {
+                const uint32_t sh = (uint32_t)((reinterpret_cast<uintptr_t>(a.src) + moff + (size_t)j * n + done) & 3u) * 8u;
+#pragma unroll
+                for (int h = 0; h < 4; h++) pw[j][h] = __funnelshift_r(pr[j][h], pr[j][h + 1], sh);
+            }
+            uint32_t w[16];
+#pragma unroll
+            for (int h = 0; h < 4; h++) {
+                const uint32_t u0 = __byte_perm(pw[0][h], pw[1][h], 0x5140), u1 = __byte_perm(pw[0][h], pw[1][h], 0x7362);
+                const uint32_t v0 = __byte_perm(pw[2][h], ew[h], 0x5140), v1 = __byte_perm(pw[2][h], ew[h], 0x7362);
+                w[4 * h + 0] = __byte_perm(u0, v0, 0x5410); w[4 * h + 1] = __byte_perm(u0, v0, 0x7632);
+                w[4 * h + 2] = __byte_perm(u1, v1, 0x5410); w[4 * h + 3] = __byte_perm(u1, v1, 0x7632);
+            }
+            uint8_t *d = out + (size_t)done * 4 + k * 64;
+            if (ve == 16) {
+                if (al == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        reinterpret_cast<uint4 *>(d)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                } else if ((al & 7) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) reinterpret_cast<uint2 *>(d)[i] = make_uint2(w[2 * i], w[2 * i + 1]);
+                } else if ((al & 3) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) reinterpret_cast<uint32_t *>(d)[i] = w[i];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; i++) d[i] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+                }
+            } else {
+                // whole elements only: a word is either kept or zero
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    if ((uint32_t)i < ve) {
+                        if ((al & 3) == 0) reinterpret_cast<uint32_t *>(d)[i] = w[i];
+                        else
+                            for (int b = 0; b < 4; b++) d[4 * i + b] = (uint8_t)(w[i] >> (8 * b));
+                    } else {
+                        w[i] = 0u;
+                    }
+                }
+            }
+            if (CRC) {
+                acc = crc_advance<0>(tla, acc);
+#pragma unroll
+                for (int i = 0; i < 16; i++) acc = crc_feed4<F_LOGS>(tls, acc ^ w[i]);
+                if ((t & 127u) == 127u || t + 1 == my_tiles) {
+                    // close the 64 KiB piece: lane units -> row end, XOR over the group
+                    uint32_t v = crc_mulmod(a.tabs->lane_mul8_4[k], acc);
+                    v ^= __shfl_xor_sync(grp_mask, v, 1);
+                    v ^= __shfl_xor_sync(grp_mask, v, 2);
+                    v ^= __shfl_xor_sync(grp_mask, v, 4);
+                    if (k == 0) {
+                        const uint32_t p = t >> 7, rows = (t & 127u) + 1;
+                        const uint32_t plen = min(PIECE_BYTES, 4 * n - p * PIECE_BYTES);
+                        if (rows * 512u != plen) v = crc_unshift(a.tabs->x2, v, rows * 512u - plen);
+                        a.piece_crc[piece0 + p] = v;
+                    }
+                    acc = 0;
+                }
+            }
+            continue;
+        }
+
+        // ---- SINK_BF16: merge with the stored plane, write, checksum ------------------
         uint32_t w[8];
 #pragma unroll
         for (int h = 0; h < 4; h++)

@@ -108,10 +108,13 @@ static int stream_smem_ok()
 
 // CFN = 128 is for streams the caller knows to have at most F_SMALL_LIVE live symbols;
 // CFN = 0 is the per-stream wide table (12 streams per SM), CFN = -1 one wide table per CTA.
+static int sm_count(int *out);
+
 template <int SINK, bool CRC, int CFN>
-static int launch_stream(const StreamArgs &a, cudaStream_t cs)
+static int launch_stream(const StreamArgs &a0, cudaStream_t cs)
 {
-    if (a.njobs == 0) return LMZ_GPU_OK;
+    if (a0.njobs == 0) return LMZ_GPU_OK;
+    StreamArgs a = a0;
     constexpr int WARPS = stream_warps(CFN, CRC);
     static bool done[64];
     int rc = stream_smem_ok();
@@ -121,7 +124,20 @@ static int launch_stream(const StreamArgs &a, cudaStream_t cs)
     rc = opt_in_smem(k_stream<SINK, CRC, WARPS, CFN>, shm, done);
     if (rc) return rc;
     constexpr unsigned groups = stream_groups(CFN, WARPS);
-    unsigned blocks = (a.njobs + groups - 1) / groups;
+    unsigned per = groups;
+    if (!a.count) {
+        // as many waves of CTAs as full CTAs would need, the streams spread evenly over them
+        int sms = 0;
+        rc = sm_count(&sms);
+        if (rc) return rc;
+        const unsigned slots = (unsigned)sms * (CFN < 0 ? 2u : 1u);
+        const unsigned waves = (a.njobs + slots * groups - 1) / (slots * groups);
+        per = (a.njobs + waves * slots - 1) / (waves * slots);
+        per = (per + 3u) & ~3u;
+        if (per > groups) per = groups;
+    }
+    a.per_cta = per;
+    unsigned blocks = (a.njobs + per - 1) / per;
     k_stream<SINK, CRC, WARPS, CFN><<<blocks, WARPS * 32, shm, cs>>>(a);
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return fail_cuda("launch k_stream", le);
@@ -131,7 +147,6 @@ static int launch_stream(const StreamArgs &a, cudaStream_t cs)
 // `force_mode` < 0 picks by batch size.
 static int g_force_table_mode = -1;
 
-static int sm_count(int *out);
 
 static StreamArgs as_stream_args(const RansArgs &a)
 {

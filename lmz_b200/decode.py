@@ -54,7 +54,7 @@ class ArchiveDecoder:
     uint8 tensor holding `plan.payload` followed by `gpu.pad_bytes()` of slack."""
 
     def __init__(self, ar, device=None, checksum: bool = True, out=None, plan=None,
-                 fuse: bool = True):
+                 fuse=True):
         import torch
 
         lib = gpu.library()
@@ -114,6 +114,7 @@ class ArchiveDecoder:
         c.d_fused_jobs, c.d_fused_status = self.d_fused_jobs.data_ptr(), self.d_fused_status.data_ptr()
         c.n_fused = p.fused_jobs.size
         c.n_fused_small = p.n_fused_small
+        c.n_fused_f32, c.n_fused_f32_small = p.n_fused_f32, p.n_fused_f32_small
         c.d_chunks, c.d_piece_chunk = self.d_chunks.data_ptr(), self.d_piece_chunk.data_ptr()
         c.d_cond_jobs, c.d_cond_state = self.d_cond_jobs.data_ptr(), self.d_cond_state.data_ptr()
         c.d_cond_pieces = self.d_cond_pieces.data_ptr()
@@ -131,7 +132,9 @@ class ArchiveDecoder:
         # kernels launched by one run(): stream decode, 3 cond kernels + segment decode,
         # up to four finish launches, the verdict kernel
         self.launches_per_run = (1 if p.stream_jobs.size else 0) + (4 if ncond else 0) + \
-            (1 if p.n_fused_small else 0) + (1 if p.fused_jobs.size > p.n_fused_small else 0) + \
+            (1 if p.n_fused_small else 0) + \
+            (1 if p.fused_jobs.size - p.n_fused_f32 > p.n_fused_small else 0) + \
+            (1 if p.n_fused_f32_small else 0) + (1 if p.n_fused_f32 > p.n_fused_f32_small else 0) + \
             int(sum(p.piece_split[i + 1] > p.piece_split[i] for i in (0, 1, 3, 4))) + 1
 
     def upload(self, pinned=None, non_blocking: bool = False):

@@ -63,8 +63,10 @@ class Plan:
     piece_split: np.ndarray        # 6 boundaries: p1 cond, p1 plain, fused, p2 cond, p2 plain
     cond_jobs: np.ndarray
     cond_pieces: np.ndarray
-    fused_jobs: np.ndarray = field(default=None)
-    n_fused_small: int = 0         # leading fused jobs with at most SMALL_LIVE live symbols
+    fused_jobs: np.ndarray = field(default=None)   # BF16 chunks, then 4-byte-element chunks
+    n_fused_small: int = 0         # leading BF16 fused jobs with at most SMALL_LIVE live symbols
+    n_fused_f32: int = 0           # trailing fused jobs that are 4-byte-element chunks
+    n_fused_f32_small: int = 0     # the first of those, with at most SMALL_LIVE live symbols
     stream_owner: np.ndarray = field(default=None)   # record index of each stream job
     coded_bytes: int = 0           # sum of clen: algorithmic bytes read
     base_bytes: int = 0            # bytes of delta bases read back
@@ -78,6 +80,10 @@ def _gather(blob: np.ndarray, offs: np.ndarray, width: int) -> np.ndarray:
     return blob[offs[:, None] + np.arange(width, dtype=np.int64)[None, :]]
 
 
+# Fewest 4-byte-element chunks worth the fused kernel: a launch that cannot fill the SMs'
+# stream slots (148 x 76) is bound by each warp's own instruction stream, and there the
+# two-pass path (lean stream kernel, then the merge kernel) measured faster.
+FUSE_F32_MIN = 8192
 SMALL_LIVE = 104       # largest alphabet the denser fused-kernel instance takes (csrc/fused_kernel.cuh)
 
 
@@ -102,10 +108,12 @@ def _align16(x):
     return (x + 15) & ~15
 
 
-def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=None,
+def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
                out_range=None) -> Plan:
     """`fuse` routes BF16 chunks whose exponent plane is rANS and whose sign/mantissa
-    plane is stored to the fused decode+merge+checksum kernel (no scratch plane).
+    plane is stored to the fused decode+merge+checksum kernel (no scratch plane), and
+    4-byte-element chunks whose top byte plane alone is coded likewise when there are
+    at least FUSE_F32_MIN of them (`fuse="all"`: however few).
     `select` (record indices) plans only those chunks -- one rank's share of a
     partitioned decode, sources of its refs and deltas included by the caller.
     `payload_range` = (lo, hi) uploads only those archive bytes (every selected chunk's
@@ -250,6 +258,15 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=No
                 fused[fi] = True
                 f_src[fi], f_len[fi], f_mant[fi] = starts[fz, 0], lens[fz, 0], starts[fz, 1]
                 stored = stored | fz[:, None]          # no scratch stream for these
+            if fuse and cid == fmt.CODEC_SPLIT and npl == 4:
+                # top byte plane coded, the three lower planes stored (and then back to back)
+                fz = ~pass2[i] & ~stored[:, 3] & stored[:, :3].all(axis=1) & (nelem > 0)
+                if fuse != "all" and int(fz.sum()) < FUSE_F32_MIN:
+                    fz[:] = False
+                fi = i[fz]
+                fused[fi] = True
+                f_src[fi], f_len[fi], f_mant[fi] = starts[fz, 3], lens[fz, 3], starts[fz, 0]
+                stored = stored | fz[:, None]
             rr, pp = np.nonzero(~stored)
             add_streams(starts[rr, pp], lens[rr, pp], nelem[rr], i[rr], pp)
             np.bitwise_or.at(scratch_mask, i[rr], (1 << pp).astype(np.uint8))
@@ -364,12 +381,14 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=No
     whole = f_len[corder[fpos]] >= 548              # table + states present (else the kernel rejects it)
     small = np.zeros(fpos.size, dtype=bool)
     small[whole] = _alphabet_sizes(blob, f_src[corder[fpos]][whole]) <= SMALL_LIVE
-    fpos = np.concatenate([fpos[small], fpos[~small]])      # ... small alphabets first
+    wide4 = esize[corder[fpos]] == 4                # ... BF16 before 4-byte elements,
+    fpos = np.concatenate([fpos[~wide4 & small], fpos[~wide4 & ~small],     # small alphabets first
+                           fpos[wide4 & small], fpos[wide4 & ~small]])
     fused_jobs = np.zeros(fpos.size, dtype=FUSED_JOB)
     frec = corder[fpos]
     fused_jobs["src_off"], fused_jobs["src_len"] = f_src[frec], f_len[frec]
     fused_jobs["mant_off"], fused_jobs["dst_off"] = f_mant[frec], dst[frec]
-    fused_jobs["n"], fused_jobs["piece0"] = rlen[frec] // 2, piece0[fpos]
+    fused_jobs["n"], fused_jobs["piece0"] = rlen[frec] // esize[frec], piece0[fpos]
 
     payload = blob[:hi - lo]
     extra = np.concatenate(extras) if extras else np.zeros(0, dtype=np.uint8)
@@ -377,7 +396,8 @@ def build_plan(ar: fmt.Archive, fuse: bool = True, select=None, payload_range=No
                 stream_jobs=stream_jobs, seg_jobs=seg_jobs, chunks=chunks,
                 piece_chunk=piece_chunk, piece_split=split, cond_jobs=cond,
                 cond_pieces=cond_pieces, stream_owner=s_owner[order], fused_jobs=fused_jobs,
-                n_fused_small=int(small.sum()),
+                n_fused_small=int((~wide4 & small).sum()), n_fused_f32=int(wide4.sum()),
+                n_fused_f32_small=int((wide4 & small).sum()),
                 coded_bytes=int(clen.sum()), base_bytes=int(rlen[is_delta].sum()))
 
 

@@ -11,10 +11,10 @@ from oracle import archive as oa, synth
 pytestmark = pytest.mark.gpu
 
 
-def _roundtrip(blob, source, checksum=True):
+def _roundtrip(blob, source, checksum=True, fuse=True):
     import zlib
     from lmz_b200 import decode
-    dec = decode.ArchiveDecoder(blob, checksum=checksum)
+    dec = decode.ArchiveDecoder(blob, checksum=checksum, fuse=fuse)
     dec.run()
     dec.check()
     got = dec.output.cpu().numpy()
@@ -82,6 +82,42 @@ def test_byte_plane_splits(dtype, n):
     src = _float_file(dtype, n, 3)
     for kw in (dict(), dict(mapped=True)):
         _roundtrip(oa.write_archive([("f.safetensors", src)], **kw), src)
+
+
+@pytest.mark.parametrize("n,pad", [(1 << 20, 0), (70001, 0), (16384 * 9 + 5, 3), (3, 1), (200000, 2)])
+def test_fp32_chunks_take_the_fused_kernel(n, pad):
+    """FP32 weights of N(0, 0.02): the top byte plane is rANS-coded and the three lower
+    planes are stored, so the chunks go to the fused decode + interleave + checksum
+    kernel; `pad` shifts the data area to every 4-byte phase of the 16-byte store, and
+    the same archive is decoded with the two-pass path and without checksums too."""
+    from lmz_b200 import archive, decode, plan
+    rng = np.random.default_rng(n)
+    w = (rng.standard_normal(n) * 0.02).astype("<f4")
+    src = synth.safetensors_bytes([("lead", "F32", (pad,), np.zeros(pad, "<f4").view(np.uint8)),
+                                   ("w", "F32", (n,), w.view(np.uint8))])
+    for kw in (dict(), dict(mapped=True)):
+        blob = oa.write_archive([("f.safetensors", src)], **kw)
+        p = plan.build_plan(archive.Archive(blob), fuse="all")
+        if n >= 70001:
+            assert p.n_fused_f32 > 0 and p.n_fused_f32 == p.fused_jobs.size, (p.n_fused_f32, p.fused_jobs.size)
+        assert plan.build_plan(archive.Archive(blob)).n_fused_f32 == 0       # too few to pay
+        _roundtrip(blob, src, fuse="all")
+        _roundtrip(blob, src, checksum=False, fuse="all")
+        two_pass = decode.ArchiveDecoder(blob, fuse=False)
+        assert two_pass.plan.fused_jobs.size == 0
+        two_pass.run()
+        two_pass.check()
+        assert (two_pass.output.cpu().numpy() == src).all()
+
+
+def test_mixed_bf16_and_fp32_members_share_one_fused_launch_list(shard):
+    rng = np.random.default_rng(4)
+    f32 = synth.safetensors_bytes([("w", "F32", (300000,), (rng.standard_normal(300000) * 0.02).astype("<f4").view(np.uint8))])
+    from lmz_b200 import archive, plan
+    blob = oa.write_archive([("a.safetensors", shard), ("b.safetensors", f32)], mapped=True)
+    p = plan.build_plan(archive.Archive(blob), fuse="all")
+    assert 0 < p.n_fused_f32 < p.fused_jobs.size
+    _roundtrip(blob, np.concatenate([shard, f32]), fuse="all")
 
 
 def test_delta_chain_and_refs():

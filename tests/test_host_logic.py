@@ -122,6 +122,29 @@ def test_reader_and_planner_classify_every_layout(shard):
         assert ("m.safetensors", "model.embed_tokens.weight") in idx
 
 
+def test_planner_lists_fp32_chunks_after_bf16_in_the_fused_jobs(shard):
+    """4-byte-element chunks whose top plane alone is coded are fused jobs of their own
+    kind: listed after the BF16 ones, `mant_off` at stored plane 0 with planes 1 and 2
+    following at n and 2n, the stream at plane 3, n = rlen / 4."""
+    from lmz_b200 import archive, plan
+    rng = np.random.default_rng(8)
+    f32 = synth.safetensors_bytes([("w", "F32", (50000,), (rng.standard_normal(50000) * 0.02).astype("<f4").view(np.uint8))])
+    blob = oa.write_archive([("a.safetensors", shard), ("b.safetensors", f32)], mapped=True)
+    ar = archive.Archive(blob)
+    p = plan.build_plan(ar, fuse="all")
+    assert plan.build_plan(ar).n_fused_f32 == 0        # fewer than FUSE_F32_MIN: two passes
+    nf = p.n_fused_f32
+    assert 0 < nf < p.fused_jobs.size and p.n_fused_f32_small <= nf
+    assert p.n_fused_small <= p.fused_jobs.size - nf
+    for j in p.fused_jobs[-nf:]:
+        c = p.chunks[np.nonzero(p.chunks["piece0"] == j["piece0"])[0][-1]]
+        assert int(c["esize"]) == 4 and int(j["n"]) * 4 == int(c["rlen"])
+        po = c["plane_off"]
+        assert int(j["mant_off"]) == int(po[0]) and int(po[1]) == int(po[0]) + int(j["n"])
+        assert int(po[2]) == int(po[0]) + 2 * int(j["n"]) and int(j["src_off"]) == int(po[3])
+    assert plan.build_plan(ar, fuse=False).fused_jobs.size == 0
+
+
 def test_reader_rejects_damage(shard):
     from lmz_b200 import archive
     blob = oa.write_archive([("m.safetensors", shard)], mapped=True)
