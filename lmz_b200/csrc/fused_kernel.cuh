@@ -121,6 +121,8 @@ __host__ __device__ constexpr int stream_warps(int cfn, bool crc)
     return (int)(((crc ? stream_crc_slice(top) : top) - F_SMEM_BASE) / (4u * stream_group_bytes(cfn)));
 }
 __host__ __device__ constexpr unsigned stream_groups(int cfn, int warps) { return warps * 4; }
+static_assert(F_LOGS == 3 && stream_crc_slice(F_SMEM_BASE + F_SMEM_DYN) % 32768u == 0,
+              "crc_feed4q ORs a 32 KiB table's offsets onto its base");
 static_assert(stream_warps(128, true) == 19 && stream_warps(256, true) == 16 &&
               stream_warps(128, false) == 23 && stream_warps(256, false) == 19, "shared memory budget");
 
@@ -239,6 +241,22 @@ __device__ __forceinline__ uint32_t stream_step4(uint32_t &x, uint32_t &hist, ui
     return e;
 }
 
+// CRC slice tables of k_stream, laid out so that the warp's 32 lookups of one load never
+// share a bank: entry i of table j, copy r sits at word 32 i + 8 j + r -- a table owns a
+// quarter of the banks and each of its eight copies one bank of that quarter.  Lane k of
+// group g uses copy k, and the groups take the four bytes of a state word in rotated order
+// (group g starts at byte g), so in each of the four loads the groups are in four different
+// tables, i.e. bank quarters.  b[i] = table base + this lane's word for load i; rot = 8 g.
+struct CrcQuarters {
+    uint32_t b[4], rot;
+};
+__device__ __forceinline__ uint32_t crc_feed4q(const CrcQuarters &q, uint32_t s)
+{
+    const uint32_t r = __funnelshift_r(s, s, q.rot);     // byte i of r = byte (i + g) & 3 of s
+    return lds_u32(((r << 7) & 0x7f80u) | q.b[0]) ^ lds_u32(((r >> 1) & 0x7f80u) | q.b[1]) ^
+           lds_u32(((r >> 9) & 0x7f80u) | q.b[2]) ^ lds_u32(((r >> 17) & 0x7f80u) | q.b[3]);
+}
+
 __device__ __forceinline__ uint32_t dynamic_smem_bytes()
 {
     uint32_t v;
@@ -280,7 +298,11 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     const uint32_t l1_sa = SHARED ? l1_0 : WIDE ? l1_0 + gi * F_WIDE_BYTES : l1_0 + warp * 4096 + g * 4;
     const uint32_t cf_sa = cf_0 + gi * CFB;
     const uint32_t stage_sa = stage_0 + gi * STG;
-    const uint32_t tls = tab0 + 4 * (lane & ((1u << F_LOGS) - 1));   // this lane's slice-table replica
+    // byte (i + g) & 3 of a state word goes through slice table 3 - ((i + g) & 3)
+    CrcQuarters cq;
+#pragma unroll
+    for (uint32_t i = 0; i < 4; i++) cq.b[i] = tab0 + 32u * (3u - ((i + g) & 3u)) + 4u * k;
+    cq.rot = 8u * g;
     const uint32_t tla = adv0 - 4096u;                              // crc_advance<0> adds 4 .. 7 KiB
 
     MRingT<NSL, stream_mirror(CFN, WARPS)> ring;
@@ -326,10 +348,11 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         for (uint32_t j = 0; j < NSL; j++) mbar_init(&ring.bars[j], 1);
     mbar_fence_init();
     if (CRC && fits) {
-        // slice-by-4 tables, each word 8 times; then "advance by one row minus one lane unit"
+        // slice-by-4 tables, eight copies in the bank-quartered layout of CrcQuarters; then
+        // "advance by one row minus one lane unit"
         uint32_t *ts = reinterpret_cast<uint32_t *>(gen(tab0)), *ta = reinterpret_cast<uint32_t *>(gen(adv0));
         for (uint32_t i = threadIdx.x; i < 1024u << F_LOGS; i += WARPS * 32)
-            ts[i] = (&a.tabs->slice[0][0])[i >> F_LOGS];
+            ts[i] = a.tabs->slice[(i >> 3) & 3u][i >> 5];
         const uint32_t *row_adv = SINK == SINK_F32 ? &a.tabs->adv_row4[0][0] : &a.tabs->adv_row[0][0];
         for (uint32_t i = threadIdx.x; i < 1024u; i += WARPS * 32) ta[i] = row_adv[i];
     }
@@ -461,12 +484,12 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
                 sts_u8(stage_sa + s4 * NLANES + k, e);
                 e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + (s4 + 1) * NLANES + k, e);
-                if (SINK == SINK_BF16 && CRC && pending) acc = crc_feed4<F_LOGS>(tls, acc ^ wp[s4 >> 1]);
+                if (SINK == SINK_BF16 && CRC && pending) acc = crc_feed4q(cq, acc ^ wp[s4 >> 1]);
                 e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + (s4 + 2) * NLANES + k, e);
                 e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + (s4 + 3) * NLANES + k, e);
-                if (SINK == SINK_BF16 && CRC && pending) acc = crc_feed4<F_LOGS>(tls, acc ^ wp[(s4 >> 1) + 1]);
+                if (SINK == SINK_BF16 && CRC && pending) acc = crc_feed4q(cq, acc ^ wp[(s4 >> 1) + 1]);
                 caddr += 2 * __popc(hist);
             }
             pending = false;
@@ -474,7 +497,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
             if (SINK == SINK_BF16 && CRC && pending) {
                 acc = crc_advance<0>(tla, acc);
 #pragma unroll
-                for (int i = 0; i < 8; i++) acc = crc_feed4<F_LOGS>(tls, acc ^ wp[i]);
+                for (int i = 0; i < 8; i++) acc = crc_feed4q(cq, acc ^ wp[i]);
                 pending = false;
             }
 #pragma unroll 1
@@ -563,7 +586,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
             if (CRC) {
                 acc = crc_advance<0>(tla, acc);
 #pragma unroll
-                for (int i = 0; i < 16; i++) acc = crc_feed4<F_LOGS>(tls, acc ^ w[i]);
+                for (int i = 0; i < 16; i++) acc = crc_feed4q(cq, acc ^ w[i]);
                 if ((t & 127u) == 127u || t + 1 == my_tiles) {
                     // close the 64 KiB piece: lane units -> row end, XOR over the group
                     uint32_t v = crc_mulmod(a.tabs->lane_mul8_4[k], acc);
@@ -627,7 +650,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
             } else {
                 acc = crc_advance<0>(tla, acc);
 #pragma unroll
-                for (int i = 0; i < 8; i++) acc = crc_feed4<F_LOGS>(tls, acc ^ w[i]);
+                for (int i = 0; i < 8; i++) acc = crc_feed4q(cq, acc ^ w[i]);
                 // close the 64 KiB piece: lane units -> row end, XOR over the group
                 uint32_t v = crc_mulmod(a.tabs->lane_mul8[k], acc);
                 v ^= __shfl_xor_sync(grp_mask, v, 1);
