@@ -6,6 +6,8 @@ probing, and the artifact sits beside its sources so it travels with the tree.
 """
 from __future__ import annotations
 
+import contextlib
+import fcntl
 import os
 import shutil
 import subprocess
@@ -34,6 +36,22 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
+@contextlib.contextmanager
+def _build_lock():
+    """An exclusive lock on a file beside the library (no lock where the directory is
+    read-only: the compile then fails on its own account)."""
+    try:
+        f = open(LIB + ".lock", "w")
+    except OSError:
+        yield
+        return
+    try:
+        fcntl.flock(f, fcntl.LOCK_EX)
+        yield
+    finally:
+        f.close()
+
+
 def build(force: bool = False, verbose: bool = False) -> str | None:
     """Path of the built library, compiling it if sources are newer. None on failure
     (reason in `last_error`); never raises."""
@@ -52,24 +70,30 @@ def build(force: bool = False, verbose: bool = False) -> str | None:
             return LIB
         last_error = "nvcc was not found (set NVCC or put it on PATH)"
         return None
-    tmp = LIB + ".tmp"
-    cmd = [nvcc, *NVCC_FLAGS, "-o", tmp, *SOURCES]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    try:
-        p = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True, timeout=900)
-    except Exception as exc:
-        last_error = f"nvcc did not run: {exc}"
-        return None
-    if verbose:
-        print(p.stderr)
-    if p.returncode != 0:
-        last_error = "nvcc failed: " + (p.stderr.strip().splitlines() or ["?"])[-1]
+    # Several processes may get here at once (one rank per GPU): one of them compiles, the
+    # others wait on the lock and find the library fresh; each output file has its own name,
+    # and the rename is atomic.
+    with _build_lock():
+        if not force and not _stale():
+            return LIB
+        tmp = f"{LIB}.{os.getpid()}.tmp"
+        cmd = [nvcc, *NVCC_FLAGS, "-o", tmp, *SOURCES]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        try:
+            p = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True, timeout=900)
+        except Exception as exc:
+            last_error = f"nvcc did not run: {exc}"
+            return None
         if verbose:
             print(p.stderr)
-        return None
-    os.replace(tmp, LIB)
-    return LIB
+        if p.returncode != 0:
+            last_error = "nvcc failed: " + (p.stderr.strip().splitlines() or ["?"])[-1]
+            if os.path.exists(tmp):
+                os.unlink(tmp)
+            return None
+        os.replace(tmp, LIB)
+        return LIB
 
 
 if __name__ == "__main__":
