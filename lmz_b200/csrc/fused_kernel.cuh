@@ -52,7 +52,7 @@ __host__ __device__ constexpr uint32_t stream_ring_bytes(int cfn, int warps)
     return F_SLOT * stream_nslot(cfn, warps) + stream_mirror(cfn, warps) + 16;
 }
 __host__ __device__ constexpr uint32_t stream_stage(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 272u : F_STAGE; }
-constexpr uint32_t F_LOGS = 3;                     // CRC slice tables replicated 8x (32 KiB): 4x and 16x measured slower
+constexpr uint32_t F_LOGS = 3;                     // eight copies of the CRC slice tables (32 KiB), one per lane of a group: see CrcQuarters
 constexpr uint32_t F_CRC_BYTES = (4096u << F_LOGS) + 4096u;   // + the row-advance tables, once
 constexpr uint32_t F_ROW = 256, F_UNIT = 32;       // bytes of BF16 one group / one lane emits per tile
 constexpr uint32_t F_SMALL_LIVE = 104;             // largest alphabet the CFN = 128 instance takes
