@@ -80,6 +80,26 @@ def test_validate_is_host_side(lib_path, orc):
     assert lib.lmz_gpu_validate(s, struct.pack("<QQ", 0, 100), 1) == -3
 
 
+def _hold_build_lock(args):
+    import time
+    from lmz_b200 import build
+    with build._build_lock():
+        t0 = time.monotonic()
+        time.sleep(args)
+        return t0, time.monotonic()
+
+
+def test_concurrent_builds_take_turns(lib_path):
+    """One rank per GPU may find the library stale at the same moment: the build lock
+    admits one process at a time (the others then find the library fresh)."""
+    import multiprocessing as mp
+    from lmz_b200 import build
+    with mp.get_context("spawn").Pool(2) as pool:
+        (a0, a1), (b0, b1) = pool.map(_hold_build_lock, [0.4, 0.4])
+    assert a1 <= b0 or b1 <= a0, "both processes held the build lock at once"
+    assert build.build() == build.LIB and not build._stale()
+
+
 def test_import_is_free_of_cuda_side_effects():
     """Importing the package neither builds nor loads anything, and LMZ_NO_GPU
     disables the decoder (the reference's tests/test_lmz.py:2573-2607)."""
