@@ -217,8 +217,26 @@ def cpu_decode_sample(blob, sample_mb: int, threads: int, lib_kind: str):
     return done / dt / 1e9, what, lib_kind
 
 
+_RESULT = sys.stdout
+
+
+def own_stdout():
+    """Keep stdout for the one JSON line: libraries that write to file descriptor 1
+    (NCCL prints its version banner there) are sent to stderr instead."""
+    global _RESULT
+    sys.stdout.flush()
+    _RESULT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
+def emit(line: dict):
+    _RESULT.write(json.dumps(line) + "\n")
+    _RESULT.flush()
+
+
 def main():
     a = parse_args()
+    own_stdout()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -412,7 +430,7 @@ def main():
         "default_layout": other,
         "partitioned": part,
     }
-    print(json.dumps(line))
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -611,7 +629,7 @@ def run_reference(a, rank: int):
         "e2e": {"value": round(v, 3), "unit": "GB/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 if __name__ == "__main__":
