@@ -37,6 +37,8 @@ MODELS = {
     "llama-8layer": dict(layers=8, hidden=4096, ffn=14336, kv=1024, vocab=1024, shards=1),
     "llama-2layer": dict(layers=2, hidden=4096, ffn=14336, kv=1024, vocab=1024, shards=1),
     "llama-tiny": dict(layers=2, hidden=1024, ffn=3584, kv=256, vocab=8000, shards=2),
+    # the single 4096 x 14336 BF16 tensor (117 MB) of the first configuration
+    "config1-tensor": dict(kind="spec", spec=[[("w", "BF16", (4096, 14336))]]),
     # other configurations (not the headline): each rank's own 1/8 tensor-parallel slice of a
     # 70B BF16 model (17.6 GB) or of an FP32 XLM-R-large container, and a 3-checkpoint BF16
     # delta chain on the Pythia-160m shapes
@@ -78,29 +80,80 @@ def per_rank_archives(a) -> bool:
     return MODELS[a.model].get("tp", 1) > 1
 
 
+def archive_key(model: str, layout: str, chunk_size: int, seed: int) -> str:
+    return f"lmzb200-{model}-{layout}-{chunk_size}-{seed}"
+
+
+def build_archive(model: str, layout: str, chunk_size: int = 0, seed: int = 1, nproc=None,
+                  want_files: bool = False):
+    """The synthetic archive of a workload, written by the checker's reference-exact
+    writer.  Returns (archive bytes, files) where files is [(relative path, bytes)] of
+    the model's source files when `want_files` (else None)."""
+    from oracle import archive as oa, bigwrite, synth
+    m = dict(MODELS[model])
+    kind = m.pop("kind", "llama")
+    mapped = layout == "mapped"
+    cs = chunk_size or None
+    if kind == "chain":
+        files = [(f"step{i}/model.safetensors", f) for i, f in enumerate(synth.delta_chain_files(**m))]
+        blob = np.frombuffer(oa.write_archive(files, chunk_size=cs, mapped=mapped), dtype=np.uint8)
+        return blob, (files if want_files else None)
+    spec = m["spec"] if kind == "spec" else synth.xlmr_spec(**m) if kind == "xlmr" else synth.llama_spec(**m)
+    blob, layouts = bigwrite.write_model_archive(spec, seed=seed, chunk_size=cs, mapped=mapped, nproc=nproc)
+    files = None
+    if want_files:
+        files = [(f"model-{i + 1:05d}-of-{len(layouts):05d}.safetensors", lay.bytes(0, lay.size))
+                 for i, lay in enumerate(layouts)]
+    return blob, files
+
+
+def model_files_and_archive(model: str, layout: str, seed: int = 1):
+    """(source files, archive, pin key) -- what tests/golden/make_bench_pins.py compares
+    with the reference's own writer."""
+    blob, files = build_archive(model, layout, 0, seed, want_files=True)
+    return files, blob, archive_key(model, layout, 0, seed)
+
+
+def archive_digests(blob) -> dict:
+    """sha256 of the payload region and of the raw chunk records."""
+    import hashlib
+    from oracle import archive as oa
+    recs = oa.Archive(blob).records
+    toff = int(np.frombuffer(np.asarray(blob[-40:-32]).tobytes(), dtype="<u8")[0])
+    return {"payload_sha256": hashlib.sha256(memoryview(np.ascontiguousarray(blob[32:toff]))).hexdigest(),
+            "records_sha256": hashlib.sha256(recs.tobytes()).hexdigest()}
+
+
+def pin_status(key: str, blob) -> str:
+    """Compare an archive with the digests tests/golden/bench_pins.json holds for it
+    (written from the reference's own `lmz.api.compress` output on the same files)."""
+    try:
+        with open(os.path.join(ROOT, "tests", "golden", "bench_pins.json")) as f:
+            pin = json.load(f).get(key)
+    except OSError:
+        pin = None
+    if pin is None:
+        return "no pin for this workload"
+    d = archive_digests(blob)
+    if d["payload_sha256"] != pin["payload_sha256"] or d["records_sha256"] != pin["records_sha256"]:
+        raise SystemExit(f"the generated archive {key} differs from the reference-written pin")
+    return "payload and chunk records sha256-equal to the reference writer's output"
+
+
 def get_archive(a, rank: int, barrier) -> np.ndarray:
     """The benchmark archive as a numpy byte array, generated once per box and
-    cached in /dev/shm (ranks other than 0 wait for rank 0)."""
-    cs = a.chunk_size or None
+    cached in /dev/shm (ranks other than 0 wait for rank 0), and checked there against
+    its reference-written pin; the verdict is kept beside the cached file."""
     own = per_rank_archives(a)
     seed = a.seed * 64 + rank if own else a.seed
-    key = f"lmzb200-{a.model}-{a.layout}-{a.chunk_size}-{seed}.lmz"
-    cache = os.path.join("/dev/shm" if os.path.isdir("/dev/shm") else "/tmp", key)
+    key = archive_key(a.model, a.layout, a.chunk_size, seed)
+    cache = os.path.join("/dev/shm" if os.path.isdir("/dev/shm") else "/tmp", key + ".lmz")
     if (own or rank == 0) and (a.no_cache or not os.path.exists(cache)):
-        from oracle import archive as oa, bigwrite, synth
         t = time.time()
-        m = dict(MODELS[a.model])
-        kind = m.pop("kind", "llama")
-        mapped = a.layout == "mapped"
-        if kind == "chain":
-            files = synth.delta_chain_files(**m)
-            blob = np.frombuffer(oa.write_archive(
-                [(f"step{i}/model.safetensors", f) for i, f in enumerate(files)],
-                chunk_size=cs, mapped=mapped), dtype=np.uint8)
-        else:
-            spec = synth.xlmr_spec(**m) if kind == "xlmr" else synth.llama_spec(**m)
-            nproc = max(1, (os.cpu_count() or 1) // int(os.environ.get("LOCAL_WORLD_SIZE", "1"))) if own else None
-            blob, _ = bigwrite.write_model_archive(spec, seed=seed, chunk_size=cs, mapped=mapped, nproc=nproc)
+        nproc = max(1, (os.cpu_count() or 1) // int(os.environ.get("LOCAL_WORLD_SIZE", "1"))) if own else None
+        blob, _ = build_archive(a.model, a.layout, a.chunk_size, seed, nproc=nproc)
+        with open(cache + ".pin", "w") as f:
+            f.write(pin_status(key, blob))
         tmp = cache + f".{os.getpid()}"
         blob.tofile(tmp)
         os.replace(tmp, cache)
@@ -109,6 +162,16 @@ def get_archive(a, rank: int, barrier) -> np.ndarray:
     barrier()
     # one copy of the archive per box: every rank maps the same pages
     return np.memmap(cache, dtype=np.uint8, mode="r+")
+
+
+def archive_pin(a, rank: int = 0) -> str:
+    own = per_rank_archives(a)
+    key = archive_key(a.model, a.layout, a.chunk_size, a.seed * 64 + rank if own else a.seed)
+    try:
+        with open(os.path.join("/dev/shm" if os.path.isdir("/dev/shm") else "/tmp", key + ".lmz.pin")) as f:
+            return f.read()
+    except OSError:
+        return "unknown"
 
 
 class ClockSampler:

@@ -78,6 +78,35 @@ static int sm_count(int *out)
 struct SideStream {
     cudaStream_t stream = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr;
+    std::mutex busy;     // held by the host thread that is between its fork and its join
+};
+
+// From fork to join one host thread owns the device's side stream and its two events
+// (another thread's record would move them under it); whichever way the call ends, the
+// caller's stream is made to wait for what was put on the side stream.
+struct SideScope {
+    SideStream *side = nullptr;
+    cudaStream_t main = nullptr;
+    bool forked = false;
+    std::unique_lock<std::mutex> owner;
+    cudaError_t fork(SideStream *s, cudaStream_t cs)
+    {
+        side = s; main = cs;
+        owner = std::unique_lock<std::mutex>(s->busy);
+        cudaError_t e = cudaEventRecord(s->fork, cs);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s->stream, s->fork, 0);
+        forked = e == cudaSuccess;
+        return e;
+    }
+    cudaError_t join()
+    {
+        if (!forked) return cudaSuccess;
+        forked = false;
+        cudaError_t e = cudaEventRecord(side->join, side->stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(main, side->join, 0);
+        return e;
+    }
+    ~SideScope() { join(); }
 };
 
 static int side_stream(SideStream **out)
@@ -130,6 +159,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     //     4-byte-element chunks with a coded top plane and three stored planes:
     //     decode, merge, write and checksum in one kernel
     SideStream *side = nullptr;
+    SideScope scope;
     const bool other_work = p->n_stream_jobs || p->n_cond || p->piece_split[2] > p->piece_split[0] ||
                             p->piece_split[5] > p->piece_split[3];
     if (p->n_fused && (ph & 16u)) {
@@ -138,12 +168,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
             rc = side_stream(&side);
             if (rc) return rc;
             if (side) {
-                // record + wait as a pair: another host thread must not re-record the
-                // event in between
-                static std::mutex fork_mu;
-                std::lock_guard<std::mutex> lock(fork_mu);
-                CK("cudaEventRecord", cudaEventRecord(side->fork, cs));
-                CK("cudaStreamWaitEvent", cudaStreamWaitEvent(side->stream, side->fork, 0));
+                CK("fork to the side stream", scope.fork(side, cs));
                 fs = side->stream;
             }
         }
@@ -164,22 +189,21 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         const uint32_t nsmall4 = p->n_fused_f32_small < p->n_fused_f32 ? p->n_fused_f32_small : p->n_fused_f32;
         auto part = [&](uint32_t cnt) { sa.jobs += sa.njobs; sa.status += sa.njobs; sa.njobs = cnt; };
         sa.njobs = nsmall;
-        rc = p->d_piece_crc ? launch_stream<SINK_BF16, true, 128>(sa, fs)
-                            : launch_stream<SINK_BF16, false, 128>(sa, fs);
+        rc = p->d_piece_crc ? launch_stream<SINK_BF16, true, F_SMALL_CFN>(sa, fs)
+                            : launch_stream<SINK_BF16, false, F_SMALL_CFN>(sa, fs);
         if (rc) return rc;
         part(nbf - nsmall);
         rc = p->d_piece_crc ? launch_stream<SINK_BF16, true, 256>(sa, fs)
                             : launch_stream<SINK_BF16, false, 256>(sa, fs);
         if (rc) return rc;
         part(nsmall4);
-        rc = p->d_piece_crc ? launch_stream<SINK_F32, true, 128>(sa, fs)
-                            : launch_stream<SINK_F32, false, 128>(sa, fs);
+        rc = p->d_piece_crc ? launch_stream<SINK_F32, true, F_SMALL_CFN>(sa, fs)
+                            : launch_stream<SINK_F32, false, F_SMALL_CFN>(sa, fs);
         if (rc) return rc;
         part(p->n_fused_f32 - nsmall4);
         rc = p->d_piece_crc ? launch_stream<SINK_F32, true, 256>(sa, fs)
                             : launch_stream<SINK_F32, false, 256>(sa, fs);
         if (rc) return rc;
-        if (side) CK("cudaEventRecord", cudaEventRecord(side->join, side->stream));
     }
 
     // 1. every rANS stream whose length is known up front, into scratch
@@ -242,11 +266,11 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     f.piece_cnt = (const uint32_t *)p->d_piece_cnt;
     // piece groups: 0 pass-1 conditioned, 1 pass-1 plain, 2 fused (done above),
     //               3 pass-2 conditioned, 4 pass-2 plain
-    if (side && !(ph & 4u)) CK("cudaStreamWaitEvent", cudaStreamWaitEvent(cs, side->join, 0));
+    if (!(ph & 4u)) CK("join the side stream", scope.join());
     for (int part = 0; part < 5 && (ph & 4u); part++) {
         if (part == 2) {
             // pass 2 (and the verdicts) read what the fused kernel wrote
-            if (side) CK("cudaStreamWaitEvent", cudaStreamWaitEvent(cs, side->join, 0));
+            CK("join the side stream", scope.join());
             continue;
         }
         f.piece_begin = p->piece_split[part];

@@ -41,6 +41,8 @@ struct CrcTables {
     uint32_t run_mul[256];    // x^(8 * 256 * (255 - t)): thread t's 256-byte run to the piece's end
     uint32_t adv_row4[4][256];// advance by a 512-byte group row minus one 64-byte lane unit (4-byte elements)
     uint32_t lane_mul8_4[8];  // x^(8 * 64 * (7 - k))
+    uint32_t mul_row[4][256]; // multiply a state by x^(8 * 256), one 256-byte group row, per state byte
+    uint32_t word_mul[8][8];  // x^(32 * (64 - 8k - i)): word i of lane k's 32-byte unit to the row's end
 };
 
 // Rows of the piece layout: 256 threads x 16 bytes.
@@ -97,6 +99,11 @@ inline void crc_build_tables(CrcTables &t)
     for (int j = 0; j < 4; j++)
         for (uint32_t i = 0; i < 256; i++) t.adv_row4[j][i] = crc_mulmod(adv4, i << (8 * j));
     for (uint32_t k = 0; k < 8; k++) t.lane_mul8_4[k] = crc_xpow(t.x2, 8ull * 64 * (7 - k));
+    uint32_t row = crc_xpow(t.x2, 8ull * 256);
+    for (int j = 0; j < 4; j++)
+        for (uint32_t i = 0; i < 256; i++) t.mul_row[j][i] = crc_mulmod(row, i << (8 * j));
+    for (uint32_t k = 0; k < 8; k++)
+        for (uint32_t i = 0; i < 8; i++) t.word_mul[k][i] = crc_xpow(t.x2, 32ull * (64 - 8 * k - i));
 }
 
 // Feed one little-endian 32-bit word: four table lookups.

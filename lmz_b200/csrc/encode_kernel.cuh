@@ -255,7 +255,8 @@ __global__ void k_pack_streams(const uint8_t *slots, uint32_t slot_bytes, const 
 {
     const uint32_t i = blockIdx.x;
     if (i >= nstr) return;
-    const uint64_t len = offs[2 * i + 1];
+    uint64_t len = offs[2 * i + 1];
+    if (len > slot_bytes) len = slot_bytes;        // a stream never outgrows its slot
     const uint8_t *s = slots + (size_t)(i + 1) * slot_bytes - len;
     uint8_t *d = out + offs[2 * i];
     for (uint64_t j = threadIdx.x; j < len; j += blockDim.x) d[j] = s[j];

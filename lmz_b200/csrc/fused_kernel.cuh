@@ -36,9 +36,10 @@
 
 namespace lmz {
 
+enum : int { SINK_BYTES = 0, SINK_BF16 = 1, SINK_F32 = 2 };
 constexpr uint32_t F_SLOT = 128, F_NSLOT = 4, F_RING = F_SLOT * F_NSLOT;
 constexpr uint32_t F_MIRROR = 272;                 // a tile reads at most 256 + 2 bytes ahead
-constexpr uint32_t F_RING_BYTES = F_RING + F_MIRROR + 16;   // 800
+constexpr uint32_t F_RING_BYTES = F_RING + F_MIRROR;        // 784
 constexpr uint32_t F_STAGE = 144;                  // 128 + 16: groups land 4 banks apart
 // The per-stream wide instance (CFN = 0) runs one warp per scheduler, where every
 // instruction of tile bookkeeping is paid in full, and has shared memory to spare beside
@@ -49,14 +50,17 @@ __host__ __device__ constexpr uint32_t stream_nslot(int cfn, int warps) { return
 __host__ __device__ constexpr uint32_t stream_mirror(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 528u : F_MIRROR; }
 __host__ __device__ constexpr uint32_t stream_ring_bytes(int cfn, int warps)
 {
-    return F_SLOT * stream_nslot(cfn, warps) + stream_mirror(cfn, warps) + 16;
+    return F_SLOT * stream_nslot(cfn, warps) + stream_mirror(cfn, warps);
 }
 __host__ __device__ constexpr uint32_t stream_stage(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 272u : F_STAGE; }
 constexpr uint32_t F_LOGS = 3;                     // eight copies of the CRC slice tables (32 KiB), one per lane of a group: see CrcQuarters
 constexpr uint32_t F_CRC_BYTES = (4096u << F_LOGS) + 4096u;   // + the row-advance tables, once
 constexpr uint32_t F_ROW = 256, F_UNIT = 32;       // bytes of BF16 one group / one lane emits per tile
-constexpr uint32_t F_SMALL_LIVE = 104;             // largest alphabet the CFN = 128 instance takes
-enum : int { SINK_BYTES = 0, SINK_BF16 = 1, SINK_F32 = 2 };
+#ifndef LMZ_SMALL_CFN
+#define LMZ_SMALL_CFN 128
+#endif
+constexpr int F_SMALL_CFN = LMZ_SMALL_CFN;         // level-2 slots of the dense instance
+constexpr uint32_t F_SMALL_LIVE = F_SMALL_CFN - 24; // largest alphabet it takes (the warp's streams sit 0, 8, 16, 24 entries in)
 
 struct FusedJob {
     uint64_t src_off;    // rANS stream, bytes from the source base
@@ -100,7 +104,7 @@ constexpr uint32_t F_WIDE_BYTES = PROB_SCALE * 4;   // CFN = 0: one 16 KiB slot 
 constexpr int F_WIDE_GROUPS = 12;                   // three full warps; 13 tables would fit, but not their rings
 __host__ __device__ constexpr uint32_t stream_group_bytes(int cfn)
 {
-    return (cfn > 0 ? 1024 + 4 * cfn : cfn == 0 ? F_WIDE_BYTES : 0) + F_RING_BYTES + F_STAGE + 32;   // 3024 / 2512 / 17360 / 976
+    return (cfn > 0 ? 1024 + 4 * cfn : cfn == 0 ? F_WIDE_BYTES : 0) + F_RING_BYTES + F_STAGE + 32;   // 3008 / 2496 / 17344 / 960
 }
 constexpr int F_SHARED_WARPS = 16;                  // CFN = -1: one table per CTA, two CTAs per SM (64 registers a thread)
 // Streams are carved from the bottom of the CTA's shared memory and the CRC tables
@@ -113,18 +117,31 @@ __host__ __device__ constexpr uint32_t stream_crc_slice(uint32_t top)
 {
     return (stream_crc_adv(top) - (4096u << F_LOGS)) & ~((1024u << F_LOGS) - 1u);
 }
-__host__ __device__ constexpr int stream_warps(int cfn, bool crc)
+// The BF16 sink's checksum needs no row-advance tables (see k_stream), so the 4 KiB they
+// would take, above the slice tables, hold the level-1 tables of the CTA's last warp.
+#ifdef LMZ_X_NO_TOPL1
+__host__ __device__ constexpr bool stream_top_l1(int, bool, int) { return false; }
+#else
+__host__ __device__ constexpr bool stream_top_l1(int sink, bool crc, int cfn) { return sink == SINK_BF16 && crc && cfn > 0; }
+#endif
+__host__ __device__ constexpr int stream_warps(int cfn, bool crc, int sink = SINK_BYTES)
 {
     constexpr uint32_t top = F_SMEM_BASE + F_SMEM_DYN;
     if (cfn == 0) return F_WIDE_GROUPS / 4;
     if (cfn < 0) return F_SHARED_WARPS;
-    return (int)(((crc ? stream_crc_slice(top) : top) - F_SMEM_BASE) / (4u * stream_group_bytes(cfn)));
+    const uint32_t room = (crc ? stream_crc_slice(top) : top) - F_SMEM_BASE + (stream_top_l1(sink, crc, cfn) ? 4096u : 0u);
+    int w = (int)(room / (4u * stream_group_bytes(cfn)));
+    // Registers are shared per scheduler: a 21st warp would put six on one of the four and cut every
+    // thread from 96 registers to 80 (which this kernel does not fit in), so 20 is the most.
+    if (crc && w > 20) w = 20;
+    return w;
 }
 __host__ __device__ constexpr unsigned stream_groups(int cfn, int warps) { return warps * 4; }
 static_assert(F_LOGS == 3 && stream_crc_slice(F_SMEM_BASE + F_SMEM_DYN) % 32768u == 0,
               "crc_feed4q ORs a 32 KiB table's offsets onto its base");
 static_assert(stream_warps(128, true) == 19 && stream_warps(256, true) == 16 &&
-              stream_warps(128, false) == 23 && stream_warps(256, false) == 19, "shared memory budget");
+              stream_warps(128, false) == 23 && stream_warps(256, false) == 19 &&
+              stream_warps(128, true, SINK_BF16) >= 19 && stream_warps(256, true, SINK_BF16) == 16, "shared memory budget");
 
 __device__ __forceinline__ void bulk_g2s_sa(uint32_t dst_sa, const void *src, uint32_t bytes,
                                             uint32_t bar_sa)
@@ -267,11 +284,18 @@ __device__ __forceinline__ uint32_t dynamic_smem_bytes()
 template <int SINK, bool CRC, int WARPS, int CFN>
 __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamArgs a)
 {
+    // SINK_BF16 checksums: lane k keeps one running value per word of its 32-byte unit,
+    // ra[i] = sum over the piece's rows so far of word i * x^(2048 * rows since); a row
+    // costs each of them one multiplication by x^2048 (the same four lookups as feeding a
+    // word) with no chain between the eight and no per-row advance; the constants
+    // word_mul[k][i] carry them to the piece's end.
+    constexpr bool ROWMUL = SINK == SINK_BF16 && CRC;
+    constexpr bool TOPL1 = stream_top_l1(SINK, CRC, CFN);
     extern __shared__ __align__(16) uint8_t ssm[];
     constexpr bool WIDE = CFN <= 0, SHARED = CFN < 0;
     constexpr uint32_t G = stream_groups(CFN, WARPS), CFB = WIDE ? 16u : 4u * CFN;
     constexpr uint32_t LEAD = (SHARED ? 0u : HDR_BYTES) + STATE_BYTES;
-    constexpr uint32_t MAX_LIVE = CFN == 128 ? F_SMALL_LIVE : 256u;
+    constexpr uint32_t MAX_LIVE = CFN > 0 && CFN < 256 ? (uint32_t)CFN - 24u : 256u;
     constexpr uint32_t TS = stream_tile(CFN, WARPS), NSL = stream_nslot(CFN, WARPS), RB = stream_ring_bytes(CFN, WARPS);
     constexpr uint32_t STG = stream_stage(CFN, WARPS), RINGB = F_SLOT * NSL;
     constexpr uint32_t HS = NSL == 8 ? 160u : 144u;     // header staging copy: four of them cover 548 + 15 bytes
@@ -292,10 +316,12 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     const uint32_t cf_0 = (ring_0 + G * RB + CFB - 1) & ~(CFB - 1);
     // compact: level 1 at the top; wide: 16 KiB tables from the first 16 KiB boundary up
     const uint32_t l1_0 = WIDE ? (cf_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1)
-                               : ((CRC ? tab0 : top) & ~4095u) - WARPS * 4096u;
-    const bool fits = WIDE ? l1_0 + (SHARED ? 1u : G) * F_WIDE_BYTES <= top : cf_0 + G * CFB <= l1_0;
+                               : ((CRC ? tab0 : top) & ~4095u) - (WARPS - (TOPL1 ? 1 : 0)) * 4096u;
+    // compact: this warp's 4 KiB of level 1 (the last warp's sits where the row-advance tables would)
+    auto l1_of = [&](uint32_t w) { return TOPL1 && w == WARPS - 1 ? adv0 : l1_0 + w * 4096u; };
+    const bool fits = WIDE ? l1_0 + (SHARED ? 1u : G) * F_WIDE_BYTES <= top : cf_0 + G * CFB <= l1_0 && (!TOPL1 || (adv0 & 4095u) == 0);
     auto gen = [&](uint32_t sa) { return ssm + (sa - s0); };
-    const uint32_t l1_sa = SHARED ? l1_0 : WIDE ? l1_0 + gi * F_WIDE_BYTES : l1_0 + warp * 4096 + g * 4;
+    const uint32_t l1_sa = SHARED ? l1_0 : WIDE ? l1_0 + gi * F_WIDE_BYTES : l1_of(warp) + g * 4;
     const uint32_t cf_sa = cf_0 + gi * CFB;
     const uint32_t stage_sa = stage_0 + gi * STG;
     // byte (i + g) & 3 of a state word goes through slice table 3 - ((i + g) & 3)
@@ -351,10 +377,13 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         // slice-by-4 tables, eight copies in the bank-quartered layout of CrcQuarters; then
         // "advance by one row minus one lane unit"
         uint32_t *ts = reinterpret_cast<uint32_t *>(gen(tab0)), *ta = reinterpret_cast<uint32_t *>(gen(adv0));
+        // (crc_feed4q sends byte m of a state through table 3 - m, crc_word's order; the
+        // row multiplication is in crc_apply's order, byte m through table m)
         for (uint32_t i = threadIdx.x; i < 1024u << F_LOGS; i += WARPS * 32)
-            ts[i] = a.tabs->slice[(i >> 3) & 3u][i >> 5];
+            ts[i] = ROWMUL ? a.tabs->mul_row[3u - ((i >> 3) & 3u)][i >> 5] : a.tabs->slice[(i >> 3) & 3u][i >> 5];
         const uint32_t *row_adv = SINK == SINK_F32 ? &a.tabs->adv_row4[0][0] : &a.tabs->adv_row[0][0];
-        for (uint32_t i = threadIdx.x; i < 1024u; i += WARPS * 32) ta[i] = row_adv[i];
+        if (!ROWMUL)
+            for (uint32_t i = threadIdx.x; i < 1024u; i += WARPS * 32) ta[i] = row_adv[i];
     }
     __syncthreads();
 
@@ -416,9 +445,9 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
             tb.wide = reinterpret_cast<uint32_t *>(gen(l1_0 + (warp * 4 + gg) * F_WIDE_BYTES));
             ok = build_table<T_WIDE1>(freq_of, tb, lane);
         } else {
-            tb.l1 = reinterpret_cast<uint32_t *>(gen(l1_0 + warp * 4096 + gg * 4));
+            tb.l1 = reinterpret_cast<uint32_t *>(gen(l1_of(warp) + gg * 4));
             tb.cf = reinterpret_cast<uint32_t *>(gen(cf_0 + (warp * 4 + gg) * CFB));
-            ok = build_table<T_COMPACT, 4>(freq_of, tb, lane, CFN == 128 ? 8u * gg : 0u, &nlive, MAX_LIVE);
+            ok = build_table<T_COMPACT, 4>(freq_of, tb, lane, CFN < 256 ? 8u * gg : 0u, &nlive, MAX_LIVE);
         }
         ok = ok && rd(sk) == 'R' && rd(sk + 1) == '1';
         // an alphabet too large for this instance is the caller's mistake, not the stream's
@@ -442,10 +471,10 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
 #pragma unroll
         for (int i = 0; i < 5; i++) m[i] = __ldg(mq + i);
     }
-    // CRC of a tile is folded in while the NEXT tile decodes (its 36 dependent table
-    // lookups hide behind the decode chain); `wp` holds the tile waiting to be folded.
-    uint32_t acc = 0, wp[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    bool pending = false;
+    // SINK_BF16 checksum: the eight running values ra[] are multiplied by x^2048 while the
+    // NEXT tile decodes (32 independent table lookups that hide behind the decode chain),
+    // then that tile's words are XORed in.  SINK_F32 keeps one value, `acc`.
+    uint32_t acc = 0, ra[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 
     // ---- tiles of 128 symbols ---------------------------------------------------------
     const uint32_t warp_tiles = __reduce_max_sync(0xffffffffu, my_tiles);
@@ -476,7 +505,6 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         // (lanes that never had a stream run along in full tiles; nothing of theirs is kept)
         const bool full = __all_sync(0xffffffffu, rem >= TS);
         if (full) {
-            if (SINK == SINK_BF16 && CRC && pending) acc = crc_advance<0>(tla, acc);
 #pragma unroll
             for (uint32_t s4 = 0; s4 < TS / NLANES; s4 += 4) {
                 uint32_t hist = 0, e;
@@ -484,21 +512,18 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
                 sts_u8(stage_sa + s4 * NLANES + k, e);
                 e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + (s4 + 1) * NLANES + k, e);
-                if (SINK == SINK_BF16 && CRC && pending) acc = crc_feed4q(cq, acc ^ wp[s4 >> 1]);
+                if (ROWMUL) ra[s4 >> 1] = crc_feed4q(cq, ra[s4 >> 1]);
                 e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + (s4 + 2) * NLANES + k, e);
                 e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 sts_u8(stage_sa + (s4 + 3) * NLANES + k, e);
-                if (SINK == SINK_BF16 && CRC && pending) acc = crc_feed4q(cq, acc ^ wp[(s4 >> 1) + 1]);
+                if (ROWMUL) ra[(s4 >> 1) + 1] = crc_feed4q(cq, ra[(s4 >> 1) + 1]);
                 caddr += 2 * __popc(hist);
             }
-            pending = false;
         } else {
-            if (SINK == SINK_BF16 && CRC && pending) {
-                acc = crc_advance<0>(tla, acc);
+            if (ROWMUL) {
 #pragma unroll
-                for (int i = 0; i < 8; i++) acc = crc_feed4q(cq, acc ^ wp[i]);
-                pending = false;
+                for (int i = 0; i < 8; i++) ra[i] = crc_feed4q(cq, ra[i]);
             }
 #pragma unroll 1
             for (uint32_t s = 0; s < TS / NLANES; s++) {
@@ -642,17 +667,16 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
             }
         }
         if (CRC) {
-            const bool last = t + 1 == my_tiles;
-            if (!((t & 255u) == 255u || last)) {
 #pragma unroll
-                for (int i = 0; i < 8; i++) wp[i] = w[i];
-                pending = true;
-            } else {
-                acc = crc_advance<0>(tla, acc);
+            for (int i = 0; i < 8; i++) ra[i] ^= w[i];
+            if ((t & 255u) == 255u || t + 1 == my_tiles) {
+                // close the 64 KiB piece: every running value to the row's end, XOR over the group
+                uint32_t v = 0;
 #pragma unroll
-                for (int i = 0; i < 8; i++) acc = crc_feed4q(cq, acc ^ w[i]);
-                // close the 64 KiB piece: lane units -> row end, XOR over the group
-                uint32_t v = crc_mulmod(a.tabs->lane_mul8[k], acc);
+                for (int i = 0; i < 8; i++) {
+                    v ^= crc_mulmod(a.tabs->word_mul[k][i], ra[i]);
+                    ra[i] = 0;
+                }
                 v ^= __shfl_xor_sync(grp_mask, v, 1);
                 v ^= __shfl_xor_sync(grp_mask, v, 2);
                 v ^= __shfl_xor_sync(grp_mask, v, 4);
@@ -662,7 +686,6 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
                     if (rows * F_ROW != plen) v = crc_unshift(a.tabs->x2, v, rows * F_ROW - plen);
                     a.piece_crc[piece0 + p] = v;
                 }
-                acc = 0;
             }
         }
     }

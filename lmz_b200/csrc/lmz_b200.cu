@@ -5,7 +5,10 @@
 // with the same names, argument meaning, return codes and error behaviour; the
 // rest are additive entry points for whole-archive decode.  Declarations and
 // the per-function contract live in include/lmz_b200.h.
+#include <atomic>
+#include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -20,25 +23,30 @@ using namespace lmz;
 
 #define API extern "C" __attribute__((visibility("default")))
 
+// Why the last call on this thread failed (lmz_gpu_last_error).
 static thread_local char g_err[256];
 
-static int fail_msg(int rc, const char *what)
+// Record a reason and hand back the code to return.
+static int report(int code, const char *fmt, ...)
 {
-    snprintf(g_err, sizeof g_err, "%s", what);
-    return rc;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return code;
 }
+
+static int fail_msg(int rc, const char *what) { return report(rc, "%s", what); }
 
 static int fail_cuda(const char *what, cudaError_t e)
 {
-    snprintf(g_err, sizeof g_err, "%s: %s", what, cudaGetErrorString(e));
-    return LMZ_GPU_ECUDA;
+    return report(LMZ_GPU_ECUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
-#define CK(what, x)                                        \
-    do {                                                   \
-        cudaError_t e_ = (x);                              \
-        if (e_ != cudaSuccess) return fail_cuda(what, e_); \
-    } while (0)
+// A CUDA call inside a function that returns a code: leave with ECUDA when it fails.
+#define CK(what, x)                                                                    \
+    if (cudaError_t status_of_call = (x); status_of_call != cudaSuccess)               \
+        return fail_cuda(what, status_of_call)
 
 static int device_ready()
 {
@@ -115,7 +123,7 @@ static int launch_stream(const StreamArgs &a0, cudaStream_t cs)
 {
     if (a0.njobs == 0) return LMZ_GPU_OK;
     StreamArgs a = a0;
-    constexpr int WARPS = stream_warps(CFN, CRC);
+    constexpr int WARPS = stream_warps(CFN, CRC, SINK);
     static bool done[64];
     int rc = stream_smem_ok();
     if (rc) return rc;
@@ -136,6 +144,9 @@ static int launch_stream(const StreamArgs &a0, cudaStream_t cs)
         per = (per + 3u) & ~3u;
         if (per > groups) per = groups;
     }
+#ifdef LMZ_EXPERIMENT
+    if (const char *e = getenv("LMZ_X_PER_CTA")) { unsigned v = (unsigned)atoi(e); if (v >= 4 && v <= groups) per = v & ~3u; }
+#endif
     a.per_cta = per;
     unsigned blocks = (a.njobs + per - 1) / per;
     k_stream<SINK, CRC, WARPS, CFN><<<blocks, WARPS * 32, shm, cs>>>(a);
@@ -145,7 +156,7 @@ static int launch_stream(const StreamArgs &a0, cudaStream_t cs)
 }
 
 // `force_mode` < 0 picks by batch size.
-static int g_force_table_mode = -1;
+static std::atomic<int> g_force_table_mode{-1};
 
 
 static StreamArgs as_stream_args(const RansArgs &a)
@@ -211,7 +222,7 @@ static int launch_compact_sorted(const RansArgs &a, cudaStream_t cs)
         sa.order = order;
         sa.count = counts;
         sa.order_from_back = 0;
-        rc = launch_stream<SINK_BYTES, false, 128>(sa, cs);
+        rc = launch_stream<SINK_BYTES, false, F_SMALL_CFN>(sa, cs);
         if (rc) break;
         sa.count = counts + 1;
         sa.order_from_back = 1;
@@ -234,18 +245,19 @@ static int launch_rans(const RansArgs &a, cudaStream_t cs, bool may_alloc = true
     if (a.shared_hdr) {
         // one table for the whole launch: the k_stream instance (128 streams per SM, leaner
         // steps) once every SM is full, the plain kernel (shorter chain on a lone warp) below
-        const bool plain = g_force_table_mode == T_NARROW ||
-                           (g_force_table_mode < 0 && a.njobs < (unsigned)sms * 128u);
+        const int forced = g_force_table_mode.load(std::memory_order_relaxed);
+        const bool plain = forced == T_NARROW || (forced < 0 && a.njobs < (unsigned)sms * 128u);
         return plain ? launch_rans_mode<T_WIDE, WARPS_WIDE>(a, cs)
                      : launch_stream<SINK_BYTES, false, -1>(as_stream_args(a), cs);
     }
-    int mode = g_force_table_mode;
+    const int forced = g_force_table_mode.load(std::memory_order_relaxed);
+    int mode = forced;
     if (mode < 0)
         mode = a.njobs <= (unsigned)sms * F_WIDE_GROUPS ? T_WIDE1
              : a.njobs >= COMPACT_MIN_JOBS ? T_COMPACT : T_NARROW;
     if (mode == T_WIDE1) return launch_stream<SINK_BYTES, false, 0>(as_stream_args(a), cs);
     if (mode == T_COMPACT) {
-        if (may_alloc && g_force_table_mode < 0) {
+        if (may_alloc && forced < 0) {
             int rc = launch_compact_sorted(a, cs);
             if (rc != 1) return rc;
         }
@@ -264,32 +276,35 @@ API int lmz_gpu_pad_bytes(void) { return (int)PAD_BYTES; }
 
 API int lmz_gpu_device_name(char *buf, int cap)
 {
-    int rc = device_ready();
-    if (rc) return rc;
-    int dev = 0;
+    if (!buf || cap <= 0) return fail_msg(LMZ_GPU_EUNSUPPORTED, "no room for the device name");
+    if (int rc = device_ready()) return rc;
+    int dev = 0, cc_major = 0, cc_minor = 0, sms = 0;
     CK("cudaGetDevice", cudaGetDevice(&dev));
     cudaDeviceProp prop;
     CK("cudaGetDeviceProperties", cudaGetDeviceProperties(&prop, dev));
-    snprintf(buf, (size_t)cap, "%s sm_%d%d %d SMs", prop.name, prop.major, prop.minor,
-             prop.multiProcessorCount);
+    cc_major = prop.major; cc_minor = prop.minor; sms = prop.multiProcessorCount;
+    snprintf(buf, (size_t)cap, "%s sm_%d%d %d SMs", prop.name, cc_major, cc_minor, sms);
     return LMZ_GPU_OK;
+}
+
+// What is wrong with the stream at `p` of `len` bytes as far as its first 516 bytes can
+// tell (NULL = nothing): the checks lmz_rans_decode makes before it touches a state
+// (lmz/native/lmzcore.c:1413-1427).
+static const char *header_defect(const uint8_t *p, uint64_t len)
+{
+    if (len < HDR_BYTES + STATE_BYTES) return "a stream is shorter than its own header";
+    if (p[0] != 'R' || p[1] != '1') return "a stream does not start with the rANS magic";
+    uint32_t total = 0;
+    for (const uint8_t *f = p + 4; f < p + HDR_BYTES; f += 2) total += f[0] | ((uint32_t)f[1] << 8);
+    return total == PROB_SCALE ? nullptr : "a stream's frequencies do not sum to 4096";
 }
 
 API int lmz_gpu_validate(const void *streams_v, const void *off_v, unsigned nstr)
 {
-    const uint8_t *streams = (const uint8_t *)streams_v;
-    const uint64_t *off = (const uint64_t *)off_v;
-    for (unsigned i = 0; i < nstr; i++) {
-        if (off[2 * i + 1] < HDR_BYTES + STATE_BYTES)
-            return fail_msg(LMZ_GPU_EBADSTREAM, "a stream is shorter than its own header");
-        const uint8_t *p = streams + off[2 * i];
-        if (p[0] != 'R' || p[1] != '1')
-            return fail_msg(LMZ_GPU_EBADSTREAM, "a stream does not start with the rANS magic");
-        uint32_t sum = 0;
-        for (int s = 0; s < 256; s++) sum += (uint32_t)p[4 + 2 * s] | ((uint32_t)p[5 + 2 * s] << 8);
-        if (sum != PROB_SCALE)
-            return fail_msg(LMZ_GPU_EBADSTREAM, "a stream's frequencies do not sum to 4096");
-    }
+    const uint8_t *base = static_cast<const uint8_t *>(streams_v);
+    const uint64_t *pairs = static_cast<const uint64_t *>(off_v);
+    for (const uint64_t *e = pairs; e != pairs + 2 * (size_t)nstr; e += 2)
+        if (const char *defect = header_defect(base + e[0], e[1])) return fail_msg(LMZ_GPU_EBADSTREAM, defect);
     return LMZ_GPU_OK;
 }
 
@@ -312,66 +327,62 @@ API int lmz_gpu_decode_batch_dev(const void *d_hdr, const void *d_streams, const
     return launch_rans(a, (cudaStream_t)cuda_stream);
 }
 
+namespace {
+// Device memory that lives as long as one host-form call.
+struct Transient {
+    void *p = nullptr;
+    ~Transient() { if (p) cudaFree(p); }
+    cudaError_t take(size_t bytes) { return cudaMalloc(&p, bytes ? bytes : 1); }
+    template <class T> T *as() const { return static_cast<T *>(p); }
+};
+}  // namespace
+
 API int lmz_gpu_decode_batch(const void *hdr, const void *streams, size_t nbytes, const void *off,
                              unsigned nstr, unsigned plane, void *out)
 {
     if (nstr == 0) return LMZ_GPU_OK;
     if (plane == 0) return fail_msg(LMZ_GPU_EUNSUPPORTED, "plane is zero");
-    int rc = device_ready();
-    if (rc) return rc;
-    const uint64_t *o = (const uint64_t *)off;
-    for (unsigned i = 0; i < nstr; i++)
-        if (o[2 * i] > nbytes || o[2 * i + 1] > nbytes - o[2 * i])
-            return fail_msg(LMZ_GPU_EBADSTREAM, "a stream lies outside the buffer");
-    if (hdr == NULL) {
-        rc = lmz_gpu_validate(streams, off, nstr);
-        if (rc) return rc;
+    if (int rc = device_ready()) return rc;
+    // every (offset, length) pair must lie inside the buffer, and a length must fit the
+    // 32 bits the kernels carry it in
+    const uint64_t *pairs = static_cast<const uint64_t *>(off);
+    for (unsigned i = 0; i < nstr; i++) {
+        const uint64_t at = pairs[2 * i], len = pairs[2 * i + 1];
+        if (at > nbytes || len > nbytes - at) return fail_msg(LMZ_GPU_EBADSTREAM, "a stream lies outside the buffer");
+        if (len >> 32) return fail_msg(LMZ_GPU_EUNSUPPORTED, "a stream is 4 GiB or longer");
     }
-    size_t obytes = (size_t)nstr * plane;
-    uint8_t *d_streams = NULL, *d_out = NULL, *d_hdr = NULL;
-    uint64_t *d_off = NULL;
-    uint32_t *d_flag = NULL;
-    uint32_t flag = 0;
-    rc = LMZ_GPU_ECUDA;
-#define TRY(what, call)                                            \
-    do {                                                           \
-        cudaError_t e_ = (call);                                   \
-        if (e_ != cudaSuccess) { rc = fail_cuda(what, e_); goto done; } \
-    } while (0)
-    TRY("cudaMalloc(streams)", cudaMalloc(&d_streams, nbytes + PAD_BYTES));
-    TRY("cudaMalloc(offsets)", cudaMalloc(&d_off, (size_t)nstr * 16));
-    TRY("cudaMalloc(out)", cudaMalloc(&d_out, obytes));
-    TRY("cudaMalloc(flag)", cudaMalloc(&d_flag, 4));
-    if (hdr) TRY("cudaMalloc(table)", cudaMalloc(&d_hdr, HDR_BYTES));
-    TRY("H2D streams", cudaMemcpy(d_streams, streams, nbytes, cudaMemcpyHostToDevice));
-    TRY("memset pad", cudaMemset(d_streams + nbytes, 0, PAD_BYTES));
-    TRY("memset flag", cudaMemset(d_flag, 0, 4));
-    TRY("H2D offsets", cudaMemcpy(d_off, off, (size_t)nstr * 16, cudaMemcpyHostToDevice));
-    if (hdr) TRY("H2D table", cudaMemcpy(d_hdr, hdr, HDR_BYTES, cudaMemcpyHostToDevice));
-    {
-        RansArgs a{};
-        a.src = d_streams; a.offs = d_off; a.plane = plane; a.njobs = nstr;
-        a.dst = d_out; a.shared_hdr = d_hdr; a.any_bad = d_flag;
-        rc = launch_rans(a, 0);
-        if (rc) goto done;
+    if (!hdr)
+        if (int rc = lmz_gpu_validate(streams, off, nstr)) return rc;
+
+    const size_t out_bytes = (size_t)nstr * plane, table_bytes = (size_t)nstr * 16;
+    Transient coded, table, plain, verdict, shared;
+    CK("cudaMalloc(streams)", coded.take(nbytes + PAD_BYTES));
+    CK("cudaMalloc(offsets)", table.take(table_bytes));
+    CK("cudaMalloc(out)", plain.take(out_bytes));
+    CK("cudaMalloc(verdict)", verdict.take(sizeof(uint32_t)));
+    CK("copy streams in", cudaMemcpy(coded.p, streams, nbytes, cudaMemcpyHostToDevice));
+    CK("clear the slack", cudaMemset(coded.as<uint8_t>() + nbytes, 0, PAD_BYTES));
+    CK("copy offsets in", cudaMemcpy(table.p, off, table_bytes, cudaMemcpyHostToDevice));
+    CK("clear the verdict", cudaMemset(verdict.p, 0, sizeof(uint32_t)));
+    if (hdr) {
+        CK("cudaMalloc(table)", shared.take(HDR_BYTES));
+        CK("copy table in", cudaMemcpy(shared.p, hdr, HDR_BYTES, cudaMemcpyHostToDevice));
     }
-    rc = LMZ_GPU_ECUDA;
-    TRY("cudaDeviceSynchronize", cudaDeviceSynchronize());
-    TRY("D2H flag", cudaMemcpy(&flag, d_flag, 4, cudaMemcpyDeviceToHost));
-    if (flag) {
-        rc = fail_msg(LMZ_GPU_EBADSTREAM, "a stream is malformed or truncated");
-        goto done;
-    }
-    TRY("D2H out", cudaMemcpy(out, d_out, obytes, cudaMemcpyDeviceToHost));
-    rc = LMZ_GPU_OK;
-#undef TRY
-done:
-    if (d_streams) cudaFree(d_streams);
-    if (d_off) cudaFree(d_off);
-    if (d_out) cudaFree(d_out);
-    if (d_flag) cudaFree(d_flag);
-    if (d_hdr) cudaFree(d_hdr);
-    return rc;
+    RansArgs a{};
+    a.src = coded.as<uint8_t>();
+    a.offs = table.as<uint64_t>();
+    a.plane = plane;
+    a.njobs = nstr;
+    a.dst = plain.as<uint8_t>();
+    a.shared_hdr = shared.as<uint8_t>();
+    a.any_bad = verdict.as<uint32_t>();
+    if (int rc = launch_rans(a, 0)) return rc;
+    CK("cudaDeviceSynchronize", cudaDeviceSynchronize());
+    uint32_t any_bad = 0;
+    CK("copy the verdict out", cudaMemcpy(&any_bad, verdict.p, sizeof any_bad, cudaMemcpyDeviceToHost));
+    if (any_bad) return fail_msg(LMZ_GPU_EBADSTREAM, "a stream is malformed or truncated");
+    CK("copy plaintext out", cudaMemcpy(out, plain.p, out_bytes, cudaMemcpyDeviceToHost));
+    return LMZ_GPU_OK;
 }
 
 // ------------------------------------------------------------------- additive
@@ -381,7 +392,7 @@ API int lmz_gpu_set_table_mode(int mode)
     if (mode != -1 && mode != T_NARROW && mode != T_COMPACT && mode != T_WIDE1)
         return fail_msg(LMZ_GPU_EUNSUPPORTED,
                         "table mode must be -1 (auto), 0 (narrow), 2 (compact) or 3 (wide per stream)");
-    g_force_table_mode = mode;
+    g_force_table_mode.store(mode, std::memory_order_relaxed);
     return LMZ_GPU_OK;
 }
 
@@ -427,6 +438,8 @@ API int lmz_gpu_pack_streams_dev(const void *d_slots, unsigned plane, const void
     int rc = device_ready();
     if (rc) return rc;
     if (nstr == 0) return LMZ_GPU_OK;
+    if (!d_slots || !d_offsets || !d_out) return fail_msg(LMZ_GPU_EUNSUPPORTED, "null argument");
+    if (plane == 0 || plane > ENCODE_MAX_PLANE) return fail_msg(LMZ_GPU_EUNSUPPORTED, "plane must be 1 .. 2^29 bytes");
     k_pack_streams<<<nstr, 128, 0, (cudaStream_t)cuda_stream>>>((const uint8_t *)d_slots, encode_slot_bytes(plane),
                                                               (const uint64_t *)d_offsets, nstr, (uint8_t *)d_out);
     cudaError_t le = cudaGetLastError();

@@ -7,8 +7,8 @@ balanced by coded + decoded bytes) from its own copy of those payloads into its
 own HBM, with no collective on the data path.  A ref or delta chunk needs the
 output range it names; when that range belongs to another rank, this rank
 decodes the covering plain chunks as well (one hop, as in lmz/api.py:832-864)
-rather than waiting for a peer.  `all_gather` optionally rebuilds the full
-output on every rank with one NCCL all-gather of equal, padded shards.
+rather than waiting for a peer.  For a full replica on every rank the output space is
+cut into equal slices instead and one in-place NCCL all-gather rebuilds it.
 """
 from __future__ import annotations
 
@@ -82,47 +82,103 @@ def shard(ar: fmt.Archive, rank: int, world: int):
     return select, (lo, hi)
 
 
-class ShardedDecoder:
-    """Rank `rank`'s share of an archive on its GPU (see `shard`)."""
+def slice_width(total: int, world: int) -> int:
+    """Bytes of the output space each rank holds when a full replica is rebuilt by an
+    in-place all-gather: equal slices, a multiple of 256 bytes."""
+    return ((-(-max(total, 1) // world)) + 255) & ~255
 
-    def __init__(self, ar, rank: int, world: int, device=None, checksum: bool = True):
+
+def slice_shard(ar: fmt.Archive, rank: int, world: int):
+    """(select, (lo, hi)) for the replica layout: rank `rank` produces the output bytes
+    [rank * w, (rank + 1) * w) clipped to the total, w = slice_width().  A chunk that
+    straddles a slice boundary is decoded by both neighbours, so every rank's slice is
+    complete without talking to a peer."""
+    w = slice_width(int(ar.total), world)
+    lo, hi = min(rank * w, int(ar.total)), min((rank + 1) * w, int(ar.total))
+    return cover(ar, [(lo, hi)]), (lo, hi)
+
+
+def gather_replica(buf, rank: int, world: int, width: int, group=None):
+    """All-gather in place: `buf` holds at least world * width bytes and this rank's slice
+    [rank * width, (rank + 1) * width) is filled; afterwards every slice is.  One
+    collective, no staging buffer: NCCL is given the slice as a view of the buffer it
+    gathers into (its in-place form).  On CPU tensors (gloo) the slice is cloned first,
+    because that backend does not take aliased arguments."""
+    import torch.distributed as dist
+    whole = buf[:world * width]
+    mine = whole[rank * width:(rank + 1) * width]
+    if not buf.is_cuda:
+        mine = mine.clone()
+    dist.all_gather_into_tensor(whole, mine, group=group)
+    return whole
+
+
+class ShardedDecoder:
+    """Rank `rank`'s share of an archive on its GPU.
+
+    `replica=False` (default): the chunks are partitioned by coded + decoded bytes (see
+    `shard`) and the rank's buffer holds only the stretch of the output space its chunks
+    and their sources span -- 1/world of it for an archive without refs or deltas.
+    `owned()` is the decoded range the rank is responsible for.
+
+    `replica=True`: the output space is cut into equal slices (see `slice_shard`), every
+    rank allocates the whole of it, decodes its slice, and `all_gather()` fills in the
+    rest with one in-place NCCL all-gather over NVLink."""
+
+    def __init__(self, ar, rank: int, world: int, device=None, checksum: bool = True,
+                 replica: bool = False):
+        import torch
+
         from . import decode, plan
         self.archive = ar if isinstance(ar, fmt.Archive) else fmt.Archive(ar)
-        self.rank, self.world = rank, world
-        self.select, self.range = shard(self.archive, rank, world)
+        self.rank, self.world, self.replica = rank, world, replica
+        self.select, self.range = (slice_shard if replica else shard)(self.archive, rank, world)
         r = self.archive.records
-        pay = None
-        if self.select.size:                 # upload only the stretch of the payload this rank reads
-            off = r["off"][self.select].astype(np.int64)
-            pay = (int(off.min()) & ~15, int((off + r["clen"][self.select]).max()))
-        p = plan.build_plan(self.archive, select=self.select, payload_range=pay)
-        self.decoder = decode.ArchiveDecoder(self.archive, device=device, checksum=checksum, plan=p)
-        own = self.select[(r["dst"][self.select] >= self.range[0]) &
-                          (r["dst"][self.select] < max(self.range[1], self.range[0] + 1))]
+        sel = self.select
+        pay = out_range = out = None
+        self.width = slice_width(int(self.archive.total), world)
+        dev = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        if sel.size:                 # upload only the stretch of the payload this rank reads
+            off = r["off"][sel].astype(np.int64)
+            pay = (int(off.min()) & ~15, int((off + r["clen"][sel]).max()))
+        if replica:
+            out = torch.empty(self.width * world + 64, dtype=torch.uint8, device=dev)
+        elif sel.size:
+            dst = r["dst"][sel].astype(np.int64)
+            out_range = (int(dst.min()) & ~15, int((dst + r["rlen"][sel]).max()))
+        else:
+            out_range = (0, 0)
+        self.out_lo = out_range[0] if out_range else 0
+        p = plan.build_plan(self.archive, select=sel, payload_range=pay, out_range=out_range)
+        self.decoder = decode.ArchiveDecoder(self.archive, device=dev, checksum=checksum, plan=p, out=out)
+        own = sel[(r["dst"][sel] >= self.range[0]) & (r["dst"][sel] < max(self.range[1], self.range[0] + 1))]
         self.owned_plain = int(r["rlen"][own].sum())
         self.owned_coded = int(r["clen"][own].sum())
+        self.h2d_bytes = int(pay[1] - pay[0]) if pay else 0
+        self.payload_range = pay
 
     def run(self, stream=None):
         return self.decoder.run(stream)
 
+    def upload(self, pinned, non_blocking: bool = True):
+        """Host -> device copy of just this rank's payload stretch; `pinned` is a host
+        uint8 tensor over the archive file from byte 0."""
+        if self.payload_range:
+            lo, hi = self.payload_range
+            self.decoder.upload(pinned[lo:hi], non_blocking=non_blocking)
+
     def check(self):
         self.decoder.check()
 
-    def all_gather(self, group=None):
-        """Every rank's owned range into every rank's output buffer (NCCL)."""
-        import torch
-        import torch.distributed as dist
-        out = self.decoder.d_out
-        ranges = [None] * self.world
-        dist.all_gather_object(ranges, self.range, group=group)
-        width = max(hi - lo for lo, hi in ranges)
-        width = (width + 15) & ~15
+    def owned(self):
+        """Device view of the output bytes [range[0], range[1]) this rank is responsible for."""
         lo, hi = self.range
-        mine = torch.zeros(width, dtype=torch.uint8, device=out.device)
-        mine[:hi - lo] = out[lo:hi]
-        gathered = torch.empty(width * self.world, dtype=torch.uint8, device=out.device)
-        dist.all_gather_into_tensor(gathered, mine, group=group)
-        for rk, (a, b) in enumerate(ranges):
-            if rk != self.rank:
-                out[a:b] = gathered[rk * width:rk * width + (b - a)]
-        return self.decoder.output
+        return self.decoder.d_out[lo - self.out_lo:hi - self.out_lo]
+
+    def all_gather(self, group=None):
+        """Every rank's slice into every rank's buffer (replica mode): one in-place NCCL
+        all-gather.  Returns the full output."""
+        if not self.replica:
+            raise RuntimeError("all_gather needs ShardedDecoder(..., replica=True)")
+        gather_replica(self.decoder.d_out, self.rank, self.world, self.width, group=group)
+        return self.decoder.d_out[:self.archive.total]

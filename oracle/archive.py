@@ -226,9 +226,11 @@ def write_archive(members, chunk_size: int | None = None, mapped: bool = False,
                 if not (t0 and t0["dtype"] == t["dtype"] and t0["shape"] == t["shape"]):
                     continue
                 s0 = t0["offsets"][0]                      # member 0 sits at dst 0
-                if e > s and np.array_equal(a[s:e], datas[0][s0:s0 + (e - s)]):
+                if e - s < (64 << 10):                     # DEDUP_MIN_TENSOR / DELTA_MIN_TENSOR, lmz/api.py:47,59
+                    continue
+                if np.array_equal(a[s:e], datas[0][s0:s0 + (e - s)]):
                     deltas[(s, e)] = (s0,)                 # dedup: lmz/api.py:748-753
-                elif e - s >= (64 << 10):
+                else:
                     deltas[(s, e)] = s0
         m = {"path": path, "size": int(a.size), "dst": base,
              "kind": "safetensors" if parsed else "raw", "mode": 0o644, "crc": 0}

@@ -312,6 +312,11 @@ def test_pythia_shaped_delta_chain():
     the previous plus N(0, 1e-4) on a random 30 % of elements; both later checkpoints
     are coded as deltas against checkpoint 0 (the earliest member holding the tensor)."""
     files = synth.delta_chain_files(hidden=384, ffn=1536, vocab=25152, layers=12)
+    # one tensor of checkpoint 1 left as it was in checkpoint 0: stored as a reference
+    # (the reference deduplicates identical tensors of 64 KiB or more, lmz/api.py:47,260)
+    s, e = oa.parse_safetensors(files[1])[1]["l0.attn.o.weight"]["offsets"]
+    files[1] = files[1].copy()
+    files[1][s:e] = files[0][s:e]
     blob = oa.write_archive([(f"step{i}/model.safetensors", f) for i, f in enumerate(files)])
     dec = _roundtrip(blob, np.concatenate(files))
     recs = dec.archive.records

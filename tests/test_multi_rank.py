@@ -1,6 +1,7 @@
 """The partition across ranks, on the CPU: shard() over several world sizes, and
-a two-process gloo run in which each rank decodes only its share (with the CPU
-oracle standing in for the GPU) and an all-gather rebuilds the full output."""
+a two-process gloo run in which each rank decodes only its slice (with the CPU
+oracle standing in for the GPU) and the library's in-place all-gather rebuilds the
+full output."""
 import os
 import socket
 
@@ -54,6 +55,39 @@ def test_shards_tile_the_output_and_carry_their_sources(world):
     assert max(costs) <= 1.6 * (sum(costs) / world) + int(r["rlen"].max()) * 2
 
 
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+def test_slices_tile_the_output_and_are_self_contained(world):
+    """Replica layout: equal slices; a rank's selection covers its slice and the sources of
+    every ref or delta in it."""
+    from lmz_b200 import archive, multi
+    blob, _src = _delta_archive()
+    ar = archive.Archive(blob)
+    r = ar.records
+    src = multi.sources(ar)
+    w = multi.slice_width(ar.total, world)
+    assert w % 256 == 0 and w * world >= ar.total
+    pos = 0
+    for rank in range(world):
+        select, (lo, hi) = multi.slice_shard(ar, rank, world)
+        assert lo == pos and hi - lo <= w
+        pos = hi
+        have = np.zeros(ar.total, dtype=bool)
+        plain = np.zeros(ar.total, dtype=bool)
+        for i in select:
+            have[int(r["dst"][i]):int(r["dst"][i]) + int(r["rlen"][i])] = True
+            if src[i] < 0:
+                plain[int(r["dst"][i]):int(r["dst"][i]) + int(r["rlen"][i])] = True
+        assert have[lo:hi].all()
+        for i in select:
+            if src[i] >= 0 and int(r["dst"][i]) < hi and int(r["dst"][i]) + int(r["rlen"][i]) > lo:
+                assert plain[src[i]:src[i] + int(r["rlen"][i])].all()
+    assert pos == ar.total
+    # an empty share plans to nothing
+    from lmz_b200 import plan
+    p = plan.build_plan(ar, select=np.zeros(0, dtype=np.int64), out_range=(0, 0))
+    assert p.chunks.size == 0 and p.total == 0
+
+
 def _rank_main(rank, world, port, blob_path, out_path):
     import torch
     import torch.distributed as dist
@@ -62,9 +96,10 @@ def _rank_main(rank, world, port, blob_path, out_path):
     from lmz_b200 import archive, multi
     blob = np.fromfile(blob_path, dtype=np.uint8)
     ar = archive.Archive(blob)
-    select, (lo, hi) = multi.shard(ar, rank, world)
+    select, (lo, hi) = multi.slice_shard(ar, rank, world)
+    width = multi.slice_width(ar.total, world)
     # decode the share with the CPU oracle: plain chunks first, then refs and deltas
-    out = np.zeros(ar.total, dtype=np.uint8)
+    out = np.zeros(width * world, dtype=np.uint8)
     oar = oa.Archive(blob)
     src = multi.sources(ar)
     for phase in (0, 1):
@@ -82,17 +117,13 @@ def _rank_main(rank, world, port, blob_path, out_path):
             else:
                 out[d:d + n] = codec.decode_chunk(pl, int(c["codec"]), int(c["esize"]),
                                                   int(c["flags"]), n, int(c["crc"]))
-    # all-gather of equal padded shards, as ShardedDecoder.all_gather does on NCCL
-    ranges = [None] * world
-    dist.all_gather_object(ranges, (lo, hi))
-    width = (max(b - a for a, b in ranges) + 15) & ~15
-    mine = torch.zeros(width, dtype=torch.uint8)
-    mine[:hi - lo] = torch.from_numpy(out[lo:hi].copy())
-    parts = [torch.empty(width, dtype=torch.uint8) for _ in range(world)]
-    dist.all_gather(parts, mine)
-    full = np.zeros(ar.total, dtype=np.uint8)
-    for rk, (a, b) in enumerate(ranges):
-        full[a:b] = parts[rk][:b - a].numpy()
+    # what lies outside this rank's slice must come from its peers: wipe it, then run the
+    # library's own in-place all-gather (the call ShardedDecoder.all_gather makes on NCCL)
+    out[:lo] = 0xEE
+    out[hi:] = 0xEE
+    buf = torch.from_numpy(out)
+    multi.gather_replica(buf, rank, world, width)
+    full = buf.numpy()[:ar.total]
     if rank == 0:
         full.tofile(out_path)
     dist.barrier()

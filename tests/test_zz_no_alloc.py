@@ -27,13 +27,18 @@ def _upload(blob, offs, pad):
     return d, o
 
 
-def test_noalloc_matches_the_device_entry_point_on_calls_in_a_row(gpu, orc):
-    import torch
+def _entry(gpu):
     lib = gpu.library()
     v, u = ctypes.c_void_p, ctypes.c_uint
     fn = lib.lmz_gpu_decode_batch_dev_noalloc
     fn.restype = ctypes.c_int
     fn.argtypes = [v, v, v, u, u, v, v, v]
+    return lib, fn
+
+
+def test_noalloc_matches_the_device_entry_point_on_calls_in_a_row(gpu, orc):
+    import torch
+    lib, fn = _entry(gpu)
     cs = torch.cuda.current_stream().cuda_stream
     pad = gpu.pad_bytes()
 
@@ -74,3 +79,58 @@ def test_noalloc_matches_the_device_entry_point_on_calls_in_a_row(gpu, orc):
     # beyond the fixed array's capacity: refused with a message, nothing launched
     rc = fn(None, None, None, 65537, 128, None, cs, None)
     assert rc == gpu.EUNSUPPORTED and "65536" in gpu.last_error()
+
+
+@pytest.mark.parametrize("nstr,plane,shared", [
+    (2000, 256, False),      # narrow per-stream tables
+    (12000, 64, False),      # compact tables; no index list may be allocated to sort them
+    (65536, 64, False),      # the fixed array's last word
+    (300, 512, True),        # one shared table, the plain kernel
+    (20000, 64, True),       # one shared table, the throughput kernel
+], ids=["narrow", "compact-unsorted", "capacity", "shared-plain", "shared-throughput"])
+def test_noalloc_every_launch_path_reports_its_own_stream(gpu, orc, nstr, plane, shared):
+    """Each launch path the entry point can take writes verdicts into the library's fixed
+    array: one truncated stream (cut on the host) must come back as status 2 with its
+    neighbours 0 and their bytes equal to the allocating entry point's, and the call must
+    leave the device's free memory where it was."""
+    import torch
+    lib, fn = _entry(gpu)
+    cs = torch.cuda.current_stream().cuda_stream
+    pool_n = 61
+    pool = [shaped("flat" if i % 5 else "skewed", plane, 3000 + i) for i in range(pool_n)]
+    hdr = None
+    if shared:
+        counts = np.sum([np.bincount(p, minlength=256) for p in pool], axis=0)
+        freqs = orc.rans_freqs(counts)
+        coded = [orc.rans_encode_shared(p, freqs) for p in pool]
+        hdr = torch.frombuffer(bytearray(b"R1\0\0" + freqs.astype("<u2").tobytes()), dtype=torch.uint8).cuda()
+    else:
+        coded = [orc.rans_encode(p) for p in pool]
+    victim = nstr // 2 + 1
+    streams = [coded[i % pool_n] for i in range(nstr)]
+    assert len(streams[victim]) > (32 if shared else 548) + 8, "the victim needs coded words to lose"
+    streams[victim] = streams[victim][:-6]
+    blob, offs = pack_streams(streams)
+    d, o = _upload(blob, offs, gpu.pad_bytes())
+    want = torch.zeros(nstr * plane, dtype=torch.uint8, device="cuda")
+    got = torch.zeros(nstr * plane, dtype=torch.uint8, device="cuda")
+    h = hdr.data_ptr() if hdr is not None else None
+    assert lib.lmz_gpu_decode_batch_dev(h, d.data_ptr(), o.data_ptr(), nstr, plane, want.data_ptr(), cs, 0) == 0
+    status = np.full(nstr, 0xFFFFFFFF, dtype=np.uint32)
+    fn(h, d.data_ptr(), o.data_ptr(), nstr, plane, got.data_ptr(), cs, status.ctypes.data)   # loads the kernels
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    status[:] = 0xFFFFFFFF
+    got.zero_()
+    rc = fn(h, d.data_ptr(), o.data_ptr(), nstr, plane, got.data_ptr(), cs, status.ctypes.data)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
+    assert rc == gpu.EBADSTREAM, gpu.last_error()
+    assert status[victim] == 2, status[victim]
+    others = np.delete(status, victim)
+    assert (others == 0).all(), np.unique(others)
+    g = got.cpu().numpy().reshape(nstr, plane)
+    w = want.cpu().numpy().reshape(nstr, plane)
+    keep = np.arange(nstr) != victim
+    assert (g[keep] == w[keep]).all()
+    assert (g[keep] == np.stack([pool[i % pool_n] for i in range(nstr)])[keep]).all()
