@@ -201,6 +201,10 @@ typedef struct lmz_decode_plan {
     void *d_chunk_status;       /* uint32 per chunk: 0 ok, 4 bad shape, 5 bad crc */
     void *d_chunk_crc;          /* computed crc32 per chunk, or NULL */
     void *d_any_bad;            /* uint32: bit 0 a stream failed, bit 1 a chunk failed */
+    void *d_fused_order;        /* NULL, or n_fused + 4 uint32 of work space: the library then counts
+                                 * every fused stream's alphabet on the device and sorts the jobs
+                                 * itself (n_fused_small and n_fused_f32_small are ignored, the jobs may
+                                 * come in any order within the BF16 and the 4-byte-element group) */
     uint32_t n_stream_jobs, n_seg_jobs, n_chunks, n_pieces, n_cond, n_cond_pieces, n_fused;
     uint32_t n_fused_small;     /* leading fused jobs whose streams have small alphabets (see
                                  * lmz_host_alphabet_sizes); they take the denser kernel instance */

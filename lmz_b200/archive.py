@@ -12,6 +12,7 @@ the struct-of-records the planner wants -- and is never expanded into objects.
 from __future__ import annotations
 
 import json
+import os
 import struct
 import zlib
 
@@ -62,8 +63,10 @@ class Archive:
     """Header, manifest and chunk records of one archive held in host memory."""
 
     def __init__(self, blob):
-        if isinstance(blob, (str, bytes)) and not isinstance(blob, bytes):
-            blob = np.fromfile(blob, dtype=np.uint8)
+        if isinstance(blob, (str, os.PathLike)):
+            # a file is mapped, not read: only the index at its end is touched here, and the
+            # payload pages are read when they are uploaded
+            blob = np.memmap(blob, dtype=np.uint8, mode="r")
         self.blob = blob if isinstance(blob, np.ndarray) else np.frombuffer(blob, dtype=np.uint8)
         b = self.blob
         if b.size < HEADER.size + FOOTER.size:
@@ -88,15 +91,23 @@ class Archive:
         self.members = self.manifest.get("members", [])
         self.total = int(sum(m["size"] for m in self.members))
         r = self.records
-        if r.size and int((r["off"].astype(np.uint64) + r["clen"]).max()) > self.table_off:
-            raise FormatError("a chunk payload points outside the payload region")
+        if r.size:
+            # every payload inside [header, table), compared without forming off + clen
+            # (an offset near 2^64 must not wrap into range)
+            off, room = r["off"], np.uint64(self.table_off)
+            inside = (off >= HEADER.size) & (off <= room)
+            inside &= r["clen"].astype(np.uint64) <= room - np.minimum(off, room)
+            if not inside.all():
+                raise FormatError("a chunk payload points outside the payload region")
 
     @property
     def page_mapped(self) -> bool:
         return bool(self.flags & FLAG_PAGE_MAPPED)
 
     def check_coverage(self) -> None:
-        """Chunks must tile [0, total) exactly (lmz/api.py:1038-1055)."""
+        """Chunks must tile [0, total) exactly (lmz/api.py:1038-1055).  Checked once."""
+        if getattr(self, "_covered", False):
+            return
         r = self.records
         order = np.argsort(r["dst"], kind="stable")
         dst = r["dst"][order].astype(np.int64)
@@ -109,6 +120,7 @@ class Archive:
         covered = int(end[-1]) if r.size else 0
         if covered != self.total:
             raise FormatError(f"archive covers {covered} bytes but declares {self.total}")
+        self._covered = True
 
     def tensor_index(self):
         """{(member path, tensor name): (dtype string, shape, start, end)} in the

@@ -188,6 +188,41 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         const uint32_t nsmall = p->n_fused_small < nbf ? p->n_fused_small : nbf;
         const uint32_t nsmall4 = p->n_fused_f32_small < p->n_fused_f32 ? p->n_fused_f32_small : p->n_fused_f32;
         auto part = [&](uint32_t cnt) { sa.jobs += sa.njobs; sa.status += sa.njobs; sa.njobs = cnt; };
+        if (p->d_fused_order) {
+            // the host has not looked at the tables: count alphabets here, small ones to the
+            // front of an index list, and give each class of each group its instance
+            uint32_t *order = (uint32_t *)p->d_fused_order, *counts = order + p->n_fused;
+            CK("memset fused counts", cudaMemsetAsync(counts, 0, 16, fs));
+            const uint32_t group_n[2] = {nbf, p->n_fused_f32};
+            for (int grp = 0; grp < 2; grp++) {
+                sa.njobs = group_n[grp];
+                sa.order = nullptr;
+                sa.count = nullptr;
+                if (sa.njobs) {
+                    k_classify<<<(sa.njobs + 7) / 8, 256, 0, fs>>>(sa, F_SMALL_LIVE, order, counts);
+                    cudaError_t le = cudaGetLastError();
+                    if (le != cudaSuccess) return fail_cuda("launch k_classify", le);
+                    sa.order = order;
+                    for (int big = 0; big < 2 && !rc; big++) {
+                        sa.count = counts + big;
+                        sa.order_from_back = big;
+                        const bool crc = p->d_piece_crc != nullptr;
+                        if (grp == 0)
+                            rc = big ? (crc ? launch_stream<SINK_BF16, true, 256>(sa, fs) : launch_stream<SINK_BF16, false, 256>(sa, fs))
+                                     : (crc ? launch_stream<SINK_BF16, true, F_SMALL_CFN>(sa, fs) : launch_stream<SINK_BF16, false, F_SMALL_CFN>(sa, fs));
+                        else
+                            rc = big ? (crc ? launch_stream<SINK_F32, true, 256>(sa, fs) : launch_stream<SINK_F32, false, 256>(sa, fs))
+                                     : (crc ? launch_stream<SINK_F32, true, F_SMALL_CFN>(sa, fs) : launch_stream<SINK_F32, false, F_SMALL_CFN>(sa, fs));
+                    }
+                    if (rc) return rc;
+                }
+                sa.jobs += group_n[grp];
+                sa.status += group_n[grp];
+                order += group_n[grp];
+                counts += 2;
+            }
+            sa.njobs = 0;            // nothing is left for the host-sorted launches below
+        } else {
         sa.njobs = nsmall;
         rc = p->d_piece_crc ? launch_stream<SINK_BF16, true, F_SMALL_CFN>(sa, fs)
                             : launch_stream<SINK_BF16, false, F_SMALL_CFN>(sa, fs);
@@ -204,6 +239,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         rc = p->d_piece_crc ? launch_stream<SINK_F32, true, 256>(sa, fs)
                             : launch_stream<SINK_F32, false, 256>(sa, fs);
         if (rc) return rc;
+        }
     }
 
     // 1. every rANS stream whose length is known up front, into scratch

@@ -713,7 +713,8 @@ __global__ void k_classify(StreamArgs a, uint32_t small_live, uint32_t *order, u
     if (job >= a.njobs) return;
     uint64_t soff;
     uint32_t slen;
-    if (a.sjobs) { soff = a.sjobs[job].src_off; slen = a.sjobs[job].src_len; }
+    if (a.jobs) { soff = a.jobs[job].src_off; slen = a.jobs[job].src_len; }
+    else if (a.sjobs) { soff = a.sjobs[job].src_off; slen = a.sjobs[job].src_len; }
     else { soff = a.offs[2 * job]; slen = (uint32_t)a.offs[2 * job + 1]; }
     uint32_t live = 0;
     if (slen >= HDR_BYTES + STATE_BYTES) {

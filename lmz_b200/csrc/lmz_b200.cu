@@ -133,8 +133,9 @@ static int launch_stream(const StreamArgs &a0, cudaStream_t cs)
     if (rc) return rc;
     constexpr unsigned groups = stream_groups(CFN, WARPS);
     unsigned per = groups;
-    if (!a.count) {
+    {
         // as many waves of CTAs as full CTAs would need, the streams spread evenly over them
+        // (when the device holds the count, as if every job of the launch were of this class)
         int sms = 0;
         rc = sm_count(&sms);
         if (rc) return rc;

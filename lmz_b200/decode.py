@@ -50,11 +50,13 @@ class ArchiveDecoder:
 
     `ar` is an `archive.Archive`, a path, or the archive's bytes.  With
     `checksum=False` the per-chunk crc32 is skipped (the reference's
-    `verify_checksums=False`).  `payload` may be given as an already-uploaded CUDA
-    uint8 tensor holding `plan.payload` followed by `gpu.pad_bytes()` of slack."""
+    `verify_checksums=False`).  `payload` may be given as a CUDA uint8 tensor with room
+    for `plan.payload`, the plan's host-inflated header chunks and `gpu.pad_bytes()` of
+    slack; the caller then brings the payload bytes there itself (`upload`, or copies of
+    its own) before `run`."""
 
     def __init__(self, ar, device=None, checksum: bool = True, out=None, plan=None,
-                 fuse=True):
+                 fuse=True, payload=None):
         import torch
 
         lib = gpu.library()
@@ -74,12 +76,16 @@ class ArchiveDecoder:
         with torch.cuda.device(d):
             pad = gpu.pad_bytes()
             nbytes = p.payload.size + p.extras.size
-            self.d_payload = torch.empty(nbytes + pad, dtype=torch.uint8, device=d)
+            if payload is not None and payload.numel() < nbytes + pad:
+                raise ValueError("the payload buffer is smaller than the plan's payload, header chunks and slack")
+            self.d_payload = payload if payload is not None else \
+                torch.empty(nbytes + pad, dtype=torch.uint8, device=d)
             self.h2d_bytes = int(nbytes)
             self.d_payload[nbytes:].zero_()
             if p.extras.size:
                 self.d_payload[p.payload.size:nbytes].copy_(torch.from_numpy(p.extras.copy()))
-            self.upload()
+            if payload is None:
+                self.upload()
             self.d_scratch = torch.empty(max(p.scratch_bytes, 64), dtype=torch.uint8, device=d)
             self.d_out = out if out is not None else \
                 torch.empty(p.total + 64, dtype=torch.uint8, device=d)
@@ -105,6 +111,7 @@ class ArchiveDecoder:
             self.d_chunk_status = torch.zeros(max(1, p.chunks.size), **u32)
             self.d_chunk_crc = torch.zeros(max(1, p.chunks.size), **u32)
             self.d_any_bad = torch.zeros(1, **u32)
+            self.d_fused_order = torch.zeros(p.fused_jobs.size + 4, **u32) if p.device_classify else None
             self.d_tabs = _crc_tables(lib, d)
         c = _chunks.DecodePlan()
         c.d_payload, c.d_scratch = self.d_payload.data_ptr(), self.d_scratch.data_ptr()
@@ -123,6 +130,7 @@ class ArchiveDecoder:
         c.d_crc_tables = self.d_tabs.data_ptr()
         c.d_chunk_status, c.d_chunk_crc = self.d_chunk_status.data_ptr(), self.d_chunk_crc.data_ptr()
         c.d_any_bad = self.d_any_bad.data_ptr()
+        c.d_fused_order = self.d_fused_order.data_ptr() if self.d_fused_order is not None else None
         c.n_stream_jobs, c.n_seg_jobs = p.stream_jobs.size, p.seg_jobs.size
         c.n_chunks, c.n_pieces = p.chunks.size, p.n_pieces
         c.n_cond, c.n_cond_pieces = ncond, p.cond_pieces.size
@@ -131,10 +139,13 @@ class ArchiveDecoder:
         self._c = c
         # kernels launched by one run(): stream decode, 3 cond kernels + segment decode,
         # up to four finish launches, the verdict kernel
-        self.launches_per_run = (1 if p.stream_jobs.size else 0) + (4 if ncond else 0) + \
-            (1 if p.n_fused_small else 0) + \
-            (1 if p.fused_jobs.size - p.n_fused_f32 > p.n_fused_small else 0) + \
-            (1 if p.n_fused_f32_small else 0) + (1 if p.n_fused_f32 > p.n_fused_f32_small else 0) + \
+        nbf = p.fused_jobs.size - p.n_fused_f32
+        if p.device_classify:                # per group: the count kernel and both instances
+            fused_launches = 3 * ((1 if nbf else 0) + (1 if p.n_fused_f32 else 0))
+        else:
+            fused_launches = (1 if p.n_fused_small else 0) + (1 if nbf > p.n_fused_small else 0) + \
+                (1 if p.n_fused_f32_small else 0) + (1 if p.n_fused_f32 > p.n_fused_f32_small else 0)
+        self.launches_per_run = (1 if p.stream_jobs.size else 0) + (4 if ncond else 0) + fused_launches + \
             int(sum(p.piece_split[i + 1] > p.piece_split[i] for i in (0, 1, 3, 4))) + 1
 
     def upload(self, pinned=None, non_blocking: bool = False):
@@ -234,15 +245,7 @@ class PipelinedDecoder:
         import torch
         self.archive = ar if isinstance(ar, fmt.Archive) else fmt.Archive(ar)
         r = self.archive.records
-        if nslices is None:
-            big = int((r["rlen"] >= (1 << 20)).sum())
-            nslices = 8 if big == 0 else max(1, min(8, big // 1900))
-        sourced = np.isin(r["codec"], (fmt.CODEC_REF, fmt.CODEC_DELTA)).any()
-        order = np.argsort(r["off"], kind="stable")
-        nslices = 1 if sourced or r.size < nslices else nslices
-        cum = np.cumsum(r["clen"][order].astype(np.int64))
-        cuts = np.searchsorted(cum, cum[-1] * np.arange(1, nslices) / nslices) if r.size else []
-        groups = [g for g in np.split(order, cuts) if g.size]
+        groups = _slice_groups(self.archive, nslices)
         self.device = torch.device(device if device is not None else
                                    f"cuda:{torch.cuda.current_device()}")
         out = torch.empty(self.archive.total + 64, dtype=torch.uint8, device=self.device)
@@ -274,9 +277,196 @@ class PipelinedDecoder:
             dec.run(stream=compute)
         return self.d_out[:self.archive.total]
 
+    def run_from_file(self, stream=None, staging=None):
+        """The same from the archive's own bytes wherever they are (a mapped file, the page
+        cache, ordinary memory): see `load_archive`, which also plans under the copies."""
+        import torch
+        compute = stream if stream is not None else torch.cuda.current_stream(self.device)
+        up = _Uploader(self.archive.blob, self.device, staging)
+        up.copy_stream.wait_stream(compute)
+        for dec, (lo, hi) in zip(self.slices, self.ranges):
+            up.send(lo, hi, dec.d_payload)
+        for si, dec in enumerate(self.slices):
+            compute.wait_event(up.wait(si))
+            dec.run(stream=compute)
+        up.close()
+        return self.d_out[:self.archive.total]
+
     def check(self):
         for dec in self.slices:
             dec.check()
+
+
+class Staging:
+    """Page-locked staging between a file and the device: `depth` buffers of `block`
+    bytes and the threads that fill and send them."""
+
+    _shared = None
+
+    def __init__(self, block: int = 32 << 20, depth: int = 6, threads: int = 4):
+        import concurrent.futures
+
+        import torch
+        if threads >= depth:
+            raise ValueError("staging needs more buffers than threads")
+        self.block, self.depth = block, depth
+        self.buffers = [torch.empty(block, dtype=torch.uint8).pin_memory() for _ in range(depth)]
+        self.views = [b.numpy() for b in self.buffers]
+        self.pool = concurrent.futures.ThreadPoolExecutor(threads)
+
+    @classmethod
+    def shared(cls):
+        if cls._shared is None:
+            cls._shared = cls()
+        return cls._shared
+
+
+class _Uploader:
+    """Byte ranges of a host array -> device tensors through `Staging`, in the background.
+
+    `send(lo, hi, dst)` queues one range ("a slice"); worker threads copy it block by
+    block into page-locked buffers and start each block's host -> device copy themselves on
+    one copy stream, so the caller is free to plan and launch meanwhile.  `wait(i)` blocks
+    until every block of the i-th range has been issued and returns a CUDA event that
+    completes when they have all arrived."""
+
+    def __init__(self, blob, device, staging=None):
+        import threading
+
+        import torch
+        self.blob, self.device = blob, device
+        self.st = staging if staging is not None else Staging.shared()
+        self.copy_stream = torch.cuda.Stream(device)
+        self.lock = threading.Lock()
+        self.slot_free = [None] * self.st.depth        # CUDA event: the slot's last copy has left it
+        self.nblocks = 0
+        self.left, self.ready, self.events, self.tasks = [], [], [], []
+
+    def send(self, lo: int, hi: int, dst):
+        import threading
+        si = len(self.left)
+        spans = [(b, min(b + self.st.block, hi)) for b in range(lo, hi, self.st.block)]
+        self.left.append(len(spans))
+        self.ready.append(threading.Event())
+        self.events.append(None)
+        if not spans:
+            self._finish(si)
+        for b, e in spans:
+            self.tasks.append(self.st.pool.submit(self._block, si, self.nblocks, b, e, dst[b - lo:e - lo]))
+            self.nblocks += 1
+        return si
+
+    def _finish(self, si):
+        import torch
+        with torch.cuda.stream(self.copy_stream):
+            ev = torch.cuda.Event()
+            ev.record(self.copy_stream)
+        self.events[si] = ev
+        self.ready[si].set()
+
+    def _block(self, si, index, lo, hi, dst):
+        import torch
+        try:
+            slot = index % self.st.depth
+            with torch.cuda.device(self.device):
+                if self.slot_free[slot] is not None:
+                    self.slot_free[slot].synchronize()
+                np.copyto(self.st.views[slot][:hi - lo], self.blob[lo:hi])
+                with self.lock:                      # one issuer at a time keeps stream order = event order
+                    with torch.cuda.stream(self.copy_stream):
+                        dst.copy_(self.st.buffers[slot][:hi - lo], non_blocking=True)
+                        ev = torch.cuda.Event()
+                        ev.record(self.copy_stream)
+                    self.slot_free[slot] = ev
+                    self.left[si] -= 1
+                    if self.left[si] == 0:
+                        self._finish(si)
+        except BaseException:
+            self.ready[si].set()                     # wake the waiter; result() re-raises below
+            raise
+
+    def wait(self, si):
+        self.ready[si].wait()
+        if self.events[si] is None:
+            for t in self.tasks:
+                t.result()                           # surfaces the worker's exception
+            raise RuntimeError("an upload block failed")
+        return self.events[si]
+
+    def close(self):
+        for t in self.tasks:
+            t.result()
+
+
+def _slice_groups(ar, nslices):
+    """Record indices of an archive cut into runs of consecutive payload bytes of about
+    equal size (refs and deltas read other chunks' output: one run then)."""
+    r = ar.records
+    if nslices is None:
+        big = int((r["rlen"] >= (1 << 20)).sum())
+        nslices = 8 if big == 0 else max(1, min(8, big // 1900))
+    sourced = np.isin(r["codec"], (fmt.CODEC_REF, fmt.CODEC_DELTA)).any()
+    order = np.argsort(r["off"], kind="stable")
+    nslices = 1 if sourced or r.size < nslices else nslices
+    cum = np.cumsum(r["clen"][order].astype(np.int64))
+    cuts = np.searchsorted(cum, cum[-1] * np.arange(1, nslices) / nslices) if r.size else []
+    return [g for g in np.split(order, cuts) if g.size]
+
+
+def load_archive(path, device=None, checksum: bool = True, nslices=None, stats=None, staging=None):
+    """File on disk -> verified plaintext in HBM (the load the reference times as "cold
+    disk -> VRAM", README.md:79-84).  The archive is mapped and its index read; its chunks
+    are cut into slices of consecutive payload bytes; background threads stream slice
+    after slice through page-locked staging to the device; each slice is planned while it
+    is on its way (after the copy has brought its pages in, so the planner's reads of the
+    in-payload headers cost nothing) and decoded as soon as it has arrived, under the
+    copies of the next; every chunk's verdict is checked at the end.  Returns the decoded
+    output space as a device tensor.  `stats`, a dict, receives `open_s` (map + index),
+    `run_s` (everything else), `plan_s` (planning inside run_s), `h2d_bytes`, `slices`."""
+    import time
+
+    import torch
+    t0 = time.perf_counter()
+    ar = fmt.Archive(path)
+    ar.check_coverage()
+    dev = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+    r = ar.records
+    groups = _slice_groups(ar, nslices)
+    t1 = time.perf_counter()
+    with torch.cuda.device(dev):
+        out = torch.empty(ar.total + 64, dtype=torch.uint8, device=dev)
+        compute = torch.cuda.current_stream(dev)
+        up = _Uploader(ar.blob, dev, staging)
+        pad = gpu.pad_bytes()
+        spans, payloads = [], []
+        for g in groups:
+            lo = int(r["off"][g].min())
+            hi = int((r["off"][g].astype(np.int64) + r["clen"][g]).max())
+            # room behind the payload for header chunks the planner inflates on the host
+            general = (r["codec"][g] == fmt.CODEC_ZSTD) & np.isin(r["flags"][g] & 3, (fmt.METHOD_ZSTD, fmt.METHOD_DEFLATE))
+            extra = int(r["rlen"][g][general].sum())
+            d = torch.empty(hi - lo + extra + pad, dtype=torch.uint8, device=dev)
+            spans.append((lo, hi))
+            payloads.append(d)
+            up.send(lo, hi, d)
+        decs, plan_s = [], 0.0
+        for si, g in enumerate(groups):
+            arrived = up.wait(si)                    # every block of the slice has been read and issued
+            tp = time.perf_counter()
+            p = planner.build_plan(ar, select=g, payload_range=spans[si])
+            dec = ArchiveDecoder(ar, device=dev, checksum=checksum, out=out, plan=p, payload=payloads[si])
+            plan_s += time.perf_counter() - tp
+            compute.wait_event(arrived)
+            dec.run(stream=compute)
+            decs.append(dec)
+        up.close()
+        for dec in decs:
+            dec.check()
+        torch.cuda.synchronize(dev)
+    if stats is not None:
+        stats.update(open_s=t1 - t0, run_s=time.perf_counter() - t1, plan_s=plan_s,
+                     h2d_bytes=sum(hi - lo for lo, hi in spans), slices=len(groups))
+    return out[:ar.total]
 
 
 def decode_tensors(ar, names, device=None, checksum: bool = True):

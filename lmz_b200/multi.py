@@ -23,6 +23,10 @@ def sources(ar: fmt.Archive) -> np.ndarray:
     src = np.full(r.size, -1, dtype=np.int64)
     idx = np.nonzero((r["codec"] == fmt.CODEC_REF) | (r["codec"] == fmt.CODEC_DELTA))[0]
     if idx.size:
+        # a ref payload is the 8-byte source; a delta payload starts with it and an inner codec id
+        short = r["clen"][idx] < np.where(r["codec"][idx] == fmt.CODEC_REF, 8, 9)
+        if short.any():
+            raise fmt.CorruptArchive("a ref or delta chunk is too short to name its source")
         off = r["off"][idx].astype(np.int64)
         raw = blob[off[:, None] + np.arange(8, dtype=np.int64)[None, :]]
         src[idx] = np.ascontiguousarray(raw).view("<u8")[:, 0].astype(np.int64)

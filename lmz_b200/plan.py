@@ -69,6 +69,7 @@ class Plan:
     n_fused_f32_small: int = 0     # the first of those, with at most SMALL_LIVE live symbols
     stream_owner: np.ndarray = field(default=None)   # record index of each stream job
     coded_bytes: int = 0           # sum of clen: algorithmic bytes read
+    device_classify: bool = False  # the fused jobs are not sorted by alphabet: the library counts on the device
     base_bytes: int = 0            # bytes of delta bases read back
 
     @property
@@ -109,7 +110,7 @@ def _align16(x):
 
 
 def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
-               out_range=None) -> Plan:
+               out_range=None, classify: str = "device") -> Plan:
     """`fuse` routes BF16 chunks whose exponent plane is rANS and whose sign/mantissa
     plane is stored to the fused decode+merge+checksum kernel (no scratch plane), and
     4-byte-element chunks whose top byte plane alone is coded likewise when there are
@@ -120,7 +121,11 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
     payload must lie inside); offsets in the plan are then relative to `lo`.
     `out_range` = (lo, hi) decodes into a buffer that holds only those bytes of the
     output space (every selected chunk, and the sources of selected refs and deltas,
-    must lie inside); `Plan.total` is then hi - lo."""
+    must lie inside); `Plan.total` is then hi - lo.
+    `classify`: which side counts the live symbols of each fused stream's table to give
+    small alphabets the denser kernel instance -- "device" (a kernel, after the upload; the
+    host then never touches the payload's stream headers) or "host" (here, with numpy or
+    the library's host helper)."""
     ar.check_coverage()
     r = ar.records if select is None else ar.records[np.asarray(select, dtype=np.int64)]
     lo, hi = (0, int(ar.table_off)) if payload_range is None else map(int, payload_range)
@@ -380,7 +385,8 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
     fpos = np.nonzero(g == 2)[0]                    # fused chunks, in launch order ...
     whole = f_len[corder[fpos]] >= 548              # table + states present (else the kernel rejects it)
     small = np.zeros(fpos.size, dtype=bool)
-    small[whole] = _alphabet_sizes(blob, f_src[corder[fpos]][whole]) <= SMALL_LIVE
+    if classify == "host":
+        small[whole] = _alphabet_sizes(blob, f_src[corder[fpos]][whole]) <= SMALL_LIVE
     wide4 = esize[corder[fpos]] == 4                # ... BF16 before 4-byte elements,
     fpos = np.concatenate([fpos[~wide4 & small], fpos[~wide4 & ~small],     # small alphabets first
                            fpos[wide4 & small], fpos[wide4 & ~small]])
@@ -398,7 +404,8 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
                 cond_pieces=cond_pieces, stream_owner=s_owner[order], fused_jobs=fused_jobs,
                 n_fused_small=int((~wide4 & small).sum()), n_fused_f32=int(wide4.sum()),
                 n_fused_f32_small=int((wide4 & small).sum()),
-                coded_bytes=int(clen.sum()), base_bytes=int(rlen[is_delta].sum()))
+                coded_bytes=int(clen.sum()), base_bytes=int(rlen[is_delta].sum()),
+                device_classify=classify != "host")
 
 
 def _inflate(raw: bytes) -> bytes:

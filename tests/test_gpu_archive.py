@@ -11,10 +11,11 @@ from oracle import archive as oa, synth
 pytestmark = pytest.mark.gpu
 
 
-def _roundtrip(blob, source, checksum=True, fuse=True):
+def _roundtrip(blob, source, checksum=True, fuse=True, classify="device"):
     import zlib
-    from lmz_b200 import decode
-    dec = decode.ArchiveDecoder(blob, checksum=checksum, fuse=fuse)
+    from lmz_b200 import archive, decode, plan
+    ar = archive.Archive(blob)
+    dec = decode.ArchiveDecoder(ar, checksum=checksum, plan=plan.build_plan(ar, fuse=fuse, classify=classify))
     dec.run()
     dec.check()
     got = dec.output.cpu().numpy()
@@ -58,9 +59,10 @@ def test_wide_exponent_alphabets_take_the_large_table_instance():
     narrow = synth.normal_bf16(300_000, 5)
     src = synth.safetensors_bytes([("wide", "BF16", (n,), wide), ("narrow", "BF16", (300_000,), narrow)])
     blob = oa.write_archive([("m.safetensors", src)], mapped=True)
-    p = plan.build_plan(archive.Archive(blob))
+    p = plan.build_plan(archive.Archive(blob), classify="host")
     assert 0 < p.n_fused_small < p.fused_jobs.size, (p.n_fused_small, p.fused_jobs.size)
-    _roundtrip(blob, src)
+    _roundtrip(blob, src, classify="host")
+    _roundtrip(blob, src, classify="device")
 
 
 def test_without_checksums(shard):
@@ -337,3 +339,46 @@ def test_per_rank_tensor_parallel_slices():
         dec = _roundtrip(oa.write_archive([(f"rank{rank}.safetensors", src)]), src)
         t = dec.tensors()[(f"rank{rank}.safetensors", "o.weight")]
         assert t.cpu().numpy().tobytes() == row.tobytes()
+
+
+def test_load_archive_streams_a_file_through_staging(shard, tmp_path):
+    """decode.load_archive: file -> page-locked staging -> HBM with the decode of earlier
+    slices under the copies; small staging blocks here so that every slice takes several."""
+    from lmz_b200 import decode
+    for kw in (dict(mapped=True), dict()):
+        blob = oa.write_archive([("m.safetensors", shard)], **kw)
+        path = tmp_path / f"a{len(kw)}.lmz"
+        path.write_bytes(blob)
+        stats = {}
+        out = decode.load_archive(str(path), stats=stats)
+        assert (out.cpu().numpy() == shard).all()
+        assert stats["h2d_bytes"] <= len(blob) and stats["run_s"] > 0
+        ar = decode.fmt.Archive(str(path))
+        pd = decode.PipelinedDecoder(ar)
+        small = decode.Staging(block=1 << 16, depth=3, threads=2)
+        assert (pd.run_from_file(staging=small).cpu().numpy() == shard).all()
+        pd.check()
+
+
+def test_host_and_device_classification_agree(shard):
+    """The fused jobs sorted by alphabet on the host (numpy / the library's host helper) and
+    on the device (k_classify) decode to the same bytes, wide alphabets included."""
+    rng = np.random.default_rng(12)
+    n = 400_000
+    e = np.minimum(rng.geometric(0.03, n) - 1, 199).astype(np.uint16)
+    b = rng.integers(0, 256, n).astype(np.uint16)
+    wide = (((b & 0x80) << 8) | (e << 7) | (b & 0x7F)).astype("<u2").view(np.uint8)
+    f32 = (rng.standard_normal(300_000) * 0.02).astype("<f4").view(np.uint8)
+    src = synth.safetensors_bytes([("wide", "BF16", (n,), wide), ("narrow", "BF16", (200_000,), synth.normal_bf16(200_000, 6))])
+    src2 = synth.safetensors_bytes([("f", "F32", (300_000,), f32)])
+    both = np.concatenate([src, src2])
+    blob = oa.write_archive([("a.safetensors", src), ("b.safetensors", src2)], mapped=True)
+    from lmz_b200 import archive, decode, plan
+    ar = archive.Archive(blob)
+    for classify in ("host", "device"):
+        p = plan.build_plan(ar, fuse="all", classify=classify)
+        assert p.device_classify == (classify == "device") and p.n_fused_f32 > 0
+        dec = decode.ArchiveDecoder(ar, plan=p)
+        dec.run()
+        dec.check()
+        assert (dec.output.cpu().numpy() == both).all()

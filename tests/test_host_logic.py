@@ -210,6 +210,16 @@ def test_planner_rejects_hostile_records(shard):
     with pytest.raises(archive.FormatError):
         archive.Archive(_rewrite_table(blob, outside))
 
+    def wraps(r):                                  # off + clen would wrap past 2^64 into range
+        r["off"][1] = (1 << 64) - 8
+
+    def in_header(r):
+        r["off"][1] = 4
+
+    for hostile in (wraps, in_header):
+        with pytest.raises(archive.FormatError, match="outside the payload"):
+            archive.Archive(_rewrite_table(blob, hostile))
+
     def unknown_codec(r):
         r["codec"][1] = 7
 
