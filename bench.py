@@ -56,11 +56,18 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    ap.add_argument("--model", default="llama-3.1-8b", choices=sorted(MODELS))
+    ap.add_argument("--model", default="llama-3.1-8b", choices=sorted(MODELS) + ["stress"],
+                    help="a model archive, or 'stress': the decoder stress batch matrix (batch decode entry point)")
+    ap.add_argument("--stress-pool", type=int, default=256, help="distinct streams per (distribution, length)")
+    ap.add_argument("--stress-lengths", default="1,17,4096,65536,1048576,4194304")
+    ap.add_argument("--stress-batches", default="1,7,64,4096")
     ap.add_argument("--layout", default="mapped", choices=("mapped", "default"),
                     help="mapped = 64 KiB blocks (lmz compress --mapped); default = 8 MiB chunks")
     ap.add_argument("--chunk-size", type=int, default=0, help="override the layout's chunk size")
     ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--shared-tables", type=int, default=0,
+                    help="write the archive with the shared-table option: one exponent table per run of N BF16 chunks "
+                         "(a multiple of 80 fills the decoder's thread blocks)")
     ap.add_argument("--no-crc", action="store_true", help="skip the per-chunk crc32")
     ap.add_argument("--no-fuse", action="store_true",
                     help="decode planes to scratch and merge in k_finish instead of the fused kernel")
@@ -72,7 +79,8 @@ def parse_args():
 def workload_name(a) -> str:
     cs = a.chunk_size or ((64 << 10) if a.layout == "mapped" else (8 << 20))
     dt = "f32" if MODELS[a.model].get("kind") == "xlmr" else "bf16"
-    return f"{a.model} {dt} N(0,0.02) seed {a.seed}, lmz archive, {cs >> 10} KiB chunks"
+    st = f", one shared exponent table per {a.shared_tables} chunks" if getattr(a, "shared_tables", 0) else ""
+    return f"{a.model} {dt} N(0,0.02) seed {a.seed}, lmz archive, {cs >> 10} KiB chunks{st}"
 
 
 def per_rank_archives(a) -> bool:
@@ -80,12 +88,12 @@ def per_rank_archives(a) -> bool:
     return MODELS[a.model].get("tp", 1) > 1
 
 
-def archive_key(model: str, layout: str, chunk_size: int, seed: int) -> str:
-    return f"lmzb200-{model}-{layout}-{chunk_size}-{seed}"
+def archive_key(model: str, layout: str, chunk_size: int, seed: int, shared_tables: int = 0) -> str:
+    return f"lmzb200-{model}-{layout}-{chunk_size}-{seed}" + (f"-t{shared_tables}" if shared_tables else "")
 
 
 def build_archive(model: str, layout: str, chunk_size: int = 0, seed: int = 1, nproc=None,
-                  want_files: bool = False):
+                  want_files: bool = False, shared_tables: int = 0):
     """The synthetic archive of a workload, written by the checker's reference-exact
     writer.  Returns (archive bytes, files) where files is [(relative path, bytes)] of
     the model's source files when `want_files` (else None)."""
@@ -96,10 +104,12 @@ def build_archive(model: str, layout: str, chunk_size: int = 0, seed: int = 1, n
     cs = chunk_size or None
     if kind == "chain":
         files = [(f"step{i}/model.safetensors", f) for i, f in enumerate(synth.delta_chain_files(**m))]
-        blob = np.frombuffer(oa.write_archive(files, chunk_size=cs, mapped=mapped), dtype=np.uint8)
+        blob = np.frombuffer(oa.write_archive(files, chunk_size=cs, mapped=mapped, shared_tables=shared_tables),
+                             dtype=np.uint8)
         return blob, (files if want_files else None)
     spec = m["spec"] if kind == "spec" else synth.xlmr_spec(**m) if kind == "xlmr" else synth.llama_spec(**m)
-    blob, layouts = bigwrite.write_model_archive(spec, seed=seed, chunk_size=cs, mapped=mapped, nproc=nproc)
+    blob, layouts = bigwrite.write_model_archive(spec, seed=seed, chunk_size=cs, mapped=mapped, nproc=nproc,
+                                                 shared_tables=shared_tables)
     files = None
     if want_files:
         files = [(f"model-{i + 1:05d}-of-{len(layouts):05d}.safetensors", lay.bytes(0, lay.size))
@@ -133,7 +143,8 @@ def pin_status(key: str, blob) -> str:
     except OSError:
         pin = None
     if pin is None:
-        return "no pin for this workload"
+        return ("no pin: the shared-table option is this repository's format extension" if "-t" in key.rsplit("-", 1)[-1]
+                else "no pin for this workload")
     d = archive_digests(blob)
     if d["payload_sha256"] != pin["payload_sha256"] or d["records_sha256"] != pin["records_sha256"]:
         raise SystemExit(f"the generated archive {key} differs from the reference-written pin")
@@ -146,12 +157,13 @@ def get_archive(a, rank: int, barrier) -> np.ndarray:
     its reference-written pin; the verdict is kept beside the cached file."""
     own = per_rank_archives(a)
     seed = a.seed * 64 + rank if own else a.seed
-    key = archive_key(a.model, a.layout, a.chunk_size, seed)
+    key = archive_key(a.model, a.layout, a.chunk_size, seed, getattr(a, "shared_tables", 0))
     cache = os.path.join("/dev/shm" if os.path.isdir("/dev/shm") else "/tmp", key + ".lmz")
     if (own or rank == 0) and (a.no_cache or not os.path.exists(cache)):
         t = time.time()
         nproc = max(1, (os.cpu_count() or 1) // int(os.environ.get("LOCAL_WORLD_SIZE", "1"))) if own else None
-        blob, _ = build_archive(a.model, a.layout, a.chunk_size, seed, nproc=nproc)
+        blob, _ = build_archive(a.model, a.layout, a.chunk_size, seed, nproc=nproc,
+                                shared_tables=getattr(a, "shared_tables", 0))
         with open(cache + ".pin", "w") as f:
             f.write(pin_status(key, blob))
         tmp = cache + f".{os.getpid()}"
@@ -166,7 +178,8 @@ def get_archive(a, rank: int, barrier) -> np.ndarray:
 
 def archive_pin(a, rank: int = 0) -> str:
     own = per_rank_archives(a)
-    key = archive_key(a.model, a.layout, a.chunk_size, a.seed * 64 + rank if own else a.seed)
+    key = archive_key(a.model, a.layout, a.chunk_size, a.seed * 64 + rank if own else a.seed,
+                      getattr(a, "shared_tables", 0))
     try:
         with open(os.path.join("/dev/shm" if os.path.isdir("/dev/shm") else "/tmp", key + ".lmz.pin")) as f:
             return f.read()
@@ -235,13 +248,12 @@ _CPU = {}
 
 def _cpu_work(span):
     """Decode records[lo:hi] of the sample in a worker process (reference C core)."""
-    from oracle import codec
+    from oracle import archive as oa
     ar, picks, lib = _CPU["ar"], _CPU["picks"], _CPU["lib"]
     done = 0
     for i in picks[span[0]:span[1]]:
         c = ar.records[i]
-        codec.decode_chunk(ar.payload(c), int(c["codec"]), int(c["esize"]), int(c["flags"]),
-                           int(c["rlen"]), int(c["crc"]), True, lib)
+        oa._decode_plain(ar, c, True, lib)
         done += int(c["rlen"])
     return done
 
@@ -303,6 +315,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if a.model == "stress":
+        return run_stress(a, rank)
     if a.impl == "reference":
         return run_reference(a, rank)
     import torch
@@ -511,26 +525,28 @@ def main():
     peak, peak_kind = measured_peak()
     # dominant kernel: the one with the largest device time
     # algorithmic bytes of each kernel: what it must read plus what it must write
-    fj = p.fused_jobs
+    fj, tj = p.fused_jobs[:p.n_fused], p.fused_jobs[p.n_fused:]      # own tables; shared tables (BF16)
     # element size of each fused job: BF16 chunks first, 4-byte-element chunks last
     fes = np.full(fj.size, 2, dtype=np.int64)
     fes[fj.size - p.n_fused_f32:] = 4
-    f_stored = int(((fes - 1) * fj["n"]).sum())        # stored planes read by the fused kernel
-    f_plain = int((fes * fj["n"]).sum())
-    fused_bytes = int(fj["src_len"].sum()) + f_stored + f_plain           # stream + planes in, plaintext out
+    f_stored = int(((fes - 1) * fj["n"]).sum() + tj["n"].sum())      # stored planes read by the fused kernel
+    f_plain = int((fes * fj["n"]).sum() + 2 * tj["n"].sum())
+    f_coded = int(fj["src_len"].sum() + tj["src_len"].sum())
+    fused_bytes = f_coded + f_stored + f_plain                        # stream + planes in, plaintext out
     stream_bytes = int(p.stream_jobs["src_len"].sum() + p.stream_jobs["n"].sum())
     fin_plain = plain - f_plain
-    finish_bytes = int(coded - fj["src_len"].sum() - f_stored - p.stream_jobs["src_len"].sum()
+    finish_bytes = int(coded - f_coded - f_stored - p.stream_jobs["src_len"].sum()
                        + p.stream_jobs["n"].sum() + fin_plain + p.base_bytes)
     kbytes = {"stream_decode": stream_bytes, "finish": finish_bytes, "fused": fused_bytes}
     kname = {"stream_decode": "k_rans / k_stream<bytes>", "finish": "k_finish",
-             "fused": "k_stream<f32>" if p.n_fused_f32 * 2 > fj.size else "k_stream<bf16>"}
+             "fused": "k_stream<f32>" if p.n_fused_f32 * 2 > fj.size + tj.size else
+                      "k_stream<bf16, shared tables>" if tj.size > fj.size else "k_stream<bf16>"}
     dom = max(kbytes, key=lambda k: phase_ms[k])
     dom_bytes = kbytes[dom]
     achieved = dom_bytes / (phase_ms[dom] / 1e3) / 1e9
     whole = (coded + plain + p.base_bytes) / (ms / a.steps / 1e3) / 1e9
     traffic = None
-    if dom == "fused" and not p.n_fused_f32:
+    if dom == "fused" and not p.n_fused_f32 and not p.n_fused_t:
         # DRAM bytes of one launch, scaled from the committed ncu capture of a smaller
         # archive of the same chunks (traffic is proportional to the chunks processed)
         try:
@@ -582,6 +598,173 @@ def main():
         dist.destroy_process_group()
 
 
+_STRESS = {}
+
+
+def _stress_make(args):
+    """(plaintext, per-stream-table stream, histogram) of one pool stream, in a worker process."""
+    from oracle import native, synth
+    dist, n, i = args
+    plain = synth.stress_plane(dist, n, 7919 * i + n)
+    return plain, native.best().rans_encode(plain), np.bincount(plain, minlength=256)
+
+
+def _stress_shared(args):
+    from oracle import native
+    plain, freqs = args
+    return native.best().rans_encode_shared(plain, freqs)
+
+
+def run_stress(a, rank: int):
+    """The decoder stress matrix: 8 symbol distributions x stream lengths x batch sizes, each
+    batch decoded through `lmz_gpu_decode_batch_dev` once with per-stream frequency tables
+    and once with one shared table, device resident, CUDA events, best of 5 after 3 warm-up
+    launches, every cell's output compared with the plaintext on the device.  Streams come
+    from a pool of `--stress-pool` distinct ones per (distribution, length), written by the
+    reference-exact CPU encoder and cycled when a batch is larger than the pool.  Where the
+    reference's own CUDA decoder (oracle/_ref/liblmzgpu.so) accepts the shape (plane a multiple
+    of 128) it is timed on the same device buffers."""
+    if rank != 0:
+        return
+    import ctypes
+    import multiprocessing as mp
+
+    import torch
+
+    from lmz_b200 import gpu
+    from oracle import native, synth
+    ok, why = gpu.available()
+    if not ok:
+        raise SystemExit(f"the CUDA library is unavailable: {why}")
+    lib = gpu.library()
+    sig = [ctypes.c_void_p] * 3 + [ctypes.c_uint, ctypes.c_uint, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint]
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "liblmzgpu.so")
+    ref = ctypes.CDLL(ref_path) if os.path.exists(ref_path) else None
+    if ref is not None:
+        ref.lmz_gpu_decode_batch_dev.restype = ctypes.c_int
+        ref.lmz_gpu_decode_batch_dev.argtypes = sig
+    lengths = [int(x) for x in a.stress_lengths.split(",")]
+    batches = [int(x) for x in a.stress_batches.split(",")]
+    cs = torch.cuda.current_stream().cuda_stream
+    pad = gpu.pad_bytes()
+    cells, tot_bytes, tot_ms, peak = [], 0, 0.0, measured_peak()[0]
+    best_cell = None
+    clk_ctx = ClockSampler(0)
+    t_start = time.time()
+    with clk_ctx as clk, mp.get_context("fork").Pool(os.cpu_count() or 1) as pool:
+        for dist in synth.STRESS_DISTRIBUTIONS:
+            for n in lengths:
+                P = max(1, min(a.stress_pool, max(batches)))
+                made = pool.map(_stress_make, [(dist, n, i) for i in range(P)], chunksize=max(1, P // 64))
+                plains = [m[0] for m in made]
+                freqs = native.best().rans_freqs(np.sum([m[2] for m in made], axis=0))
+                shared = pool.map(_stress_shared, [(pl, freqs) for pl in plains], chunksize=max(1, P // 64))
+                d_plain = torch.from_numpy(np.stack(plains)).cuda()
+                hdr = torch.frombuffer(bytearray(b"R1\0\0" + freqs.astype("<u2").tobytes()), dtype=torch.uint8).cuda()
+                for kind, streams in (("per-stream", [m[1] for m in made]), ("shared", shared)):
+                    lens = np.array([len(x) for x in streams], dtype=np.int64)
+                    starts = np.cumsum(lens) - lens
+                    d_blob = torch.zeros(int(lens.sum()) + pad, dtype=torch.uint8, device="cuda")
+                    d_blob[:int(lens.sum())] = torch.frombuffer(bytearray(b"".join(streams)), dtype=torch.uint8).cuda()
+                    for B in batches:
+                        idx = np.arange(B) % P
+                        offs = np.empty(2 * B, dtype=np.int64)
+                        offs[0::2], offs[1::2] = starts[idx], lens[idx]
+                        d_off = torch.from_numpy(offs).cuda()
+                        out = torch.empty(B * n, dtype=torch.uint8, device="cuda")
+                        h = hdr.data_ptr() if kind == "shared" else None
+
+                        def timed(fn):
+                            best = None
+                            for it in range(8):
+                                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                                e0.record()
+                                rc = fn(h, d_blob.data_ptr(), d_off.data_ptr(), B, n, out.data_ptr(), cs, 0)
+                                e1.record()
+                                torch.cuda.synchronize()
+                                if rc != 0:
+                                    return None
+                                if it >= 3:
+                                    best = e0.elapsed_time(e1) if best is None else min(best, e0.elapsed_time(e1))
+                            return best
+
+                        def same():
+                            got = out.view(B, n)
+                            return all(torch.equal(got[r0:r0 + P], d_plain[:min(P, B - r0)]) for r0 in range(0, B, P))
+
+                        out.zero_()
+                        ms = timed(lib.lmz_gpu_decode_batch_dev)
+                        if ms is None:
+                            raise SystemExit(f"stress cell {dist}/{n}/{B}/{kind} failed: {gpu.last_error()}")
+                        if not same():
+                            raise SystemExit(f"stress cell {dist}/{n}/{B}/{kind} decoded to the wrong bytes")
+                        cell = {"dist": dist, "len": n, "batch": B, "tables": kind, "ms": round(ms, 4),
+                                "gbps": round(B * n / ms / 1e6, 2), "ref_gbps": None}
+                        if ref is not None and n % 128 == 0:
+                            out.zero_()
+                            rms = timed(ref.lmz_gpu_decode_batch_dev)
+                            if rms is not None:
+                                if not same():
+                                    raise SystemExit(f"the reference's decoder differs on {dist}/{n}/{B}/{kind}")
+                                cell["ref_gbps"] = round(B * n / rms / 1e6, 2)
+                        moved = int(lens[idx].sum()) + B * n
+                        cell["hbm_frac"] = round(moved / ms / 1e6 / peak, 4)
+                        cells.append(cell)
+                        tot_bytes += B * n
+                        tot_ms += ms
+                        if best_cell is None or cell["gbps"] > best_cell["gbps"]:
+                            best_cell = dict(cell, moved=moved)
+                        del out, d_off
+                    del d_blob
+                del d_plain
+                print(f"[stress] {dist} {n}: {time.time() - t_start:.0f}s", file=sys.stderr)
+    # CPU baseline: the reference-exact CPU decoder on one cell's pool, every core
+    cpu = cpu_stress_baseline(a)
+    value = tot_bytes / tot_ms / 1e6
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": 1, "steps": 5, "warmup": 3,
+        "ms_per_step": round(tot_ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "decoder stress batch: 8 distributions x lengths x batch sizes x {per-stream, shared} tables, "
+                               "lmz_gpu_decode_batch_dev", "lengths": lengths, "batches": batches,
+                   "pool": f"{a.stress_pool} distinct streams per (distribution, length), cycled in larger batches",
+                   "value_is": "total symbols of all cells / total best-of-5 time of all cells",
+                   "l2": "the largest cells stream up to 17 GB per launch; small cells fit the 126 MB L2 and are launch-bound"},
+        "clocks": clk.summary(),
+        "e2e": None, "gpu_launches": len(cells) * 8,
+        "roofline": {"bound": "hbm", "kernel": "k_stream<bytes> / k_rans", "achieved": round(best_cell["moved"] / best_cell["ms"] / 1e6, 1),
+                     "peak": peak, "unit": "GB/s", "frac": best_cell["hbm_frac"], "traffic": None,
+                     "cell": {k: best_cell[k] for k in ("dist", "len", "batch", "tables")}},
+        "cpu_baseline": cpu,
+        "cells": cells,
+    }
+    emit(line)
+
+
+def cpu_stress_baseline(a):
+    """`lmz_rans_decode` of the reference's C core (the checker's port where it is absent) over
+    64 exponent-like streams of 1 Mi symbols, one worker process per core."""
+    import multiprocessing as mp
+    from oracle import native
+    made = [_stress_make(("exponent", 1 << 20, i)) for i in range(8)]
+    _STRESS["streams"] = [m[1] for m in made]
+    threads = os.cpu_count() or 1
+    with mp.get_context("fork").Pool(threads) as pool:
+        pool.map(_stress_decode, range(threads))
+        t = time.perf_counter()
+        done = sum(pool.map(_stress_decode, range(threads * 8)))
+        dt = time.perf_counter() - t
+    return {"value": round(done / dt / 1e9, 3), "unit": "GB/s", "cores": threads,
+            "kind": "reference" if native.ref() is not None else "port",
+            "sample": f"{threads * 8} decodes of 1 Mi-symbol exponent-like streams, {threads} worker processes"}
+
+
+def _stress_decode(i):
+    from oracle import native
+    s = _STRESS["streams"][i % len(_STRESS["streams"])]
+    return int(native.best().rans_decode(s, 1 << 20).size)
+
+
 def batch_decode_compare(dec, p):
     """`lmz_gpu_decode_batch_dev` on the archive's own exponent streams (device resident,
     per-stream tables, 32768 symbols each): this library, and the reference's CUDA decoder
@@ -591,7 +774,7 @@ def batch_decode_compare(dec, p):
     import ctypes
     import torch
     from lmz_b200 import gpu
-    fj = p.fused_jobs
+    fj = p.fused_jobs[:p.n_fused]
     sel = np.nonzero(fj["n"] == 32768)[0][:65536]
     if sel.size < 1024:
         return None
@@ -706,6 +889,8 @@ def cpu_baseline_subprocess(a):
            "--cpu-sample-mb", str(a.cpu_sample_mb)]
     if a.chunk_size:
         cmd += ["--chunk-size", str(a.chunk_size)]
+    if a.shared_tables:
+        cmd += ["--shared-tables", str(a.shared_tables)]
     if a.no_cache:
         cmd += ["--no-cache"]
     env = dict(os.environ)
@@ -747,8 +932,7 @@ def verify_sample(dec, blob, nsample: int = 24):
         c = recs[i]
         if c["codec"] in (codec.CODEC_REF, codec.CODEC_DELTA):
             continue
-        want = codec.decode_chunk(ar.payload(c), int(c["codec"]), int(c["esize"]), int(c["flags"]),
-                                  int(c["rlen"]), int(c["crc"]), True)
+        want = oa._decode_plain(ar, c, True, None)
         got = out[int(c["dst"]):int(c["dst"]) + int(c["rlen"])].cpu().numpy()
         if not (got == want).all():
             raise SystemExit(f"chunk {i} differs from the CPU oracle")

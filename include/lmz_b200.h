@@ -86,7 +86,8 @@ int lmz_gpu_set_device(int device);
  * streams that carry their own table.  -1 = by batch size (default), 0 = narrow
  * (5 KiB per stream), 2 = compact (2 KiB, the most streams per SM), 3 = a wide
  * 16 KiB table per stream (one lookup per symbol; 12 streams per SM, for launches
- * small enough to be bound by per-symbol latency).  A tuning and testing knob;
+ * small enough to be bound by per-symbol latency), 4 = the same with 13 streams per SM
+ * and every symbol stored straight to its output byte.  A tuning and testing knob;
  * results are identical. */
 int lmz_gpu_set_table_mode(int mode);
 
@@ -118,7 +119,8 @@ int lmz_gpu_decode_streams_dev(const void *d_jobs, unsigned njobs, const void *d
  *
  * Arguments as lmz_gpu_decode_batch_dev (no tpb).  h_status is host memory for nstr
  * uint32 verdicts (0 ok, 1 bad header, 2 truncated, 3 input timeout, 0x100 trailing
- * slack) or NULL.  The call waits for cuda_stream and returns LMZ_GPU_EBADSTREAM if
+ * slack) or NULL.  The call is synchronous -- it waits for cuda_stream and copies the
+ * verdicts to the host before it returns -- and returns LMZ_GPU_EBADSTREAM if
  * any stream failed, LMZ_GPU_EUNSUPPORTED if nstr exceeds the maximum (split the
  * batch).  The first call on each device looks up the array's device address; make
  * that call before starting any stream capture.  All calls on a device share the
@@ -156,6 +158,10 @@ int lmz_gpu_pack_streams_dev(const void *d_slots, unsigned plane, const void *d_
 /* sizeof of {stream job, chunk job, cond job, cond state, fused job}, so a host
  * planner can check its mirrored layouts. */
 int lmz_gpu_struct_sizes(unsigned *out5);
+
+/* Chunks of a shared-table archive that one thread block decodes against one table (80):
+ * the unit a planner pads each table's run of jobs to. */
+int lmz_gpu_shared_group(void);
 
 /* Output bytes one thread block finishes at a time (65536); chunks are cut into
  * pieces of this size and checksummed piecewise. */
@@ -201,6 +207,7 @@ typedef struct lmz_decode_plan {
     void *d_chunk_status;       /* uint32 per chunk: 0 ok, 4 bad shape, 5 bad crc */
     void *d_chunk_crc;          /* computed crc32 per chunk, or NULL */
     void *d_any_bad;            /* uint32: bit 0 a stream failed, bit 1 a chunk failed */
+    const void *d_tables;       /* shared-table chunks: the archive's 516-byte tables, 528 bytes apart */
     void *d_fused_order;        /* NULL, or n_fused + 4 uint32 of work space: the library then counts
                                  * every fused stream's alphabet on the device and sorts the jobs
                                  * itself (n_fused_small and n_fused_f32_small are ignored, the jobs may
@@ -210,6 +217,10 @@ typedef struct lmz_decode_plan {
                                  * lmz_host_alphabet_sizes); they take the denser kernel instance */
     uint32_t n_fused_f32;       /* trailing fused jobs that are 4-byte-element chunks (counted in n_fused) */
     uint32_t n_fused_f32_small; /* the first of those, with small alphabets */
+    uint32_t n_fused_t;         /* shared-table BF16 chunks: further jobs after the n_fused in d_fused_jobs (and
+                                 * d_fused_status), `flags` = table number in d_tables, listed table by table
+                                 * and each table's run padded with empty jobs (n = 0) to a multiple of
+                                 * lmz_gpu_shared_group() */
     uint32_t piece_split[6];    /* piece-id boundaries of the five chunk groups */
     uint32_t phases;            /* 0 = everything; else bit 0 stream decode, bit 1 conditioned-chunk
                                  * kernels, bit 2 finish, bit 3 verdicts, bit 4 fused chunks

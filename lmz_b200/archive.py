@@ -27,6 +27,14 @@ RECORD = np.dtype([("off", "<u8"), ("dst", "<u8"), ("clen", "<u4"), ("rlen", "<u
 
 CODEC_STORED, CODEC_ZSTD, CODEC_SPLIT, CODEC_BF16, CODEC_REF = 0, 1, 2, 3, 4   # lmz/format.py:58-66
 CODEC_BF16C, CODEC_BLK, CODEC_GBLK, CODEC_DELTA = 5, 6, 7, 8
+# Shared-table option -- the format lever the reference proposes without defining a layout
+# (docs/gpu-residency-handover.md:37-66); this one is this repository's.  A BF16 chunk whose
+# exponent plane is coded against a 516-byte table stored once, in the payload region, for a
+# run of chunks: payload = <IIQ (plane 0 length, plane 1 length, file offset of the table),
+# plane 0 as [8 states][words] (scratchpad/gpu/shared_enc.c:1-13), plane 1 stored.
+CODEC_BF16T = 9
+FLAG_SHARED_TABLES = 4
+TABLE_BYTES = 516
 METHOD_STORED, METHOD_ZSTD, METHOD_DEFLATE, METHOD_RANS = 0, 1, 2, 3          # lmz/entropy.py:17-22
 FLAG_PAGE_MAPPED = 1
 

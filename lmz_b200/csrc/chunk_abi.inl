@@ -16,6 +16,7 @@ API int lmz_gpu_struct_sizes(unsigned *out5)
 }
 
 API int lmz_gpu_piece_bytes(void) { return (int)PIECE_BYTES; }
+API int lmz_gpu_shared_group(void) { return F_SHARED_SINK_WARPS * 4; }
 
 API int lmz_gpu_crc_tables(void *host_dst, size_t cap)
 {
@@ -109,15 +110,16 @@ struct SideScope {
     ~SideScope() { join(); }
 };
 
-static int side_stream(SideStream **out)
+// `which`: 0 = the fused kernel's stream, 1 = the conditioned chunks' counting stream.
+static int side_stream(SideStream **out, int which = 0)
 {
-    static SideStream per_dev[64];
+    static SideStream per_dev[2][64];
     static std::mutex mu;
     int dev = 0;
     CK("cudaGetDevice", cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) { *out = nullptr; return LMZ_GPU_OK; }
     std::lock_guard<std::mutex> lock(mu);
-    SideStream &s = per_dev[dev];
+    SideStream &s = per_dev[which][dev];
     if (!s.stream) {
         CK("cudaStreamCreate", cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
         CK("cudaEventCreate", cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming));
@@ -160,9 +162,11 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     //     decode, merge, write and checksum in one kernel
     SideStream *side = nullptr;
     SideScope scope;
+    if (p->n_fused_t % (F_SHARED_SINK_WARPS * 4u))
+        return fail_msg(LMZ_GPU_EUNSUPPORTED, "n_fused_t is not a multiple of lmz_gpu_shared_group()");
     const bool other_work = p->n_stream_jobs || p->n_cond || p->piece_split[2] > p->piece_split[0] ||
                             p->piece_split[5] > p->piece_split[3];
-    if (p->n_fused && (ph & 16u)) {
+    if ((p->n_fused || p->n_fused_t) && (ph & 16u)) {
         cudaStream_t fs = cs;
         if (ph == 0x1fu && other_work) {        // whole decode: run the fused kernel beside the rest
             rc = side_stream(&side);
@@ -240,6 +244,24 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
                             : launch_stream<SINK_F32, false, 256>(sa, fs);
         if (rc) return rc;
         }
+        if (p->n_fused_t) {
+            // chunks of a shared-table archive: every CTA takes one table's next 80 of them
+            StreamArgs ta{};
+            ta.src = (const uint8_t *)p->d_payload;
+            ta.jobs = (const FusedJob *)p->d_fused_jobs + p->n_fused;
+            ta.njobs = p->n_fused_t;
+            ta.dst = (uint8_t *)p->d_out;
+            ta.status = (uint32_t *)p->d_fused_status + p->n_fused;
+            ta.any_bad = (uint32_t *)p->d_any_bad;
+            ta.piece_crc = (uint32_t *)p->d_piece_crc;
+            ta.tabs = (const CrcTables *)p->d_crc_tables;
+            ta.tables = (const uint8_t *)p->d_tables;
+            ta.per_cta = F_SHARED_SINK_WARPS * 4;
+            if (!ta.tables) return fail_msg(LMZ_GPU_EUNSUPPORTED, "shared-table chunks without d_tables");
+            rc = p->d_piece_crc ? launch_stream<SINK_BF16, true, -1>(ta, fs)
+                                : launch_stream<SINK_BF16, false, -1>(ta, fs);
+            if (rc) return rc;
+        }
     }
 
     // 1. every rANS stream whose length is known up front, into scratch
@@ -280,12 +302,26 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         a.dst = (uint8_t *)p->d_scratch;
         a.status = (uint32_t *)p->d_seg_status;
         a.any_bad = (uint32_t *)p->d_any_bad;
-        rc = launch_rans(a, cs);
+        // the bucket populations need only the bucket map, the segment decodes only the sizes:
+        // both follow k_cond_plan and are independent of each other, so the counting (a pass over
+        // the exponent planes at memory speed) runs beside the segment decodes (a few long streams
+        // per SM, bound by their length)
+        SideStream *aux = nullptr;
+        SideScope counting;
+        rc = side_stream(&aux, 1);
         if (rc) return rc;
-        k_cond_count<<<p->n_cond_pieces, 256, 0, cs>>>(c);
-        k_cond_scan<<<(p->n_cond * 8 + 127) / 128, 128, 0, cs>>>(c.chunks, c.cond_jobs, c.ncond, c.piece_cnt);
+        cudaStream_t ks = cs;
+        if (aux && p->n_seg_jobs) {
+            CK("fork to the counting stream", counting.fork(aux, cs));
+            ks = aux->stream;
+        }
+        k_cond_count<<<p->n_cond_pieces, 256, 0, ks>>>(c);
+        k_cond_scan<<<(p->n_cond * 8 + 127) / 128, 128, 0, ks>>>(c.chunks, c.cond_jobs, c.ncond, c.piece_cnt);
         cudaError_t le = cudaGetLastError();
         if (le != cudaSuccess) return fail_cuda("launch cond kernels", le);
+        rc = launch_rans(a, cs);
+        if (rc) return rc;
+        CK("join the counting stream", counting.join());
     }
 
     // 3. finish: pass 1 (plain chunks), then pass 2 (refs and deltas, which read pass 1's output)

@@ -44,15 +44,21 @@ constexpr uint32_t F_STAGE = 144;                  // 128 + 16: groups land 4 ba
 // The per-stream wide instance (CFN = 0) runs one warp per scheduler, where every
 // instruction of tile bookkeeping is paid in full, and has shared memory to spare beside
 // its 12 tables: its tiles are twice as long (256 symbols) and its ring twice as deep.
-__host__ __device__ constexpr bool stream_long_tiles(int cfn, int warps) { return cfn == 0 && warps == 3; }
+__host__ __device__ constexpr bool stream_long_tiles(int cfn, int warps) { return cfn == 0 && (warps == 3 || warps == 4); }
+// The same with a thirteenth stream (a fourth warp that carries one): its table fits only when the
+// tables need no 16 KiB alignment, the ring has six slots instead of eight and nothing is staged --
+// every symbol goes straight to its byte of the output.  For launches of 12 x SMs + 1 ... 13 x SMs
+// streams (the 1915 long streams of an 8B model at the reference's default chunking, on 148 SMs).
+__host__ __device__ constexpr bool stream_direct(int cfn, int warps) { return cfn == 0 && warps == 4; }
+constexpr uint32_t F_DIRECT_GROUPS = 13;
 __host__ __device__ constexpr uint32_t stream_tile(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 256u : 128u; }
-__host__ __device__ constexpr uint32_t stream_nslot(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 8u : F_NSLOT; }
+__host__ __device__ constexpr uint32_t stream_nslot(int cfn, int warps) { return stream_direct(cfn, warps) ? 6u : stream_long_tiles(cfn, warps) ? 8u : F_NSLOT; }
 __host__ __device__ constexpr uint32_t stream_mirror(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 528u : F_MIRROR; }
 __host__ __device__ constexpr uint32_t stream_ring_bytes(int cfn, int warps)
 {
     return F_SLOT * stream_nslot(cfn, warps) + stream_mirror(cfn, warps);
 }
-__host__ __device__ constexpr uint32_t stream_stage(int cfn, int warps) { return stream_long_tiles(cfn, warps) ? 272u : F_STAGE; }
+__host__ __device__ constexpr uint32_t stream_stage(int cfn, int warps) { return stream_direct(cfn, warps) ? 0u : stream_long_tiles(cfn, warps) ? 272u : F_STAGE; }
 constexpr uint32_t F_LOGS = 3;                     // eight copies of the CRC slice tables (32 KiB), one per lane of a group: see CrcQuarters
 constexpr uint32_t F_CRC_BYTES = (4096u << F_LOGS) + 4096u;   // + the row-advance tables, once
 constexpr uint32_t F_ROW = 256, F_UNIT = 32;       // bytes of BF16 one group / one lane emits per tile
@@ -87,6 +93,8 @@ struct StreamArgs {
     uint32_t *piece_crc;        // SINK_BF16 with checksums: R() per 64 KiB piece
     const CrcTables *tabs;
     const uint8_t *shared_hdr;  // CFN = -1: the 516-byte table every stream of the launch shares
+    const uint8_t *tables;      // CFN = -1, or NULL: the 516-byte tables of a shared-table archive, F_TABLE_STRIDE
+                                // bytes apart; a CTA's streams all use table number `flags` of its first job
     // Optional indirection, filled on the device by k_classify: the launch covers the
     // first *count entries of `order` (read from its end backwards when order_from_back),
     // each the index of a job; CTAs past the count leave at once.
@@ -107,6 +115,8 @@ __host__ __device__ constexpr uint32_t stream_group_bytes(int cfn)
     return (cfn > 0 ? 1024 + 4 * cfn : cfn == 0 ? F_WIDE_BYTES : 0) + F_RING_BYTES + F_STAGE + 32;   // 3008 / 2496 / 17344 / 960
 }
 constexpr int F_SHARED_WARPS = 16;                  // CFN = -1: one table per CTA, two CTAs per SM (64 registers a thread)
+constexpr uint32_t F_TABLE_STRIDE = 528;            // 516 rounded up to 16
+constexpr int F_SHARED_SINK_WARPS = 20;             // CFN = -1 with the BF16 sink: one CTA per SM, 80 chunks sharing its table
 // Streams are carved from the bottom of the CTA's shared memory and the CRC tables
 // from the top (slice tables 8 KiB aligned, row-advance tables above them), so the
 // launch asks for everything the device lets one CTA have: 227 KiB that start
@@ -128,7 +138,7 @@ __host__ __device__ constexpr int stream_warps(int cfn, bool crc, int sink = SIN
 {
     constexpr uint32_t top = F_SMEM_BASE + F_SMEM_DYN;
     if (cfn == 0) return F_WIDE_GROUPS / 4;
-    if (cfn < 0) return F_SHARED_WARPS;
+    if (cfn < 0) return sink == SINK_BF16 ? F_SHARED_SINK_WARPS : F_SHARED_WARPS;
     const uint32_t room = (crc ? stream_crc_slice(top) : top) - F_SMEM_BASE + (stream_top_l1(sink, crc, cfn) ? 4096u : 0u);
     int w = (int)(room / (4u * stream_group_bytes(cfn)));
     // Registers are shared per scheduler: a 21st warp would put six on one of the four and cut every
@@ -195,13 +205,14 @@ struct MRingT {
 
 // Table lookups and the state update of one decode step, before the refill.
 // Returns the level-2 entry (its low byte is the symbol); x2 is the new state.
-template <int CFN>
+template <int CFN, bool ALIGNED = true>
 __device__ __forceinline__ uint32_t stream_advance(uint32_t x, uint32_t l1_sa, uint32_t cf_sa, uint32_t &x2)
 {
     uint32_t e;
     if (CFN <= 0) {
-        // wide table at l1_sa (16 KiB aligned; the stream's own, or the CTA's shared one): one lookup
-        e = lds_u32(((x << 2) & 0x3ffcu) | l1_sa);
+        // wide table at l1_sa (the stream's own, or the CTA's shared one): one lookup.  A 16 KiB
+        // aligned table is indexed by OR, any other by a shift-add.
+        e = lds_u32(ALIGNED ? ((x << 2) & 0x3ffcu) | l1_sa : l1_sa + ((x & 0xfffu) << 2));
     } else {
         // level 1: the warp's four tables are interleaved word by word, so bucket b of
         // this group sits 16 * b bytes in -- the slot's bits 4-11, unshifted
@@ -218,13 +229,13 @@ __device__ __forceinline__ uint32_t stream_advance(uint32_t x, uint32_t l1_sa, u
 
 // One decode step, any lane mix.  `caddr` is the shared address of the cursor
 // (linear within a tile thanks to the mirror).
-template <int CFN>
+template <int CFN, bool ALIGNED = true>
 __device__ __forceinline__ uint32_t stream_step(uint32_t &x, uint32_t &caddr, uint32_t l1_sa,
                                                 uint32_t cf_sa, uint32_t lt_mask, uint32_t grp_mask,
                                                 bool active)
 {
     uint32_t x2;
-    const uint32_t e = stream_advance<CFN>(x, l1_sa, cf_sa, x2);
+    const uint32_t e = stream_advance<CFN, ALIGNED>(x, l1_sa, cf_sa, x2);
     const bool need = active && x2 < RANS_LOW;
     const uint32_t vote = __ballot_sync(0xffffffffu, need);
     const uint32_t addr = caddr + 2 * __popc(vote & lt_mask);
@@ -241,13 +252,13 @@ __device__ __forceinline__ uint32_t stream_step(uint32_t &x, uint32_t &caddr, ui
 // lane's = bits of the older bytes plus the lanes below it in the newest, so one
 // popcount of hist & below (= 0xffffff00 | lanes below) gives the offset from
 // the block's cursor.  The caller adds 2 * popc(hist) to `cbase` after step 3.
-template <int CFN, bool FIRST>
+template <int CFN, bool FIRST, bool ALIGNED = true>
 __device__ __forceinline__ uint32_t stream_step4(uint32_t &x, uint32_t &hist, uint32_t cbase,
                                                  uint32_t l1_sa, uint32_t cf_sa, uint32_t below,
                                                  uint32_t vsel)
 {
     uint32_t x2;
-    const uint32_t e = stream_advance<CFN>(x, l1_sa, cf_sa, x2);
+    const uint32_t e = stream_advance<CFN, ALIGNED>(x, l1_sa, cf_sa, x2);
     const bool need = x2 < RANS_LOW;
     const uint32_t vote = __ballot_sync(0xffffffffu, need);
     hist = __byte_perm(vote, FIRST ? 0u : hist, vsel);
@@ -282,7 +293,7 @@ __device__ __forceinline__ uint32_t dynamic_smem_bytes()
 }
 
 template <int SINK, bool CRC, int WARPS, int CFN>
-__global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamArgs a)
+__global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 : 1) k_stream(StreamArgs a)
 {
     // SINK_BF16 checksums: lane k keeps one running value per word of its 32-byte unit,
     // ra[i] = sum over the piece's rows so far of word i * x^(2048 * rows since); a row
@@ -293,15 +304,20 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     constexpr bool TOPL1 = stream_top_l1(SINK, CRC, CFN);
     extern __shared__ __align__(16) uint8_t ssm[];
     constexpr bool WIDE = CFN <= 0, SHARED = CFN < 0;
-    constexpr uint32_t G = stream_groups(CFN, WARPS), CFB = WIDE ? 16u : 4u * CFN;
+    constexpr bool DIRECT = stream_direct(CFN, WARPS);
+    static_assert(!DIRECT || SINK == SINK_BYTES, "the 13-stream instance writes bytes only");
+    constexpr uint32_t G = DIRECT ? F_DIRECT_GROUPS : stream_groups(CFN, WARPS), CFB = WIDE ? 16u : 4u * CFN;
     constexpr uint32_t LEAD = (SHARED ? 0u : HDR_BYTES) + STATE_BYTES;
     constexpr uint32_t MAX_LIVE = CFN > 0 && CFN < 256 ? (uint32_t)CFN - 24u : 256u;
     constexpr uint32_t TS = stream_tile(CFN, WARPS), NSL = stream_nslot(CFN, WARPS), RB = stream_ring_bytes(CFN, WARPS);
     constexpr uint32_t STG = stream_stage(CFN, WARPS), RINGB = F_SLOT * NSL;
-    constexpr uint32_t HS = NSL == 8 ? 160u : 144u;     // header staging copy: four of them cover 548 + 15 bytes
-    static_assert(!WIDE || !CRC, "the wide instance has no room for CRC tables");
+    constexpr uint32_t HS = NSL != F_NSLOT ? 160u : 144u;     // header staging copy: four of them cover 548 + 15 bytes
+    static_assert(CFN != 0 || !CRC, "the per-stream wide instance has no room for CRC tables");
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    const uint32_t k = lane & 7u, g = lane >> 3, gi = warp * 4 + g;
+    // DIRECT: the fourth warp carries one stream; its other three groups shadow it (same tables,
+    // ring and states, no copies requested, nothing stored) so that the warp decodes full tiles
+    const uint32_t k = lane & 7u, g = lane >> 3, gi = DIRECT ? min(warp * 4 + g, G - 1) : warp * 4 + g;
+    const bool shadow = DIRECT && warp * 4 + g > gi;
     const uint32_t grp_mask = 0xffu << (g * 8), lt_mask = ((1u << k) - 1u) << (g * 8);
     const uint32_t below = 0xffffff00u | ((1u << k) - 1u), vsel = 0x6540u + g;
 
@@ -315,11 +331,11 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     const uint32_t ring_0 = stage_0 + G * STG;
     const uint32_t cf_0 = (ring_0 + G * RB + CFB - 1) & ~(CFB - 1);
     // compact: level 1 at the top; wide: 16 KiB tables from the first 16 KiB boundary up
-    const uint32_t l1_0 = WIDE ? (cf_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1)
+    const uint32_t l1_0 = DIRECT ? cf_0 : WIDE ? (cf_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1)
                                : ((CRC ? tab0 : top) & ~4095u) - (WARPS - (TOPL1 ? 1 : 0)) * 4096u;
     // compact: this warp's 4 KiB of level 1 (the last warp's sits where the row-advance tables would)
     auto l1_of = [&](uint32_t w) { return TOPL1 && w == WARPS - 1 ? adv0 : l1_0 + w * 4096u; };
-    const bool fits = WIDE ? l1_0 + (SHARED ? 1u : G) * F_WIDE_BYTES <= top : cf_0 + G * CFB <= l1_0 && (!TOPL1 || (adv0 & 4095u) == 0);
+    const bool fits = WIDE ? l1_0 + (SHARED ? 1u : G) * F_WIDE_BYTES <= (CRC ? tab0 : top) : cf_0 + G * CFB <= l1_0 && (!TOPL1 || (adv0 & 4095u) == 0);
     auto gen = [&](uint32_t sa) { return ssm + (sa - s0); };
     const uint32_t l1_sa = SHARED ? l1_0 : WIDE ? l1_0 + gi * F_WIDE_BYTES : l1_of(warp) + g * 4;
     const uint32_t cf_sa = cf_0 + gi * CFB;
@@ -370,7 +386,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     ring.valid_slots = n ? (skew + slen + F_SLOT - 1) / F_SLOT : 0;
     ring.issued = 0; ring.ready = 0; ring.dead = false;
 
-    if (k == 0)
+    if (k == 0 && !shadow)
         for (uint32_t j = 0; j < NSL; j++) mbar_init(&ring.bars[j], 1);
     mbar_fence_init();
     if (CRC && fits) {
@@ -392,7 +408,8 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         // fails every stream of the CTA
         uint32_t *poison = reinterpret_cast<uint32_t *>(gen(cf_0));
         if (warp == 0) {
-            const uint8_t *h = a.shared_hdr;
+            // one table for the launch, or the one this CTA's chunks name (a shared-table archive)
+            const uint8_t *h = (a.tables && a.jobs) ? a.tables + (size_t)a.jobs[blockIdx.x * per_cta].flags * F_TABLE_STRIDE : a.shared_hdr;
             Tables tb{};
             tb.wide = reinterpret_cast<uint32_t *>(gen(l1_0));
             bool ok = fits && build_table<T_WIDE1>(
@@ -413,7 +430,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
     // boundary falls) land linearly from the ring's start: four copies, one on each of
     // the first four slot barriers, which have then completed one phase -- as if ring
     // slots 0..3 had been filled and consumed -- when normal ring operation takes over.
-    if (!SHARED && k == 0 && n) {
+    if (!SHARED && k == 0 && n && !shadow) {
         for (uint32_t j = 0; j < 4; j++) {
             mbar_expect_tx(&ring.bars[j], HS);
             bulk_g2s_sa(ring.sa + HS * j, ring.abase + HS * j, HS, smem_addr(&ring.bars[j]));
@@ -433,7 +450,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
 #pragma unroll 1
     for (uint32_t gg = 0; !SHARED && gg < 4; gg++) {
         uint32_t on = __shfl_sync(0xffffffffu, n, gg * 8);
-        if (!on) continue;
+        if (!on || (DIRECT && warp * 4 + gg >= G)) continue;
         uint32_t sk = __shfl_sync(0xffffffffu, skew, gg * 8);
         const uint32_t rsa = ring_0 + (warp * 4 + gg) * RB;
         auto rd = [&](uint32_t o) { return lds_u8(rsa + o); };     // header sits in the first 548+15 bytes
@@ -451,7 +468,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         }
         ok = ok && rd(sk) == 'R' && rd(sk + 1) == '1';
         // an alphabet too large for this instance is the caller's mistake, not the stream's
-        if (!ok && g == gg) { st = nlive > MAX_LIVE ? ST_BAD_SHAPE : ST_BAD_HEADER; n = 0; }
+        if (!ok && gi == warp * 4 + gg) { st = nlive > MAX_LIVE ? ST_BAD_SHAPE : ST_BAD_HEADER; n = 0; }
     }
     __syncwarp();
 
@@ -484,7 +501,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
         const uint32_t rem = n > done ? n - done : 0;
         __syncwarp();
         if (rem) {
-            ring.issue(cursor, k == 0);
+            ring.issue(cursor, k == 0 && !shadow);
             ring.require(cursor + 2 * TS);         // every lane sees the completion itself
         }
         // SINK_F32: the tile's stored bytes are requested before the decode, which hides
@@ -500,23 +517,29 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
                 for (int i = 0; i < 5; i++) pr[j][i] = mine ? __ldg(pq + i) : 0u;
             }
         }
-        const uint32_t caddr0 = ring.sa + (cursor & (RINGB - 1));
+        const uint32_t caddr0 = ring.sa + ((RINGB & (RINGB - 1)) == 0 ? cursor & (RINGB - 1) : cursor % RINGB);
         uint32_t caddr = caddr0;
         // (lanes that never had a stream run along in full tiles; nothing of theirs is kept)
         const bool full = __all_sync(0xffffffffu, rem >= TS);
+        // a decoded symbol goes to the group's staging row, or (DIRECT) straight to its output byte
+        uint8_t *const orow = out + done + k;
+        auto put = [&](uint32_t step, uint32_t e) {
+            if (DIRECT) { if (!shadow) orow[step * NLANES] = (uint8_t)e; }
+            else sts_u8(stage_sa + step * NLANES + k, e);
+        };
         if (full) {
 #pragma unroll
             for (uint32_t s4 = 0; s4 < TS / NLANES; s4 += 4) {
                 uint32_t hist = 0, e;
-                e = stream_step4<CFN, true>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
-                sts_u8(stage_sa + s4 * NLANES + k, e);
-                e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
-                sts_u8(stage_sa + (s4 + 1) * NLANES + k, e);
+                e = stream_step4<CFN, true, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                put(s4, e);
+                e = stream_step4<CFN, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                put(s4 + 1, e);
                 if (ROWMUL) ra[s4 >> 1] = crc_feed4q(cq, ra[s4 >> 1]);
-                e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
-                sts_u8(stage_sa + (s4 + 2) * NLANES + k, e);
-                e = stream_step4<CFN, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
-                sts_u8(stage_sa + (s4 + 3) * NLANES + k, e);
+                e = stream_step4<CFN, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                put(s4 + 2, e);
+                e = stream_step4<CFN, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                put(s4 + 3, e);
                 if (ROWMUL) ra[(s4 >> 1) + 1] = crc_feed4q(cq, ra[(s4 >> 1) + 1]);
                 caddr += 2 * __popc(hist);
             }
@@ -528,13 +551,13 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
 #pragma unroll 1
             for (uint32_t s = 0; s < TS / NLANES; s++) {
                 bool active = s * NLANES + k < rem;
-                uint32_t e = stream_step<CFN>(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
-                if (active) sts_u8(stage_sa + s * NLANES + k, e);
+                uint32_t e = stream_step<CFN, !DIRECT>(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
+                if (active) put(s, e);
             }
         }
         cursor += caddr - caddr0;
         __syncwarp();
-        if (!rem) continue;
+        if (!rem || DIRECT) continue;
         constexpr uint32_t PER = TS / NLANES;                  // this lane's symbols of the tile: 16 or 32
         uint4 evs[PER / 16];
 #pragma unroll
@@ -692,7 +715,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 ? 2 : 1) k_stream(StreamAr
 
     // ---- verdict -----------------------------------------------------------------------
     const uint32_t all_rest = __ballot_sync(0xffffffffu, x == RANS_LOW) & grp_mask;
-    if (have && k == 0) {
+    if (have && k == 0 && !shadow) {
         if (st == ST_OK && n) {
             const uint32_t used = cursor - skew;
             if (ring.dead) st = ST_TIMEOUT;

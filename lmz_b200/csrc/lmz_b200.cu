@@ -118,31 +118,35 @@ static int stream_smem_ok()
 // CFN = 0 is the per-stream wide table (12 streams per SM), CFN = -1 one wide table per CTA.
 static int sm_count(int *out);
 
-template <int SINK, bool CRC, int CFN>
+template <int SINK, bool CRC, int CFN, int WARPS_ = 0>
 static int launch_stream(const StreamArgs &a0, cudaStream_t cs)
 {
     if (a0.njobs == 0) return LMZ_GPU_OK;
     StreamArgs a = a0;
-    constexpr int WARPS = stream_warps(CFN, CRC, SINK);
+    constexpr int WARPS = WARPS_ ? WARPS_ : stream_warps(CFN, CRC, SINK);
     static bool done[64];
     int rc = stream_smem_ok();
     if (rc) return rc;
     // the shared-table instance needs little shared memory and runs two CTAs per SM
-    constexpr uint32_t shm = CFN < 0 ? 2u * F_WIDE_BYTES + WARPS * 4 * stream_group_bytes(CFN) : F_SMEM_DYN;
+    constexpr bool PAIRED = CFN < 0 && SINK == SINK_BYTES;      // two CTAs per SM
+    constexpr uint32_t shm = PAIRED ? 2u * F_WIDE_BYTES + WARPS * 4 * stream_group_bytes(CFN) : F_SMEM_DYN;
     rc = opt_in_smem(k_stream<SINK, CRC, WARPS, CFN>, shm, done);
     if (rc) return rc;
-    constexpr unsigned groups = stream_groups(CFN, WARPS);
+    constexpr bool DIRECT = stream_direct(CFN, WARPS);
+    constexpr unsigned groups = DIRECT ? F_DIRECT_GROUPS : stream_groups(CFN, WARPS);
     unsigned per = groups;
-    {
+    if (a.per_cta) {
+        per = a.per_cta;          // the caller's job list is laid out for this many streams per CTA
+    } else {
         // as many waves of CTAs as full CTAs would need, the streams spread evenly over them
         // (when the device holds the count, as if every job of the launch were of this class)
         int sms = 0;
         rc = sm_count(&sms);
         if (rc) return rc;
-        const unsigned slots = (unsigned)sms * (CFN < 0 ? 2u : 1u);
+        const unsigned slots = (unsigned)sms * (PAIRED ? 2u : 1u);
         const unsigned waves = (a.njobs + slots * groups - 1) / (slots * groups);
         per = (a.njobs + waves * slots - 1) / (waves * slots);
-        per = (per + 3u) & ~3u;
+        if (!DIRECT) per = (per + 3u) & ~3u;
         if (per > groups) per = groups;
     }
 #ifdef LMZ_EXPERIMENT
@@ -255,8 +259,10 @@ static int launch_rans(const RansArgs &a, cudaStream_t cs, bool may_alloc = true
     int mode = forced;
     if (mode < 0)
         mode = a.njobs <= (unsigned)sms * F_WIDE_GROUPS ? T_WIDE1
+             : a.njobs <= (unsigned)sms * F_DIRECT_GROUPS ? T_WIDE13
              : a.njobs >= COMPACT_MIN_JOBS ? T_COMPACT : T_NARROW;
     if (mode == T_WIDE1) return launch_stream<SINK_BYTES, false, 0>(as_stream_args(a), cs);
+    if (mode == T_WIDE13) return launch_stream<SINK_BYTES, false, 0, 4>(as_stream_args(a), cs);
     if (mode == T_COMPACT) {
         if (may_alloc && forced < 0) {
             int rc = launch_compact_sorted(a, cs);
@@ -390,9 +396,9 @@ API int lmz_gpu_decode_batch(const void *hdr, const void *streams, size_t nbytes
 
 API int lmz_gpu_set_table_mode(int mode)
 {
-    if (mode != -1 && mode != T_NARROW && mode != T_COMPACT && mode != T_WIDE1)
+    if (mode != -1 && mode != T_NARROW && mode != T_COMPACT && mode != T_WIDE1 && mode != T_WIDE13)
         return fail_msg(LMZ_GPU_EUNSUPPORTED,
-                        "table mode must be -1 (auto), 0 (narrow), 2 (compact) or 3 (wide per stream)");
+                        "table mode must be -1 (auto), 0 (narrow), 2 (compact), 3 (wide per stream) or 4 (wide, 13 per SM)");
     g_force_table_mode.store(mode, std::memory_order_relaxed);
     return LMZ_GPU_OK;
 }

@@ -32,7 +32,7 @@ namespace lmz {
 //             words may be strided (L1S) so that several streams interleave.
 // Narrow and wide store the frequency minus one because a single-symbol stream has
 // f = 4096; compact stores 4096 - f for the same reason.
-enum : int { T_NARROW = 0, T_WIDE = 1, T_COMPACT = 2, T_WIDE1 = 3 };   // T_WIDE1: a wide table per stream
+enum : int { T_NARROW = 0, T_WIDE = 1, T_COMPACT = 2, T_WIDE1 = 3, T_WIDE13 = 4 };   // T_WIDE1 / T_WIDE13: a wide table per stream, 12 / 13 streams per SM (a launch choice, the same table)
 
 struct Tables {
     uint8_t *sym;        // T_NARROW

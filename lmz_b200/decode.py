@@ -65,7 +65,8 @@ class ArchiveDecoder:
         lib.lmz_gpu_struct_sizes(ctypes.byref(sizes))
         want = (planner.STREAM_JOB.itemsize, planner.CHUNK_JOB.itemsize,
                 planner.COND_JOB.itemsize, planner.COND_STATE_BYTES, planner.FUSED_JOB.itemsize)
-        if tuple(sizes) != want or lib.lmz_gpu_piece_bytes() != planner.PIECE:
+        if tuple(sizes) != want or lib.lmz_gpu_piece_bytes() != planner.PIECE or \
+                lib.lmz_gpu_shared_group() != planner.T_GROUP:
             raise RuntimeError("the CUDA library and the planner disagree on job layouts")
         self.archive = ar if isinstance(ar, fmt.Archive) else fmt.Archive(ar)
         self.plan = p = plan if plan is not None else planner.build_plan(self.archive, fuse=fuse)
@@ -111,7 +112,8 @@ class ArchiveDecoder:
             self.d_chunk_status = torch.zeros(max(1, p.chunks.size), **u32)
             self.d_chunk_crc = torch.zeros(max(1, p.chunks.size), **u32)
             self.d_any_bad = torch.zeros(1, **u32)
-            self.d_fused_order = torch.zeros(p.fused_jobs.size + 4, **u32) if p.device_classify else None
+            self.d_fused_order = torch.zeros(p.n_fused + 4, **u32) if p.device_classify else None
+            self.d_tables = _dev(p.tables, d) if p.n_fused_t else None
             self.d_tabs = _crc_tables(lib, d)
         c = _chunks.DecodePlan()
         c.d_payload, c.d_scratch = self.d_payload.data_ptr(), self.d_scratch.data_ptr()
@@ -119,7 +121,8 @@ class ArchiveDecoder:
         c.d_stream_jobs, c.d_seg_jobs = self.d_stream_jobs.data_ptr(), self.d_seg_jobs.data_ptr()
         c.d_stream_status, c.d_seg_status = self.d_stream_status.data_ptr(), self.d_seg_status.data_ptr()
         c.d_fused_jobs, c.d_fused_status = self.d_fused_jobs.data_ptr(), self.d_fused_status.data_ptr()
-        c.n_fused = p.fused_jobs.size
+        c.n_fused, c.n_fused_t = p.n_fused, p.n_fused_t
+        c.d_tables = self.d_tables.data_ptr() if self.d_tables is not None else None
         c.n_fused_small = p.n_fused_small
         c.n_fused_f32, c.n_fused_f32_small = p.n_fused_f32, p.n_fused_f32_small
         c.d_chunks, c.d_piece_chunk = self.d_chunks.data_ptr(), self.d_piece_chunk.data_ptr()
@@ -139,12 +142,13 @@ class ArchiveDecoder:
         self._c = c
         # kernels launched by one run(): stream decode, 3 cond kernels + segment decode,
         # up to four finish launches, the verdict kernel
-        nbf = p.fused_jobs.size - p.n_fused_f32
+        nbf = p.n_fused - p.n_fused_f32
         if p.device_classify:                # per group: the count kernel and both instances
             fused_launches = 3 * ((1 if nbf else 0) + (1 if p.n_fused_f32 else 0))
         else:
             fused_launches = (1 if p.n_fused_small else 0) + (1 if nbf > p.n_fused_small else 0) + \
                 (1 if p.n_fused_f32_small else 0) + (1 if p.n_fused_f32 > p.n_fused_f32_small else 0)
+        fused_launches += 1 if p.n_fused_t else 0
         self.launches_per_run = (1 if p.stream_jobs.size else 0) + (4 if ncond else 0) + fused_launches + \
             int(sum(p.piece_split[i + 1] > p.piece_split[i] for i in (0, 1, 3, 4))) + 1
 
@@ -338,8 +342,11 @@ class _Uploader:
         self.st = staging if staging is not None else Staging.shared()
         self.copy_stream = torch.cuda.Stream(device)
         self.lock = threading.Lock()
+        self.turn = threading.Condition()
         self.slot_free = [None] * self.st.depth        # CUDA event: the slot's last copy has left it
+        self.slot_round = [0] * self.st.depth          # blocks that have been through each buffer
         self.nblocks = 0
+        self.failed = False
         self.left, self.ready, self.events, self.tasks = [], [], [], []
 
     def send(self, lo: int, hi: int, dst):
@@ -367,8 +374,15 @@ class _Uploader:
     def _block(self, si, index, lo, hi, dst):
         import torch
         try:
-            slot = index % self.st.depth
+            slot, rnd = index % self.st.depth, index // self.st.depth
             with torch.cuda.device(self.device):
+                # a buffer takes its blocks strictly in turn: block `index` may fill it only after
+                # block `index - depth` has issued its copy (tasks start in order but may finish in
+                # any) and that copy has left the buffer
+                with self.turn:
+                    self.turn.wait_for(lambda: self.slot_round[slot] == rnd or self.failed)
+                if self.failed:
+                    raise RuntimeError("an earlier upload block failed")
                 if self.slot_free[slot] is not None:
                     self.slot_free[slot].synchronize()
                 np.copyto(self.st.views[slot][:hi - lo], self.blob[lo:hi])
@@ -381,7 +395,13 @@ class _Uploader:
                     self.left[si] -= 1
                     if self.left[si] == 0:
                         self._finish(si)
+                with self.turn:
+                    self.slot_round[slot] = rnd + 1
+                    self.turn.notify_all()
         except BaseException:
+            self.failed = True
+            with self.turn:
+                self.turn.notify_all()
             self.ready[si].set()                     # wake the waiter; result() re-raises below
             raise
 

@@ -43,6 +43,9 @@ COND_JOB = np.dtype([("exp_off", "<u8"), ("seg_src", "<u8", 8), ("seg_scratch", 
 FUSED_JOB = np.dtype([("src_off", "<u8"), ("mant_off", "<u8"), ("dst_off", "<u8"),
                       ("src_len", "<u4"), ("n", "<u4"), ("piece0", "<u4"), ("flags", "<u4")])
 COND_STATE_BYTES = 360
+T_GROUP = 80                   # shared-table chunks one thread block decodes against one table (lmz_gpu_shared_group)
+TABLE_STRIDE = 528             # spacing of the tables handed to the device
+BF16T_HDR = np.dtype([("len0", "<u4"), ("len1", "<u4"), ("table", "<u8")])
 BF16C_HDR = np.dtype([("k", "u1"), ("exp_m", "u1"), ("sm_m", "u1", 8), ("exp_len", "<u4"),
                       ("seg_len", "<u4", 8)])       # lmz/codec.py:50
 assert (STREAM_JOB.itemsize, CHUNK_JOB.itemsize, COND_JOB.itemsize, BF16C_HDR.itemsize) == \
@@ -70,6 +73,13 @@ class Plan:
     stream_owner: np.ndarray = field(default=None)   # record index of each stream job
     coded_bytes: int = 0           # sum of clen: algorithmic bytes read
     device_classify: bool = False  # the fused jobs are not sorted by alphabet: the library counts on the device
+    n_fused_t: int = 0             # trailing fused jobs of shared-table chunks (padded per table to T_GROUP)
+    tables: np.ndarray = field(default=None)   # the shared tables, TABLE_STRIDE bytes apart
+
+    @property
+    def n_fused(self) -> int:
+        """Fused jobs that carry their own table (BF16, then 4-byte elements)."""
+        return int(self.fused_jobs.size) - self.n_fused_t
     base_bytes: int = 0            # bytes of delta bases read back
 
     @property
@@ -277,6 +287,37 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
             np.bitwise_or.at(scratch_mask, i[rr], (1 << pp).astype(np.uint8))
             known[i] = True
 
+    # BF16 against a shared table (this repository's format option, archive.CODEC_BF16T)
+    is_t = np.zeros(N, dtype=bool)
+    table_of = np.zeros(N, dtype=np.int64)
+    tables = np.zeros((0, TABLE_STRIDE), dtype=np.uint8)
+    ti = np.nonzero((ecodec == fmt.CODEC_BF16T) & ~is_ref)[0]
+    if ti.size:
+        if pass2[ti].any():
+            raise FormatError("a delta whose difference is shared-table coded is not something any writer produces")
+        if (esize[ti] != 2).any() or (rlen[ti] % 2).any() or (eclen[ti] < 16).any():
+            raise CorruptArchive("a shared-table bf16 chunk is malformed")
+        h = np.ascontiguousarray(_gather(blob, eoff[ti], 16)).view(BF16T_HDR)[:, 0]
+        len0, len1 = h["len0"].astype(np.int64), h["len1"].astype(np.int64)
+        nelem = rlen[ti] // 2
+        if (16 + len0 + len1 > eclen[ti]).any() or (len1 != nelem).any():
+            raise CorruptArchive("a shared-table bf16 chunk has inconsistent plane lengths")
+        toff = h["table"].astype(np.int64)
+        if (h["table"] < fmt.HEADER.size).any() or (h["table"] > np.uint64(int(ar.table_off) - fmt.TABLE_BYTES)).any():
+            raise CorruptArchive("a shared-table bf16 chunk names a table outside the payload region")
+        uniq, inv = np.unique(toff, return_inverse=True)
+        tables = np.zeros((uniq.size, TABLE_STRIDE), dtype=np.uint8)
+        tables[:, :fmt.TABLE_BYTES] = _gather(ar.blob, uniq, fmt.TABLE_BYTES)      # read from the file itself: a
+        table_of[ti] = inv                                                         # table may lie outside this plan's payload range
+        kind[ti] = K_BF16
+        plane_off[ti, 0], plane_off[ti, 1] = eoff[ti] + 16, eoff[ti] + 16 + len0
+        nz = nelem > 0
+        fused[ti[nz]] = is_t[ti[nz]] = True
+        f_src[ti], f_len[ti], f_mant[ti] = eoff[ti] + 16, len0, eoff[ti] + 16 + len0
+        if (~nz).any():
+            raise CorruptArchive("a shared-table bf16 chunk is empty")
+        known[ti] = True
+
     # exponent-conditioned BF16 (lmz/codec.py:1075-1146)
     ci = np.nonzero((ecodec == fmt.CODEC_BF16C) & ~is_ref)[0]
     cond = np.zeros(ci.size, dtype=COND_JOB)
@@ -382,7 +423,9 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
         cond["piece0"] = piece0[pos_of[ci]]
         chunks["aux"][pos_of[ci]] = np.arange(ci.size)
     cond_pieces = np.nonzero(chunks["kind"][piece_chunk] == K_COND)[0].astype(np.uint32)
-    fpos = np.nonzero(g == 2)[0]                    # fused chunks, in launch order ...
+    fall = np.nonzero(g == 2)[0]
+    tpos = fall[is_t[corder[fall]]]                 # shared-table chunks: jobs of their own, below
+    fpos = fall[~is_t[corder[fall]]]                # fused chunks, in launch order ...
     whole = f_len[corder[fpos]] >= 548              # table + states present (else the kernel rejects it)
     small = np.zeros(fpos.size, dtype=bool)
     if classify == "host":
@@ -395,6 +438,24 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
     fused_jobs["src_off"], fused_jobs["src_len"] = f_src[frec], f_len[frec]
     fused_jobs["mant_off"], fused_jobs["dst_off"] = f_mant[frec], dst[frec]
     fused_jobs["n"], fused_jobs["piece0"] = rlen[frec] // esize[frec], piece0[fpos]
+    n_fused_t = 0
+    if tpos.size:
+        # table by table, each table's run padded with empty jobs to whole thread blocks
+        tid = table_of[corder[tpos]]
+        o = np.argsort(tid, kind="stable")
+        tpos, tid = tpos[o], tid[o]
+        per = np.bincount(tid, minlength=tables.shape[0])
+        padded = -(-per // T_GROUP) * T_GROUP
+        n_fused_t = int(padded.sum())
+        first = np.cumsum(padded) - padded
+        slot = first[tid] + (np.arange(tpos.size) - (np.cumsum(per) - per)[tid])
+        tj = np.zeros(n_fused_t, dtype=FUSED_JOB)
+        tj["flags"] = np.repeat(np.arange(tables.shape[0]), padded)
+        trec = corder[tpos]
+        tj["src_off"][slot], tj["src_len"][slot] = f_src[trec], f_len[trec]
+        tj["mant_off"][slot], tj["dst_off"][slot] = f_mant[trec], dst[trec]
+        tj["n"][slot], tj["piece0"][slot] = rlen[trec] // 2, piece0[tpos]
+        fused_jobs = np.concatenate((fused_jobs, tj))
 
     payload = blob[:hi - lo]
     extra = np.concatenate(extras) if extras else np.zeros(0, dtype=np.uint8)
@@ -405,7 +466,7 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
                 n_fused_small=int((~wide4 & small).sum()), n_fused_f32=int(wide4.sum()),
                 n_fused_f32_small=int((wide4 & small).sum()),
                 coded_bytes=int(clen.sum()), base_bytes=int(rlen[is_delta].sum()),
-                device_classify=classify != "host")
+                device_classify=classify != "host", n_fused_t=n_fused_t, tables=tables)
 
 
 def _inflate(raw: bytes) -> bytes:

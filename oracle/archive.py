@@ -65,6 +65,13 @@ class Archive:
         return self.blob[int(r["off"]):int(r["off"]) + int(r["clen"])]
 
 
+def _decode_plain(ar, c, verify, lib):
+    if int(c["codec"]) == codec.CODEC_BF16T:
+        return codec.decode_bf16t(ar.payload(c), int(c["rlen"]), int(c["crc"]), verify, lib, ar.blob)
+    return codec.decode_chunk(ar.payload(c), int(c["codec"]), int(c["esize"]), int(c["flags"]),
+                              int(c["rlen"]), int(c["crc"]), verify, lib)
+
+
 def decode_archive(blob, workers: int = 1, verify: bool = True, lib=None) -> np.ndarray:
     """Every chunk decoded into one output buffer (lmz/api.py:889-975 without
     the file writes; coverage check :1038-1055)."""
@@ -94,8 +101,7 @@ def decode_archive(blob, workers: int = 1, verify: bool = True, lib=None) -> np.
                 raise codec.Corrupt(f"source at byte {p} is not covered")
             if c["codec"] in (codec.CODEC_REF, codec.CODEC_DELTA):
                 raise codec.Corrupt("a ref or delta chunk points at another one")
-            data = codec.decode_chunk(ar.payload(c), int(c["codec"]), int(c["esize"]),
-                                      int(c["flags"]), rl, int(c["crc"]), verify, lib)
+            data = _decode_plain(ar, c, verify, lib)
             a, b = p - d, min(end - d, rl)
             buf[p - src:p - src + (b - a)] = data[a:b]
             p = d + b
@@ -115,8 +121,7 @@ def decode_archive(blob, workers: int = 1, verify: bool = True, lib=None) -> np.
             data = codec.decode_delta(pl, int(c["esize"]), int(c["flags"]), rl,
                                       resolve(src, rl), int(c["crc"]), verify, lib)
         else:
-            data = codec.decode_chunk(pl, cid, int(c["esize"]), int(c["flags"]), rl,
-                                      int(c["crc"]), verify, lib)
+            data = _decode_plain(ar, c, verify, lib)
         out[d:d + rl] = data
 
     if workers <= 1:
@@ -198,14 +203,20 @@ def _chunkify(regions, size: int, chunk_size: int, deltas):
 
 
 def write_archive(members, chunk_size: int | None = None, mapped: bool = False,
-                  delta: bool = True, workers: int = 1, level: int = 1, lib=None) -> bytes:
+                  delta: bool = True, workers: int = 1, level: int = 1, lib=None,
+                  shared_tables: int = 0) -> bytes:
     """An archive of `members` = [(path, bytes-like)], laid out as the
     reference's `compress` lays it out (lmz/api.py:651-815, format.py:279-322).
 
     Delta candidates are chosen by a simpler rule than the reference's sampled
     search (lmz/api.py:592-598 keeps the earliest member holding a tensor as
     the source): a tensor of >= 64 KiB whose name, dtype and shape also appear
-    in member 0 is coded as a delta against member 0's bytes."""
+    in member 0 is coded as a delta against member 0's bytes.
+
+    `shared_tables` = N > 0 turns on the shared-table option (codec.CODEC_BF16T): runs of
+    up to N consecutive BF16 chunks of one member whose exponent plane is rANS-coded and
+    whose sign/mantissa plane is stored share one frequency table, stored once before the
+    run, wherever that is measured to be smaller than their own tables."""
     if chunk_size is None:
         chunk_size = (64 << 10) if mapped else (8 << 20)
     chunk_size = max(chunk_size, 1 << 16)
@@ -260,8 +271,40 @@ def write_archive(members, chunk_size: int | None = None, mapped: bool = False,
     else:
         results = [work(t) for t in plan]
 
+    # shared-table runs: (first result, table) for every run that pays
+    run_table, run_of = {}, {}
+    if shared_tables > 0:
+        fits = [r[3] == codec.CODEC_BF16 and r[5] == 3 for r in results]
+        i = 0
+        while i < len(results):
+            if not fits[i]:
+                i += 1
+                continue
+            j = i
+            while j < len(results) and fits[j] and plan[j][0] == plan[i][0] and j - i < shared_tables:
+                j += 1
+            exps = [L.split_bf16(datas[plan[t][0]][plan[t][2]:plan[t][3]])[0] for t in range(i, j)]
+            own = [len(results[t][2][1]) for t in range(i, j)]          # parts = [header, plane 0, plane 1]
+            freqs = encode.shared_table_for(exps, own, L) if j - i > 1 else None
+            if freqs is not None:
+                run_table[i] = freqs
+                for t in range(i, j):
+                    run_of[t] = i
+            i = j
+
     body, recs, off = [b"\0" * 32], np.zeros(len(results), dtype=RECORD), 32
+    table_at = {}
     for i, (dst, rlen, parts, cid, es, flags, crc) in enumerate(results):
+        if i in run_table:
+            body.append(b"R1\0\0" + run_table[i].astype("<u2").tobytes())
+            table_at[i] = off
+            off += 516
+        if i in run_of:
+            first = run_of[i]
+            shared = encode.encode_bf16t(datas[plan[i][0]][plan[i][2]:plan[i][3]], run_table[first],
+                                         table_at[first], L)
+            if shared is not None:
+                parts, cid = shared[0], codec.CODEC_BF16T
         clen = 0
         for p in parts:
             p = p.tobytes() if isinstance(p, np.ndarray) else bytes(p)
@@ -276,5 +319,9 @@ def write_archive(members, chunk_size: int | None = None, mapped: bool = False,
     table_c = zlib.compress(recs.tobytes(), 3)
     man_c = zlib.compress(json.dumps(manifest, separators=(",", ":")).encode(), 3)
     body += [table_c, man_c, FOOTER.pack(off, len(table_c), off + len(table_c), len(man_c), TAIL)]
-    body[0] = HEADER.pack(MAGIC, 6, 1 if mapped else 0, total, 0, 0)
+    if table_at:
+        manifest["shared_tables"] = {"count": len(table_at), "run": int(shared_tables), "table_bytes": 516}
+        body[-2] = zlib.compress(json.dumps(manifest, separators=(",", ":")).encode(), 3)
+        body[-1] = FOOTER.pack(off, len(table_c), off + len(table_c), len(body[-2]), TAIL)
+    body[0] = HEADER.pack(MAGIC, 6, (1 if mapped else 0) | (codec.FLAG_SHARED_TABLES if table_at else 0), total, 0, 0)
     return b"".join(body)

@@ -47,29 +47,64 @@ _G = {}
 
 def _work(span):
     lo, hi = span
-    layouts, tasks, tmpdir = _G["layouts"], _G["tasks"], _G["tmpdir"]
+    layouts, tasks, tmpdir, run_len = _G["layouts"], _G["tasks"], _G["tmpdir"], _G.get("shared_tables", 0)
     L = native.best()
     recs, pos = [], 0
     path = os.path.join(tmpdir, f"part-{lo}.bin")
     with open(path, "wb", buffering=1 << 22) as f:
-        for t in range(lo, hi):
-            m, s, e, es, kind = tasks[t]
-            data = layouts[m].bytes(s, e)
-            parts, cid, flags, crc = encode.encode_chunk(data, es, kind, 1, True, L)
+        def put(parts, rlen, crc, cid, es, flags, table_pos=-1):
+            nonlocal pos
             clen = 0
             for p in parts:
                 b = p.tobytes() if isinstance(p, np.ndarray) else bytes(p)
                 f.write(b)
                 clen += len(b)
-            recs.append((pos, clen, e - s, crc, cid, es, flags))
+            recs.append((pos, clen, rlen, crc, cid, es, flags, table_pos))
             pos += clen
+
+        def flush(run):
+            """A run of BF16 chunks with a coded exponent plane and a stored mantissa plane:
+            one table for all of them where that is measured to be smaller."""
+            nonlocal pos
+            freqs = None
+            if len(run) > 1:
+                exps = [L.split_bf16(d)[0] for d, *_ in run]
+                freqs = encode.shared_table_for(exps, [len(parts[1]) for _d, parts, *_ in run], L)
+            table_pos = -1
+            if freqs is not None:
+                f.write(b"R1\0\0" + freqs.astype("<u2").tobytes())
+                table_pos, pos = pos, pos + 516
+            for data, parts, cid, flags, crc, es in run:
+                shared = encode.encode_bf16t(data, freqs, 0, L) if freqs is not None else None
+                if shared is not None:               # the table's file offset is patched in by the parent
+                    put(shared[0], data.size, crc, codec.CODEC_BF16T, es, flags, table_pos)
+                else:
+                    put(parts, data.size, crc, cid, es, flags)
+            run.clear()
+
+        run, run_member = [], -1
+        for t in range(lo, hi):
+            m, s, e, es, kind = tasks[t]
+            data = layouts[m].bytes(s, e)
+            parts, cid, flags, crc = encode.encode_chunk(data, es, kind, 1, True, L)
+            if run_len > 0 and cid == codec.CODEC_BF16 and flags == 3:
+                if run and (m != run_member or len(run) >= run_len):
+                    flush(run)
+                run.append((data, parts, cid, flags, crc, es))
+                run_member = m
+                continue
+            flush(run)
+            put(parts, e - s, crc, cid, es, flags)
+        flush(run)
     return lo, hi, path, recs, pos
 
 
 def write_model_archive(spec, seed: int = 1, chunk_size: int | None = None, mapped: bool = False,
-                        nproc: int | None = None, sigma: float = 0.02):
+                        nproc: int | None = None, sigma: float = 0.02, shared_tables: int = 0):
     """Returns (archive bytes as a numpy array, layouts).  `spec` is a list of
-    shards, each a list of (name, dtype, shape)."""
+    shards, each a list of (name, dtype, shape).  `shared_tables` = N > 0: the shared-table
+    option of `archive.write_archive`, in runs of up to N chunks (a run never crosses from
+    one worker's stretch of chunks into the next)."""
     if chunk_size is None:
         chunk_size = (64 << 10) if mapped else (8 << 20)
     chunk_size = max(chunk_size, 1 << 16)
@@ -87,7 +122,7 @@ def write_model_archive(spec, seed: int = 1, chunk_size: int | None = None, mapp
     if lo < len(tasks):
         spans.append((lo, len(tasks)))
     tmpdir = tempfile.mkdtemp(prefix="lmzgen-", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
-    _G.update(layouts=layouts, tasks=tasks, tmpdir=tmpdir)
+    _G.update(layouts=layouts, tasks=tasks, tmpdir=tmpdir, shared_tables=int(shared_tables))
     try:
         if nproc > 1:
             with mp.get_context("fork").Pool(nproc) as pool:
@@ -109,18 +144,24 @@ def write_model_archive(spec, seed: int = 1, chunk_size: int | None = None, mapp
                     "entropy": "deflate", "checksum": "crc32", "total_size": base,
                     "members": members, "chunks": len(tasks), "table_raw_len": recs.nbytes}
         off = 32
+        patch_at, patch_to = [], []          # shared-table chunks: where their table ended up
         for lo, hi, path, rr, size in results:
-            for j, (pos, clen, rlen, crc, cid, es, flags) in enumerate(rr):
+            for j, (pos, clen, rlen, crc, cid, es, flags, table_pos) in enumerate(rr):
                 m, s, _e, _es, _k = tasks[lo + j]
                 recs[lo + j] = (off + pos, bases[m] + s, clen, rlen, crc, cid, es, flags)
+                if table_pos >= 0:
+                    patch_at.append(off + pos + 8)
+                    patch_to.append(off + table_pos)
             off += size
+        if patch_at:
+            manifest["shared_tables"] = {"count": len(set(patch_to)), "run": int(shared_tables), "table_bytes": 516}
         table_c = zlib.compress(recs.tobytes(), 3)
         man_c = zlib.compress(json.dumps(manifest, separators=(",", ":")).encode(), 3)
         tail = table_c + man_c + archive.FOOTER.pack(off, len(table_c), off + len(table_c),
                                                       len(man_c), archive.TAIL)
         blob = np.empty(32 + total_payload + len(tail), dtype=np.uint8)
-        blob[:32] = np.frombuffer(archive.HEADER.pack(archive.MAGIC, 6, 1 if mapped else 0,
-                                                      base, 0, 0), dtype=np.uint8)
+        hflags = (1 if mapped else 0) | (codec.FLAG_SHARED_TABLES if patch_at else 0)
+        blob[:32] = np.frombuffer(archive.HEADER.pack(archive.MAGIC, 6, hflags, base, 0, 0), dtype=np.uint8)
         p = 32
         for lo, hi, path, rr, size in results:
             if size:
@@ -128,6 +169,9 @@ def write_model_archive(spec, seed: int = 1, chunk_size: int | None = None, mapp
             p += size
             os.unlink(path)
         blob[p:] = np.frombuffer(tail, dtype=np.uint8)
+        if patch_at:
+            at = np.asarray(patch_at, dtype=np.int64)[:, None] + np.arange(8, dtype=np.int64)[None, :]
+            blob[at] = np.asarray(patch_to, dtype="<u8").view(np.uint8).reshape(-1, 8)
         return blob, layouts
     finally:
         for f in os.listdir(tmpdir):

@@ -23,6 +23,14 @@ from . import native
 
 CODEC_STORED, CODEC_ZSTD, CODEC_SPLIT, CODEC_BF16, CODEC_REF = 0, 1, 2, 3, 4
 CODEC_BF16C, CODEC_BLK, CODEC_GBLK, CODEC_DELTA = 5, 6, 7, 8
+# Shared-table option (the format lever of docs/gpu-residency-handover.md:37-66, which the
+# reference proposes but does not define; this layout is this repository's): a BF16 chunk
+# whose exponent plane is coded against a 516-byte table stored ONCE in the payload region
+# for a run of chunks.  Payload = <IIQ (plane 0 length, plane 1 length, file offset of the
+# table), plane 0 as [8 states][words] (scratchpad/gpu/shared_enc.c:1-13), plane 1 stored.
+CODEC_BF16T = 9
+BF16T_HDR = struct.Struct("<IIQ")
+FLAG_SHARED_TABLES = 4         # archive header flag: some chunks are CODEC_BF16T
 M_STORED, M_ZSTD, M_DEFLATE, M_RANS = 0, 1, 2, 3
 KIND_BYTES, KIND_BF16 = 0, 1
 
@@ -148,6 +156,30 @@ def decode_chunk(payload, codec: int, esize: int, flags: int, rlen: int,
             out = native.oracle().merge_planes(planes, esize)
     else:
         raise Corrupt(f"codec {codec} is outside the decode path this checker covers")
+    if verify and crc and (zlib.crc32(out) & 0xFFFFFFFF) != crc:
+        raise Corrupt("chunk failed its checksum")
+    return out
+
+
+def decode_bf16t(payload, rlen: int, crc: int, verify: bool, lib, blob) -> np.ndarray:
+    """A shared-table BF16 chunk: prepending the table makes the exponent stream an ordinary
+    lmz stream again (scratchpad/gpu/prep_shared.py:101-112)."""
+    L = _lib(lib)
+    p = native._arr(payload)
+    if rlen % 2 or p.size < BF16T_HDR.size:
+        raise Corrupt("shared-table bf16 chunk is truncated")
+    len0, len1, toff = BF16T_HDR.unpack_from(p, 0)
+    nelem = rlen // 2
+    if BF16T_HDR.size + len0 + len1 > p.size or len1 != nelem:
+        raise Corrupt("shared-table bf16 chunk has inconsistent plane lengths")
+    whole = native._arr(blob)
+    if toff < 32 or toff + 516 > whole.size:
+        raise Corrupt("shared-table bf16 chunk names a table outside the file")
+    table = whole[toff:toff + 516]
+    stream = np.concatenate((table, p[BF16T_HDR.size:BF16T_HDR.size + len0]))
+    exp = decode_stream(stream, M_RANS, nelem, L)
+    sm = p[BF16T_HDR.size + len0:BF16T_HDR.size + len0 + len1]
+    out = L.merge_bf16(exp, sm)
     if verify and crc and (zlib.crc32(out) & 0xFFFFFFFF) != crc:
         raise Corrupt("chunk failed its checksum")
     return out

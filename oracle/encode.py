@@ -183,6 +183,36 @@ def encode_chunk(data, esize: int, kind: int = KIND_BYTES, level: int = 1,
     return [payload], CODEC_ZSTD, used & 3, crc
 
 
+def shared_table_for(exp_planes, own_lengths, L):
+    """The table a run of exponent planes would share -- the reference's normalisation of
+    their summed histogram (scratchpad/gpu/shared_enc.c:49-85), so every symbol that occurs
+    anywhere can be coded -- or None when the run is cheaper with its own tables.  The choice
+    is by measured cross-entropy (docs/gpu-residency-handover.md:60-63): the bits the shared
+    table would spend on the run plus its 516 bytes, against the streams as they are."""
+    hists = [L.histogram(p).astype(np.float64) for p in exp_planes]
+    total = np.sum(hists, axis=0)
+    freqs = L.rans_freqs(total.astype(np.uint64))
+    if freqs is None:
+        return None
+    f = freqs.astype(np.float64)
+    bits = float(np.sum(total[f > 0] * -np.log2(f[f > 0] / 4096.0)))
+    shared = bits / 8.0 + 32 * len(exp_planes) + 516
+    return freqs if shared < float(sum(own_lengths)) else None
+
+
+def encode_bf16t(data, freqs, table_off: int, L, checksum: bool = True):
+    """(parts, crc) of a shared-table BF16 chunk (codec.CODEC_BF16T), or None when the
+    exponent plane does not pay against `freqs`."""
+    from .codec import BF16T_HDR
+    a = native._arr(data)
+    pa, pb = L.split_bf16(a)
+    stream = L.rans_encode_shared(pa, freqs)
+    if BF16T_HDR.size + len(stream) + pb.size >= a.size:
+        return None
+    crc = (zlib.crc32(a) & 0xFFFFFFFF) if checksum else 0
+    return [BF16T_HDR.pack(len(stream), pb.size, table_off), stream, pb], crc
+
+
 def encode_delta(data, base, esize: int, kind: int, src: int, level: int = 1,
                  checksum: bool = True, lib=None):
     """(parts, flags, crc); the codec id is CODEC_DELTA (lmz/codec.py:1018-1031)."""

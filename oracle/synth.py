@@ -243,3 +243,38 @@ class ShardLayout:
             a = max(lo, self.data_start)
             out[a - lo:] = self.data(a - self.data_start, hi - self.data_start)
         return out
+
+
+STRESS_DISTRIBUTIONS = ("uniform", "single", "two", "geometric", "zipf", "exponent", "mantissa", "zero-runs")
+
+
+def stress_plane(name: str, n: int, seed: int) -> np.ndarray:
+    """One byte plane of the decoder stress configuration: uniform over 256 values, a single
+    symbol, two symbols at p = 0.999, geometric p = 0.3, Zipf s = 1.1, the exponent bytes and
+    the sign/mantissa bytes of N(0, 0.02) BF16 weights, and runs of zeros between random bytes."""
+    rng = np.random.default_rng(seed)
+    if name == "uniform":
+        return rng.integers(0, 256, n, dtype=np.uint8)
+    if name == "single":
+        return np.full(n, 0x5A, dtype=np.uint8)
+    if name == "two":
+        return np.where(rng.random(n) < 0.999, 3, 200).astype(np.uint8)
+    if name == "geometric":
+        return np.minimum(rng.geometric(0.3, n) - 1, 255).astype(np.uint8)
+    if name == "zipf":
+        p = 1.0 / np.arange(1, 257) ** 1.1
+        return rng.choice(256, size=n, p=p / p.sum()).astype(np.uint8)
+    if name in ("exponent", "mantissa"):
+        w = normal_bf16((n,), seed).view("<u2")
+        if name == "exponent":
+            return ((w >> 7) & 0xFF).astype(np.uint8)                 # lmz/native/lmzcore.c:430-437
+        return (((w >> 8) & 0x80) | (w & 0x7F)).astype(np.uint8)
+    if name == "zero-runs":
+        out = rng.integers(0, 256, n, dtype=np.uint8)
+        pos = 0
+        while pos < n:
+            run = int(rng.geometric(0.02))
+            out[pos:pos + run] = 0
+            pos += run + int(rng.geometric(0.1))
+        return out
+    raise KeyError(name)

@@ -31,32 +31,8 @@ def shaped(name: str, n: int, seed: int) -> np.ndarray:
 
 def distribution(name: str, n: int, seed: int) -> np.ndarray:
     """The eight symbol distributions of the decoder stress configuration."""
-    rng = np.random.default_rng(seed)
-    if name == "uniform":
-        return rng.integers(0, 256, n, dtype=np.uint8)
-    if name == "single":
-        return np.full(n, 0x5A, dtype=np.uint8)
-    if name == "two":
-        return np.where(rng.random(n) < 0.999, 3, 200).astype(np.uint8)
-    if name == "geometric":
-        return np.minimum(rng.geometric(0.3, n) - 1, 255).astype(np.uint8)
-    if name == "zipf":
-        p = 1.0 / np.arange(1, 257) ** 1.1
-        return rng.choice(256, size=n, p=p / p.sum()).astype(np.uint8)
-    if name in ("exponent", "mantissa"):
-        from oracle import synth, native
-        w = synth.normal_bf16((n,), seed)
-        pa, pb = native.oracle().split_bf16(w)
-        return pa if name == "exponent" else pb
-    if name == "zero-runs":
-        out = rng.integers(0, 256, n, dtype=np.uint8)
-        pos = 0
-        while pos < n:
-            run = int(rng.geometric(0.02))
-            out[pos:pos + run] = 0
-            pos += run + int(rng.geometric(0.1))
-        return out
-    raise KeyError(name)
+    from oracle import synth
+    return synth.stress_plane(name, n, seed)
 
 
 DISTRIBUTIONS = ("uniform", "single", "two", "geometric", "zipf", "exponent", "mantissa",

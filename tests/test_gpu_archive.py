@@ -355,7 +355,7 @@ def test_load_archive_streams_a_file_through_staging(shard, tmp_path):
         assert stats["h2d_bytes"] <= len(blob) and stats["run_s"] > 0
         ar = decode.fmt.Archive(str(path))
         pd = decode.PipelinedDecoder(ar)
-        small = decode.Staging(block=1 << 16, depth=3, threads=2)
+        small = decode.Staging(block=1 << 12, depth=3, threads=2)      # thousands of blocks through three buffers
         assert (pd.run_from_file(staging=small).cpu().numpy() == shard).all()
         pd.check()
 

@@ -8,7 +8,7 @@ from helpers import DISTRIBUTIONS, SHAPES, distribution, pack_streams, shaped
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=[0, 2, 3, -1], ids=["narrow", "compact", "wide1", "auto"])
+@pytest.fixture(autouse=True, params=[0, 2, 3, 4, -1], ids=["narrow", "compact", "wide1", "wide13", "auto"])
 def table_mode(request, gpu):
     """Every test runs with both per-stream table layouts forced."""
     lib = gpu.library()
