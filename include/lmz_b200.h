@@ -148,6 +148,35 @@ int lmz_gpu_encode_batch_dev(const void *d_planes, unsigned nstr, unsigned plane
 int lmz_gpu_pack_streams_dev(const void *d_slots, unsigned plane, const void *d_offsets, unsigned nstr,
                              void *d_out, void *cuda_stream);
 
+/* ---- chunk framing for the save path ------------------------------------------
+ * No counterpart in the reference's GPU library; the reference frames chunks on the CPU
+ * (lmz/codec.py:914-1009 encode_chunk, for BF16: :939-1003).  Together with the batch
+ * encoder these turn BF16 bytes in HBM into the chunk payloads the reference writes at
+ * chunk sizes below 2 MiB.  d_src: nbytes of BF16 data cut into chunks of `chunk` bytes
+ * (the last may be shorter); both even.
+ *
+ * lmz_gpu_split_bf16_dev: d_planes (nbytes) receives, chunk by chunk at the chunk's own
+ * offset, its exponent plane and then its sign/mantissa plane (lmz/native/lmzcore.c:430-437):
+ * the layout lmz_gpu_encode_batch_dev takes with nstr = 2 * chunks, plane = chunk / 2.
+ *
+ * lmz_gpu_frame_bf16_dev, first with d_out = NULL: d_lengths (2 uint32 per chunk, the coded
+ * length of each plane as the encoder reported it) -> d_meta (4 uint32 per chunk: payload
+ * length, codec id, flags, crc32) with the first three filled in: a coded plane is kept where
+ * it saves max(1024, n >> 8) bytes (lmz/codec.py:385-398), the chunk is CODEC_BF16 if a plane
+ * is kept and the payload is shorter than the chunk, else stored (:997-1003).  Then with
+ * d_offsets (uint64 per chunk: where its payload starts in d_out, from the lengths above),
+ * d_planes and d_slots (the encoder's slots: full chunks first, then the short last chunk's
+ * two): the payload bytes.
+ *
+ * lmz_gpu_crc32_chunks_dev: crc32 of every chunk's plaintext into d_meta (lmz/codec.py:931);
+ * d_crc_tables as for the decode (lmz_gpu_crc_tables). */
+int lmz_gpu_split_bf16_dev(const void *d_src, uint64_t nbytes, unsigned chunk, void *d_planes, void *cuda_stream);
+int lmz_gpu_frame_bf16_dev(const void *d_src, uint64_t nbytes, unsigned chunk, const void *d_lengths,
+                           void *d_meta, const void *d_planes, const void *d_slots, const void *d_offsets,
+                           void *d_out, void *cuda_stream);
+int lmz_gpu_crc32_chunks_dev(const void *d_src, uint64_t nbytes, unsigned chunk, const void *d_crc_tables,
+                             void *d_meta, void *cuda_stream);
+
 /* ---- whole-archive decode ---------------------------------------------------
  * The reference has no GPU counterpart for anything below: its chunk framing,
  * plane merge, exponent conditioning, delta undo and checksum run on the CPU
@@ -202,6 +231,7 @@ typedef struct lmz_decode_plan {
     const void *d_cond_pieces;  /* uint32 piece ids of conditioned chunks */
     void *d_hist;               /* n_cond x 256 uint32 */
     void *d_piece_cnt;          /* n_pieces x 16 uint32 */
+    void *d_piece_wcnt;         /* n_pieces x 64 uint16 */
     void *d_piece_crc;          /* n_pieces uint32, or NULL to skip checksums */
     const void *d_crc_tables;
     void *d_chunk_status;       /* uint32 per chunk: 0 ok, 4 bad shape, 5 bad crc */

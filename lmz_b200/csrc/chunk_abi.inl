@@ -52,9 +52,9 @@ static int launch_cond_finish(const FinishArgs &fa, int sms, cudaStream_t cs)
     constexpr uint32_t shm = cond_finish_smem();
     int rc = opt_in_smem(k_cond_finish, shm, done);
     if (rc) return rc;
-    unsigned per_sm = 227u * 1024u / (shm + 1024u);
-    unsigned n = fa.piece_end - fa.piece_begin;
-    unsigned grid = n < (unsigned)sms * per_sm ? n : (unsigned)sms * per_sm;
+    // one CTA per SM, three pieces in flight in each
+    unsigned n = (fa.piece_end - fa.piece_begin + CF_SUBS - 1) / CF_SUBS;
+    unsigned grid = n < (unsigned)sms ? n : (unsigned)sms;
     k_cond_finish<<<grid, CF_THREADS, shm, cs>>>(fa);
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return fail_cuda("launch k_cond_finish", le);
@@ -289,6 +289,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         c.ncond = p->n_cond;
         c.hist = (uint32_t *)p->d_hist;
         c.piece_cnt = (uint32_t *)p->d_piece_cnt;
+        c.piece_wcnt = (uint16_t *)p->d_piece_wcnt;
         c.seg_jobs = (StreamJob *)p->d_seg_jobs;
         c.payload = (const uint8_t *)p->d_payload;
         c.scratch = (const uint8_t *)p->d_scratch;
@@ -336,6 +337,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     f.cond_jobs = (const CondJob *)p->d_cond_jobs;
     f.cond_state = (const CondState *)p->d_cond_state;
     f.piece_cnt = (const uint32_t *)p->d_piece_cnt;
+    f.piece_wcnt = (const uint16_t *)p->d_piece_wcnt;
     // piece groups: 0 pass-1 conditioned, 1 pass-1 plain, 2 fused (done above),
     //               3 pass-2 conditioned, 4 pass-2 plain
     if (!(ph & 4u)) CK("join the side stream", scope.join());

@@ -122,6 +122,22 @@ __device__ __forceinline__ void bf16_merge8(const uint32_t (&a)[2], const uint32
 __device__ __forceinline__ uint32_t pad128(uint32_t i) { return i + ((i >> 7) << 2); }
 constexpr uint32_t PADDED_PIECE = PIECE_ELEMS + (PIECE_ELEMS >> 7) * 4;
 
+// CRC tables in the bank-quartered layout (k_stream, k_cond_finish), laid out so that the warp's 32 lookups of one load never
+// share a bank: entry i of table j, copy r sits at word 32 i + 8 j + r -- a table owns a
+// quarter of the banks and each of its eight copies one bank of that quarter.  Lane k of
+// group g uses copy k, and the groups take the four bytes of a state word in rotated order
+// (group g starts at byte g), so in each of the four loads the groups are in four different
+// tables, i.e. bank quarters.  b[i] = table base + this lane's word for load i; rot = 8 g.
+struct CrcQuarters {
+    uint32_t b[4], rot;
+};
+__device__ __forceinline__ uint32_t crc_feed4q(const CrcQuarters &q, uint32_t s)
+{
+    const uint32_t r = __funnelshift_r(s, s, q.rot);     // byte i of r = byte (i + g) & 3 of s
+    return lds_u32(((r << 7) & 0x7f80u) | q.b[0]) ^ lds_u32(((r >> 1) & 0x7f80u) | q.b[1]) ^
+           lds_u32(((r >> 9) & 0x7f80u) | q.b[2]) ^ lds_u32(((r >> 17) & 0x7f80u) | q.b[3]);
+}
+
 struct FinishArgs {
     const ChunkJob *chunks;
     const uint32_t *piece_chunk;   // piece id -> chunk index
@@ -134,6 +150,7 @@ struct FinishArgs {
     const CondJob *cond_jobs;
     const CondState *cond_state;
     const uint32_t *piece_cnt;     // per piece of a K_COND chunk: 8 bucket populations, 8 running totals
+    const uint16_t *piece_wcnt;    // per piece of a K_COND chunk: the populations of its eight 4096-element runs
 };
 
 constexpr uint32_t FINISH_THREADS = 256;   // threads that finish one piece together

@@ -15,6 +15,7 @@ struct CondArgs {
     uint32_t ncond;
     uint32_t *hist;                // ncond x 256, zeroed by the caller
     uint32_t *piece_cnt;           // npieces x 16: 8 populations, then 8 running totals (k_cond_scan)
+    uint16_t *piece_wcnt;          // npieces x 8 x 8: the populations of each 4096-element run of a piece
     StreamJob *seg_jobs;           // one slot per rANS-coded segment, sized by k_cond_plan
     const uint8_t *payload;
     const uint8_t *scratch;
@@ -31,13 +32,15 @@ __device__ __forceinline__ const uint8_t *cond_exp_piece(const CondArgs &a, uint
     return (cj.exp_in_scratch ? a.scratch : a.payload) + cj.exp_off + e0;
 }
 
-// 256-bin histogram of one exponent piece (lmz/native/lmzcore.c:385-397),
-// accumulated per warp in shared memory, then added to the chunk's histogram.
+// 256-bin histogram of one exponent piece (lmz/native/lmzcore.c:385-397), accumulated in
+// shared memory, then added to the chunk's histogram.  Exponent planes have a handful of
+// popular symbols, so lanes of a warp keep hitting the same counter: every warp has four
+// copies of the histogram (one per lane & 3) to spread those collisions.
 __global__ void __launch_bounds__(256) k_cond_hist(CondArgs a)
 {
-    __shared__ uint32_t h[8][256];
-    const uint32_t t = threadIdx.x, warp = t >> 5;
-    for (uint32_t i = t; i < 8 * 256; i += 256) (&h[0][0])[i] = 0;
+    __shared__ uint32_t h[32][256];
+    const uint32_t t = threadIdx.x, warp = t >> 5, mine = warp * 4 + (t & 3u);
+    for (uint32_t i = t; i < 32 * 256; i += 256) (&h[0][0])[i] = 0;
     __syncthreads();
     uint32_t ci, ne;
     const uint8_t *exp = cond_exp_piece(a, a.cond_pieces[blockIdx.x], ci, ne);
@@ -55,13 +58,13 @@ __global__ void __launch_bounds__(256) k_cond_hist(CondArgs a)
             uint32_t i = i0 + u * 256 * 4;
 #pragma unroll
             for (int z = 0; z < 4; z++)
-                if (i + z < ne) atomicAdd(&h[warp][(w[u] >> (8 * z)) & 0xff], 1u);
+                if (i + z < ne) atomicAdd(&h[mine][(w[u] >> (8 * z)) & 0xff], 1u);
         }
     }
     __syncthreads();
     uint32_t s = 0;
 #pragma unroll
-    for (int w = 0; w < 8; w++) s += h[w][t];
+    for (int w = 0; w < 32; w++) s += h[w][t];
     if (s) atomicAdd(&a.hist[(size_t)ci * 256 + t], s);
 }
 
@@ -121,54 +124,55 @@ __global__ void k_cond_plan(CondArgs a)
     cs.status = status;
 }
 
-// Bucket populations of one exponent piece, for the stable un-partition's ranks.
-// Every symbol's bucket is looked up as a pair of one-hot words (8 bits per bucket,
-// buckets 0-3 and 4-7), so counting a byte is one 8-byte shared load and two adds;
-// a thread sees at most 128 elements, which an 8-bit field holds.
+// Bucket populations of one exponent piece, for the stable un-partition's ranks: of the
+// piece (piece_cnt) and of each of its eight 4096-element runs (piece_wcnt), one run per
+// warp, which is how k_cond_finish walks the piece.  A symbol's bucket is looked up as a
+// byte (four times the bucket number) and counted as a one-hot word of 4-bit fields, one
+// shared load, a shift and an add per element; every twelve elements the nibbles are spread
+// into 8-bit fields (buckets 0, 2, 4, 6 in one word, 1, 3, 5, 7 in the other), which hold the
+// 128 elements a thread sees.  Half a KiB of shared memory: with the KiB the system reserves
+// per block that still fits beside the segment decodes that run at the same time and leave
+// under 2 KiB of an SM free.
 __global__ void __launch_bounds__(256) k_cond_count(CondArgs a)
 {
-    __shared__ uint32_t cnt[8][COND_BUCKETS];
-    __shared__ __align__(8) uint2 hot[256];
+    __shared__ __align__(256) uint32_t both[64 + 8 * COND_BUCKETS];     // one array: no padding between the two
+    uint8_t *hot = reinterpret_cast<uint8_t *>(both);                   // symbol -> 4 * bucket
+    uint32_t (*cnt)[COND_BUCKETS] = reinterpret_cast<uint32_t (*)[COND_BUCKETS]>(both + 64);
     const uint32_t t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const uint32_t q = a.cond_pieces[blockIdx.x];
     uint32_t ci, ne;
     const uint8_t *exp = cond_exp_piece(a, q, ci, ne);
-    {
-        const uint32_t b = a.cond_state[ci].lut[t];
-        hot[t] = make_uint2(b < 4 ? 1u << (8 * b) : 0u, b < 4 ? 0u : 1u << (8 * (b - 4)));
-    }
+    hot[t] = (uint8_t)(4 * a.cond_state[ci].lut[t]);
     __syncthreads();
-    const uint32_t hot_sa = smem_addr(hot);
-    uint32_t lo = 0, hi = 0;
-    auto count4 = [&](uint32_t w, uint32_t valid) {
-        const uint32_t ix[4] = {(w << 3) & 0x7f8u, (w >> 5) & 0x7f8u, (w >> 13) & 0x7f8u, (w >> 21) & 0x7f8u};
-#pragma unroll
-        for (int z = 0; z < 4; z++) {
-            if ((uint32_t)z < valid) {
-                const uint2 h = lds_u64(hot_sa + ix[z]);
-                lo += h.x;
-                hi += h.y;
-            }
-        }
+    const uint32_t hot_sa = smem_addr(hot);               // 256-byte aligned: an index is OR-ed on
+    uint32_t lo = 0, hi = 0, nib = 0;
+    auto flush = [&]() {
+        lo += nib & 0x0f0f0f0fu;
+        hi += (nib >> 4) & 0x0f0f0f0fu;
+        nib = 0;
     };
-    for (uint32_t i0 = t * 4; i0 < ne; i0 += 256 * 4 * 8) {
+    // warp w takes elements [4096 w, 4096 w + 4096): 32 words per lane, loaded 8 at a time
+    const uint32_t w0 = warp * (PIECE_ELEMS / 8);
+    for (uint32_t j0 = 0; j0 < 32; j0 += 8) {
         uint32_t w[8];
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-            uint32_t i = i0 + u * 256 * 4, v[1] = {0};
+            uint32_t i = w0 + (j0 + u) * 128 + lane * 4, v[1] = {0};
             if (i < ne) load_words<1>(exp + i, v);
             w[u] = v[0];
         }
-        if (i0 + 7 * 256 * 4 + 4 <= ne) {
+        const bool whole = w0 + (j0 + 7) * 128 + lane * 4 + 4 <= ne;
 #pragma unroll
-            for (int u = 0; u < 8; u++) count4(w[u], 4);
-        } else {
+        for (int u = 0; u < 8; u++) {
+            const uint32_t i = w0 + (j0 + u) * 128 + lane * 4;
+            const uint32_t valid = whole ? 4u : (i < ne ? min(ne - i, 4u) : 0u);
+            const uint32_t ix[4] = {w[u] & 0xffu, (w[u] >> 8) & 0xffu, (w[u] >> 16) & 0xffu, w[u] >> 24};
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                uint32_t i = i0 + u * 256 * 4;
-                count4(w[u], i < ne ? min(ne - i, 4u) : 0u);
-            }
+            for (int z = 0; z < 4; z++)
+                if (whole || (uint32_t)z < valid) nib += 1u << lds_u8(ix[z] | hot_sa);
+            if (u % 3 == 2) flush();                       // at most twelve additions between flushes
         }
+        flush();
     }
     // 8-bit fields -> 16-bit fields (a warp sees at most 4096 elements), then a butterfly
     uint32_t f[4] = {lo & 0x00ff00ffu, (lo >> 8) & 0x00ff00ffu, hi & 0x00ff00ffu, (hi >> 8) & 0x00ff00ffu};
@@ -178,11 +182,12 @@ __global__ void __launch_bounds__(256) k_cond_count(CondArgs a)
         for (int d = 16; d; d >>= 1) f[j] += __shfl_xor_sync(0xffffffffu, f[j], d);
     }
     if (lane == 0) {
-        // f[0] = buckets 0,2  f[1] = buckets 1,3  f[2] = buckets 4,6  f[3] = buckets 5,7
-        cnt[warp][0] = f[0] & 0xffffu; cnt[warp][2] = f[0] >> 16;
-        cnt[warp][1] = f[1] & 0xffffu; cnt[warp][3] = f[1] >> 16;
-        cnt[warp][4] = f[2] & 0xffffu; cnt[warp][6] = f[2] >> 16;
-        cnt[warp][5] = f[3] & 0xffffu; cnt[warp][7] = f[3] >> 16;
+        // lo bytes = buckets 0, 2, 4, 6 and hi bytes = buckets 1, 3, 5, 7:
+        // f[0] = buckets 0,4  f[1] = buckets 2,6  f[2] = buckets 1,5  f[3] = buckets 3,7
+        cnt[warp][0] = f[0] & 0xffffu; cnt[warp][4] = f[0] >> 16;
+        cnt[warp][2] = f[1] & 0xffffu; cnt[warp][6] = f[1] >> 16;
+        cnt[warp][1] = f[2] & 0xffffu; cnt[warp][5] = f[2] >> 16;
+        cnt[warp][3] = f[3] & 0xffffu; cnt[warp][7] = f[3] >> 16;
     }
     __syncthreads();
     if (t < COND_BUCKETS) {
@@ -190,6 +195,7 @@ __global__ void __launch_bounds__(256) k_cond_count(CondArgs a)
         for (int w = 0; w < 8; w++) s += cnt[w][t];
         a.piece_cnt[(size_t)q * 16 + t] = s;
     }
+    if (t < 64) a.piece_wcnt[(size_t)q * 64 + t] = (uint16_t)cnt[t >> 3][t & 7];
 }
 
 struct CheckArgs {

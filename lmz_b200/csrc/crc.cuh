@@ -43,6 +43,9 @@ struct CrcTables {
     uint32_t lane_mul8_4[8];  // x^(8 * 64 * (7 - k))
     uint32_t mul_row[4][256]; // multiply a state by x^(8 * 256), one 256-byte group row, per state byte
     uint32_t word_mul[8][8];  // x^(32 * (64 - 8k - i)): word i of lane k's 32-byte unit to the row's end
+    uint32_t mul_row512[4][256];  // multiply a state by x^(8 * 512): one 512-byte warp row (k_cond_finish)
+    uint32_t word_mul512[32][4];  // x^(32 * (128 - 4l - i)): word i of lane l's 16-byte unit to that row's end
+    uint32_t warp_mul8k[8];       // x^(8 * 8192 * (7 - w)): warp w's 8 KiB run to the piece's end
 };
 
 // Rows of the piece layout: 256 threads x 16 bytes.
@@ -104,6 +107,12 @@ inline void crc_build_tables(CrcTables &t)
         for (uint32_t i = 0; i < 256; i++) t.mul_row[j][i] = crc_mulmod(row, i << (8 * j));
     for (uint32_t k = 0; k < 8; k++)
         for (uint32_t i = 0; i < 8; i++) t.word_mul[k][i] = crc_xpow(t.x2, 32ull * (64 - 8 * k - i));
+    uint32_t row512 = crc_xpow(t.x2, 8ull * 512);
+    for (int j = 0; j < 4; j++)
+        for (uint32_t i = 0; i < 256; i++) t.mul_row512[j][i] = crc_mulmod(row512, i << (8 * j));
+    for (uint32_t l = 0; l < 32; l++)
+        for (uint32_t i = 0; i < 4; i++) t.word_mul512[l][i] = crc_xpow(t.x2, 32ull * (128 - 4 * l - i));
+    for (uint32_t w = 0; w < 8; w++) t.warp_mul8k[w] = crc_xpow(t.x2, 8ull * 8192 * (7 - w));
 }
 
 // Feed one little-endian 32-bit word: four table lookups.

@@ -269,22 +269,6 @@ __device__ __forceinline__ uint32_t stream_step4(uint32_t &x, uint32_t &hist, ui
     return e;
 }
 
-// CRC slice tables of k_stream, laid out so that the warp's 32 lookups of one load never
-// share a bank: entry i of table j, copy r sits at word 32 i + 8 j + r -- a table owns a
-// quarter of the banks and each of its eight copies one bank of that quarter.  Lane k of
-// group g uses copy k, and the groups take the four bytes of a state word in rotated order
-// (group g starts at byte g), so in each of the four loads the groups are in four different
-// tables, i.e. bank quarters.  b[i] = table base + this lane's word for load i; rot = 8 g.
-struct CrcQuarters {
-    uint32_t b[4], rot;
-};
-__device__ __forceinline__ uint32_t crc_feed4q(const CrcQuarters &q, uint32_t s)
-{
-    const uint32_t r = __funnelshift_r(s, s, q.rot);     // byte i of r = byte (i + g) & 3 of s
-    return lds_u32(((r << 7) & 0x7f80u) | q.b[0]) ^ lds_u32(((r >> 1) & 0x7f80u) | q.b[1]) ^
-           lds_u32(((r >> 9) & 0x7f80u) | q.b[2]) ^ lds_u32(((r >> 17) & 0x7f80u) | q.b[3]);
-}
-
 __device__ __forceinline__ uint32_t dynamic_smem_bytes()
 {
     uint32_t v;

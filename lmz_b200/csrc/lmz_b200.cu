@@ -18,6 +18,7 @@
 #include "cond_kernels.cuh"
 #include "fused_kernel.cuh"
 #include "encode_kernel.cuh"
+#include "save_kernels.cuh"
 
 using namespace lmz;
 
@@ -451,6 +452,80 @@ API int lmz_gpu_pack_streams_dev(const void *d_slots, unsigned plane, const void
                                                               (const uint64_t *)d_offsets, nstr, (uint8_t *)d_out);
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return fail_cuda("launch k_pack_streams", le);
+    return LMZ_GPU_OK;
+}
+
+// ---- chunk framing for the save path (no counterpart in the reference's GPU library) --------
+
+static int framing_args(const void *d_src, uint64_t nbytes, unsigned chunk)
+{
+    if (!d_src) return fail_msg(LMZ_GPU_EUNSUPPORTED, "null argument");
+    if (chunk < 2 || (chunk & 1u) || (nbytes & 1u))
+        return fail_msg(LMZ_GPU_EUNSUPPORTED, "chunk size and byte count must be even (whole BF16 elements)");
+    if (nbytes > (uint64_t)chunk * 0x7fffffffu) return fail_msg(LMZ_GPU_EUNSUPPORTED, "too many chunks for one call");
+    return LMZ_GPU_OK;
+}
+
+API int lmz_gpu_split_bf16_dev(const void *d_src, uint64_t nbytes, unsigned chunk, void *d_planes, void *cuda_stream)
+{
+    int rc = device_ready();
+    if (rc) return rc;
+    if (nbytes == 0) return LMZ_GPU_OK;
+    rc = framing_args(d_src, nbytes, chunk);
+    if (rc) return rc;
+    if (!d_planes) return fail_msg(LMZ_GPU_EUNSUPPORTED, "null argument");
+    const unsigned nchunks = (unsigned)((nbytes + chunk - 1) / chunk);
+    k_split_bf16<<<nchunks, 256, 0, (cudaStream_t)cuda_stream>>>((const uint8_t *)d_src, nbytes, chunk, (uint8_t *)d_planes);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch k_split_bf16", le);
+    return LMZ_GPU_OK;
+}
+
+API int lmz_gpu_frame_bf16_dev(const void *d_src, uint64_t nbytes, unsigned chunk, const void *d_lengths,
+                               void *d_meta, const void *d_planes, const void *d_slots, const void *d_offsets,
+                               void *d_out, void *cuda_stream)
+{
+    int rc = device_ready();
+    if (rc) return rc;
+    if (nbytes == 0) return LMZ_GPU_OK;
+    rc = framing_args(d_src, nbytes, chunk);
+    if (rc) return rc;
+    if (!d_lengths || !d_meta) return fail_msg(LMZ_GPU_EUNSUPPORTED, "null argument");
+    const unsigned nchunks = (unsigned)((nbytes + chunk - 1) / chunk), nfull = (unsigned)(nbytes / chunk);
+    cudaStream_t cs = (cudaStream_t)cuda_stream;
+    if (!d_out) {
+        k_frame_decide<<<(nchunks + 127) / 128, 128, 0, cs>>>(nbytes, chunk, nchunks, (const uint32_t *)d_lengths,
+                                                             (FrameMeta *)d_meta);
+    } else {
+        if (!d_planes || !d_slots || !d_offsets) return fail_msg(LMZ_GPU_EUNSUPPORTED, "null argument");
+        const unsigned tail = (unsigned)(nbytes - (uint64_t)nfull * chunk);
+        k_frame_pack<<<nchunks, 256, 0, cs>>>((const uint8_t *)d_src, nbytes, chunk, (const uint32_t *)d_lengths,
+                                              (const FrameMeta *)d_meta, (const uint8_t *)d_planes,
+                                              (const uint8_t *)d_slots, encode_slot_bytes(chunk / 2),
+                                              tail ? encode_slot_bytes(tail / 2) : 0u, nfull,
+                                              (const uint64_t *)d_offsets, (uint8_t *)d_out);
+    }
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch chunk framing", le);
+    return LMZ_GPU_OK;
+}
+
+API int lmz_gpu_crc32_chunks_dev(const void *d_src, uint64_t nbytes, unsigned chunk, const void *d_crc_tables,
+                                 void *d_meta, void *cuda_stream)
+{
+    int rc = device_ready();
+    if (rc) return rc;
+    if (nbytes == 0) return LMZ_GPU_OK;
+    if (!d_src || !d_crc_tables || !d_meta || chunk == 0) return fail_msg(LMZ_GPU_EUNSUPPORTED, "null argument");
+    static bool done[64];
+    constexpr uint32_t shm = 5u * (1024u << 4);       // four tables replicated 16x, and room to align them
+    rc = opt_in_smem(k_crc32_chunks, shm, done);
+    if (rc) return rc;
+    const unsigned nchunks = (unsigned)((nbytes + chunk - 1) / chunk);
+    k_crc32_chunks<<<nchunks, 256, shm, (cudaStream_t)cuda_stream>>>((const uint8_t *)d_src, nbytes, chunk,
+                                                                     (const CrcTables *)d_crc_tables, (FrameMeta *)d_meta);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch k_crc32_chunks", le);
     return LMZ_GPU_OK;
 }
 

@@ -52,6 +52,9 @@ _SIGNATURES = {
     "lmz_gpu_encode_batch_dev": (_C.c_int, [_C.c_void_p, _C.c_uint, _C.c_uint] + [_C.c_void_p] * 3),
     "lmz_gpu_pack_streams_dev": (_C.c_int, [_C.c_void_p, _C.c_uint, _C.c_void_p, _C.c_uint,
                                             _C.c_void_p, _C.c_void_p]),
+    "lmz_gpu_split_bf16_dev": (_C.c_int, [_C.c_void_p, _C.c_uint64, _C.c_uint, _C.c_void_p, _C.c_void_p]),
+    "lmz_gpu_frame_bf16_dev": (_C.c_int, [_C.c_void_p, _C.c_uint64, _C.c_uint] + [_C.c_void_p] * 7),
+    "lmz_gpu_crc32_chunks_dev": (_C.c_int, [_C.c_void_p, _C.c_uint64, _C.c_uint] + [_C.c_void_p] * 3),
 }
 
 

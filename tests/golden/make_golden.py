@@ -1,9 +1,8 @@
 """Generate the golden fixtures in this directory with the REFERENCE itself.
 
-Run in a container where the reference tree is mounted (default
-/root/reference) and oracle/_ref has been built:
+Run where the reference tree is available and oracle/_ref has been built from it:
 
-    python tests/golden/make_golden.py
+    LMZ_REFERENCE=/path/to/lmz python tests/golden/make_golden.py
 
 The reference's Python is imported unmodified; the only shim is that its
 native-core loader is pointed at oracle/_ref/liblmzcore.so (the same C source
@@ -27,7 +26,9 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("LMZ_REFERENCE", "/root/reference")
+REF = os.environ.get("LMZ_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+if not os.path.exists(os.path.join(REF, "lmz", "api.py")):
+    raise SystemExit("set LMZ_REFERENCE to the reference checkout")
 sys.path.insert(0, ROOT)
 sys.path.insert(0, REF)
 
