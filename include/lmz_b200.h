@@ -232,6 +232,7 @@ typedef struct lmz_decode_plan {
     void *d_hist;               /* n_cond x 256 uint32 */
     void *d_piece_cnt;          /* n_pieces x 16 uint32 */
     void *d_piece_wcnt;         /* n_pieces x 64 uint16 */
+    void *d_piece_lcnt;         /* n_cond_pieces x 2048 uint32 (8 KiB per conditioned piece) */
     void *d_piece_crc;          /* n_pieces uint32, or NULL to skip checksums */
     const void *d_crc_tables;
     void *d_chunk_status;       /* uint32 per chunk: 0 ok, 4 bad shape, 5 bad crc */

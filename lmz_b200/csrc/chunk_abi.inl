@@ -50,9 +50,11 @@ static int launch_cond_finish(const FinishArgs &fa, int sms, cudaStream_t cs)
     if (fa.piece_begin >= fa.piece_end) return LMZ_GPU_OK;
     static bool done[64];
     constexpr uint32_t shm = cond_finish_smem();
-    int rc = opt_in_smem(k_cond_finish, shm, done);
+    int rc = stream_smem_ok();                   // the kernel's layout counts on the same shared window as k_stream's
     if (rc) return rc;
-    // one CTA per SM, three pieces in flight in each
+    rc = opt_in_smem(k_cond_finish, shm, done);
+    if (rc) return rc;
+    // one CTA per SM, four pieces in flight in each
     unsigned n = (fa.piece_end - fa.piece_begin + CF_SUBS - 1) / CF_SUBS;
     unsigned grid = n < (unsigned)sms ? n : (unsigned)sms;
     k_cond_finish<<<grid, CF_THREADS, shm, cs>>>(fa);
@@ -278,6 +280,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     }
 
     // 2. exponent-conditioned chunks: histogram -> bucket map -> segment decodes -> ranks
+    if (p->n_cond && !p->d_piece_lcnt) return fail_msg(LMZ_GPU_EUNSUPPORTED, "conditioned chunks without d_piece_lcnt");
     if (p->n_cond && (ph & 2u)) {
         CondArgs c{};
         c.chunks = (const ChunkJob *)p->d_chunks;
@@ -290,6 +293,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         c.hist = (uint32_t *)p->d_hist;
         c.piece_cnt = (uint32_t *)p->d_piece_cnt;
         c.piece_wcnt = (uint16_t *)p->d_piece_wcnt;
+        c.piece_lcnt = (uint32_t *)p->d_piece_lcnt;
         c.seg_jobs = (StreamJob *)p->d_seg_jobs;
         c.payload = (const uint8_t *)p->d_payload;
         c.scratch = (const uint8_t *)p->d_scratch;
@@ -338,6 +342,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
     f.cond_state = (const CondState *)p->d_cond_state;
     f.piece_cnt = (const uint32_t *)p->d_piece_cnt;
     f.piece_wcnt = (const uint16_t *)p->d_piece_wcnt;
+    f.piece_lcnt = (const uint32_t *)p->d_piece_lcnt;
     // piece groups: 0 pass-1 conditioned, 1 pass-1 plain, 2 fused (done above),
     //               3 pass-2 conditioned, 4 pass-2 plain
     if (!(ph & 4u)) CK("join the side stream", scope.join());
@@ -349,6 +354,8 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         }
         f.piece_begin = p->piece_split[part];
         f.piece_end = p->piece_split[part + 1];
+        // the conditioned-piece list holds pass 1's pieces, then pass 2's
+        f.lcnt_first = part == 3 ? p->piece_split[1] - p->piece_split[0] : 0u;
         rc = (part == 0 || part == 3) ? launch_cond_finish(f, sms, cs)
                                       : launch_finish(f, sms, cs);
         if (rc) return rc;

@@ -151,6 +151,9 @@ struct FinishArgs {
     const CondState *cond_state;
     const uint32_t *piece_cnt;     // per piece of a K_COND chunk: 8 bucket populations, 8 running totals
     const uint16_t *piece_wcnt;    // per piece of a K_COND chunk: the populations of its eight 4096-element runs
+    const uint32_t *piece_lcnt;    // per conditioned piece, in the order of the conditioned-piece list: the
+                                   // populations of every lane's 32 elements (k_cond_count, k_cond_finish)
+    uint32_t lcnt_first;           // place of piece_begin in that list
 };
 
 constexpr uint32_t FINISH_THREADS = 256;   // threads that finish one piece together

@@ -51,6 +51,14 @@ __device__ __forceinline__ uint32_t smem_addr(const void *p)
     return (uint32_t)__cvta_generic_to_shared(p);
 }
 
+// Bytes of dynamic shared memory this launch was given.
+__device__ __forceinline__ uint32_t dynamic_smem_bytes()
+{
+    uint32_t v;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(v));
+    return v;
+}
+
 // Loads and stores by 32-bit shared-space address (no generic-pointer arithmetic).
 __device__ __forceinline__ uint32_t lds_u32(uint32_t saddr)
 {

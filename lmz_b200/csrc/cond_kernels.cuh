@@ -16,6 +16,9 @@ struct CondArgs {
     uint32_t *hist;                // ncond x 256, zeroed by the caller
     uint32_t *piece_cnt;           // npieces x 16: 8 populations, then 8 running totals (k_cond_scan)
     uint16_t *piece_wcnt;          // npieces x 8 x 8: the populations of each 4096-element run of a piece
+    uint32_t *piece_lcnt;          // ncond_pieces x 8 runs x 4 blocks x 32 lanes x 2 words: the populations of the
+                                   // 32 consecutive elements one lane of k_cond_finish takes, as 8-bit fields
+                                   // (buckets 0, 2, 4, 6 in the first word, 1, 3, 5, 7 in the second)
     StreamJob *seg_jobs;           // one slot per rANS-coded segment, sized by k_cond_plan
     const uint8_t *payload;
     const uint8_t *scratch;
@@ -34,37 +37,55 @@ __device__ __forceinline__ const uint8_t *cond_exp_piece(const CondArgs &a, uint
 
 // 256-bin histogram of one exponent piece (lmz/native/lmzcore.c:385-397), accumulated in
 // shared memory, then added to the chunk's histogram.  Exponent planes have a handful of
-// popular symbols, so lanes of a warp keep hitting the same counter: every warp has four
-// copies of the histogram (one per lane & 3) to spread those collisions.
+// popular symbols, so the lanes of a warp keep asking for the same counter; every lane
+// therefore has its own copy of the histogram, laid out [bin][lane]: whatever the bins, the
+// 32 additions of a warp go to 32 different banks, and only warps meet on a counter.
 __global__ void __launch_bounds__(256) k_cond_hist(CondArgs a)
 {
-    __shared__ uint32_t h[32][256];
-    const uint32_t t = threadIdx.x, warp = t >> 5, mine = warp * 4 + (t & 3u);
+    __shared__ uint32_t h[256][32];
+    const uint32_t t = threadIdx.x, lane = t & 31;
     for (uint32_t i = t; i < 32 * 256; i += 256) (&h[0][0])[i] = 0;
     __syncthreads();
     uint32_t ci, ne;
     const uint8_t *exp = cond_exp_piece(a, a.cond_pieces[blockIdx.x], ci, ne);
-    // 32 KiB per piece = 32 words per thread; loaded 8 at a time so the reads overlap
-    for (uint32_t i0 = t * 4; i0 < ne; i0 += 256 * 4 * 8) {
-        uint32_t w[8];
+    uint32_t *mine = &h[0][lane];
+    auto add4 = [&](uint32_t w) {
+        atomicAdd(mine + 32u * (w & 0xffu), 1u);
+        atomicAdd(mine + 32u * __byte_perm(w, 0u, 0x4441u), 1u);
+        atomicAdd(mine + 32u * __byte_perm(w, 0u, 0x4442u), 1u);
+        atomicAdd(mine + 32u * (w >> 24), 1u);
+    };
+    if (ne == PIECE_ELEMS && (reinterpret_cast<uintptr_t>(exp) & 15u) == 0) {
+        // a whole piece, aligned: 128 bytes per thread as eight 16-byte loads, all in flight
+        const uint4 *e4 = reinterpret_cast<const uint4 *>(exp) + t;
+        uint4 v[8];
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-            uint32_t i = i0 + u * 256 * 4, v[1] = {0};
-            if (i < ne) load_words<1>(exp + i, v);
-            w[u] = v[0];
-        }
+        for (int u = 0; u < 8; u++) v[u] = e4[u * 256];
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-            uint32_t i = i0 + u * 256 * 4;
+        for (int u = 0; u < 8; u++) { add4(v[u].x); add4(v[u].y); add4(v[u].z); add4(v[u].w); }
+    } else {
+        for (uint32_t i0 = t * 4; i0 < ne; i0 += 256 * 4 * 8) {
+            uint32_t w[8];
 #pragma unroll
-            for (int z = 0; z < 4; z++)
-                if (i + z < ne) atomicAdd(&h[mine][(w[u] >> (8 * z)) & 0xff], 1u);
+            for (int u = 0; u < 8; u++) {
+                uint32_t i = i0 + u * 256 * 4, v[1] = {0};
+                if (i < ne) load_words<1>(exp + i, v);
+                w[u] = v[0];
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                uint32_t i = i0 + u * 256 * 4;
+                if (i + 4 <= ne) add4(w[u]);
+                else
+                    for (uint32_t z = 0; i + z < ne; z++) atomicAdd(mine + 32u * ((w[u] >> (8 * z)) & 0xffu), 1u);
+            }
         }
     }
     __syncthreads();
+    // bin t: its 32 copies, each thread starting at a different one (different banks)
     uint32_t s = 0;
 #pragma unroll
-    for (int w = 0; w < 32; w++) s += h[w][t];
+    for (uint32_t l = 0; l < 32; l++) s += h[t][(l + t) & 31u];
     if (s) atomicAdd(&a.hist[(size_t)ci * 256 + t], s);
 }
 
@@ -124,58 +145,85 @@ __global__ void k_cond_plan(CondArgs a)
     cs.status = status;
 }
 
-// Bucket populations of one exponent piece, for the stable un-partition's ranks: of the
-// piece (piece_cnt) and of each of its eight 4096-element runs (piece_wcnt), one run per
-// warp, which is how k_cond_finish walks the piece.  A symbol's bucket is looked up as a
-// byte (four times the bucket number) and counted as a one-hot word of 4-bit fields, one
-// shared load, a shift and an add per element; every twelve elements the nibbles are spread
-// into 8-bit fields (buckets 0, 2, 4, 6 in one word, 1, 3, 5, 7 in the other), which hold the
-// 128 elements a thread sees.  Half a KiB of shared memory: with the KiB the system reserves
+// Bucket populations of one exponent piece, for the stable un-partition's read positions: of
+// the piece (piece_cnt), of each of its eight 4096-element runs (piece_wcnt; one run per
+// warp, which is how k_cond_finish walks the piece) and of the 32 consecutive elements every
+// lane of that kernel takes in each of a run's four blocks (piece_lcnt).  A symbol's bucket
+// is looked up as a byte (four times the bucket number) and counted as a one-hot word of
+// 4-bit fields: a byte extract, one shared load, a shift and an add per element; every
+// twelve elements the nibbles are spread into 8-bit fields (buckets 0, 2, 4, 6 in one word,
+// 1, 3, 5, 7 in the other).  Half a KiB of shared memory: with the KiB the system reserves
 // per block that still fits beside the segment decodes that run at the same time and leave
 // under 2 KiB of an SM free.
 __global__ void __launch_bounds__(256) k_cond_count(CondArgs a)
 {
-    __shared__ __align__(256) uint32_t both[64 + 8 * COND_BUCKETS];     // one array: no padding between the two
-    uint8_t *hot = reinterpret_cast<uint8_t *>(both);                   // symbol -> 4 * bucket
-    uint32_t (*cnt)[COND_BUCKETS] = reinterpret_cast<uint32_t (*)[COND_BUCKETS]>(both + 64);
+    __shared__ uint8_t hot[256];                          // symbol -> 4 * bucket
+    __shared__ uint32_t cnt[8][COND_BUCKETS];
     const uint32_t t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const uint32_t q = a.cond_pieces[blockIdx.x];
     uint32_t ci, ne;
     const uint8_t *exp = cond_exp_piece(a, q, ci, ne);
     hot[t] = (uint8_t)(4 * a.cond_state[ci].lut[t]);
     __syncthreads();
-    const uint32_t hot_sa = smem_addr(hot);               // 256-byte aligned: an index is OR-ed on
     uint32_t lo = 0, hi = 0, nib = 0;
     auto flush = [&]() {
         lo += nib & 0x0f0f0f0fu;
         hi += (nib >> 4) & 0x0f0f0f0fu;
         nib = 0;
     };
-    // warp w takes elements [4096 w, 4096 w + 4096): 32 words per lane, loaded 8 at a time
-    const uint32_t w0 = warp * (PIECE_ELEMS / 8);
-    for (uint32_t j0 = 0; j0 < 32; j0 += 8) {
-        uint32_t w[8];
+    auto add4 = [&](uint32_t w) {
+        nib += 1u << hot[w & 0xffu];
+        nib += 1u << hot[__byte_perm(w, 0u, 0x4441u)];
+        nib += 1u << hot[__byte_perm(w, 0u, 0x4442u)];
+        nib += 1u << hot[w >> 24];
+    };
+    // warp w takes elements [4096 w, 4096 w + 4096) in four blocks of 1024, lane l the 32
+    // elements from 32 l of each
+    const uint32_t w0 = warp * (PIECE_ELEMS / 8) + lane * 32;
+    uint2 *lc = reinterpret_cast<uint2 *>(a.piece_lcnt) + ((size_t)blockIdx.x * 8 + warp) * 128 + lane;
+    uint32_t run_lo = 0, run_hi = 0;
+    if (ne == PIECE_ELEMS && (reinterpret_cast<uintptr_t>(exp) & 15u) == 0) {
+        // a whole piece, aligned: eight 16-byte loads per lane, all in flight
+        const uint4 *e4 = reinterpret_cast<const uint4 *>(exp + w0);
+        uint4 v[8];
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-            uint32_t i = w0 + (j0 + u) * 128 + lane * 4, v[1] = {0};
-            if (i < ne) load_words<1>(exp + i, v);
-            w[u] = v[0];
+        for (int j = 0; j < 4; j++) { v[2 * j] = e4[j * 64]; v[2 * j + 1] = e4[j * 64 + 1]; }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t w[8] = {v[2 * j].x, v[2 * j].y, v[2 * j].z, v[2 * j].w,
+                                   v[2 * j + 1].x, v[2 * j + 1].y, v[2 * j + 1].z, v[2 * j + 1].w};
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                add4(w[c]);
+                if (c % 3 == 2) flush();                   // twelve additions at most
+            }
+            flush();
+            lc[j * 32] = make_uint2(lo, hi);
+            run_lo += lo; run_hi += hi;
+            lo = hi = 0;
         }
-        const bool whole = w0 + (j0 + 7) * 128 + lane * 4 + 4 <= ne;
+    } else {
+        for (uint32_t j = 0; j < 4; j++) {
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const uint32_t i = w0 + (j0 + u) * 128 + lane * 4;
-            const uint32_t valid = whole ? 4u : (i < ne ? min(ne - i, 4u) : 0u);
-            const uint32_t ix[4] = {w[u] & 0xffu, (w[u] >> 8) & 0xffu, (w[u] >> 16) & 0xffu, w[u] >> 24};
-#pragma unroll
-            for (int z = 0; z < 4; z++)
-                if (whole || (uint32_t)z < valid) nib += 1u << lds_u8(ix[z] | hot_sa);
-            if (u % 3 == 2) flush();                       // at most twelve additions between flushes
+            for (int c = 0; c < 8; c++) {
+                const uint32_t i = w0 + j * 1024 + 4 * c;
+                if (i < ne) {
+                    uint32_t v[1];
+                    load_words<1>(exp + i, v);
+                    if (i + 4 <= ne) add4(v[0]);
+                    else
+                        for (uint32_t z = 0; i + z < ne; z++) nib += 1u << hot[(v[0] >> (8 * z)) & 0xffu];
+                }
+                if (c % 3 == 2) flush();
+            }
+            flush();
+            lc[j * 32] = make_uint2(lo, hi);
+            run_lo += lo; run_hi += hi;
+            lo = hi = 0;
         }
-        flush();
     }
     // 8-bit fields -> 16-bit fields (a warp sees at most 4096 elements), then a butterfly
-    uint32_t f[4] = {lo & 0x00ff00ffu, (lo >> 8) & 0x00ff00ffu, hi & 0x00ff00ffu, (hi >> 8) & 0x00ff00ffu};
+    uint32_t f[4] = {run_lo & 0x00ff00ffu, (run_lo >> 8) & 0x00ff00ffu, run_hi & 0x00ff00ffu, (run_hi >> 8) & 0x00ff00ffu};
 #pragma unroll
     for (int j = 0; j < 4; j++) {
 #pragma unroll

@@ -269,13 +269,6 @@ __device__ __forceinline__ uint32_t stream_step4(uint32_t &x, uint32_t &hist, ui
     return e;
 }
 
-__device__ __forceinline__ uint32_t dynamic_smem_bytes()
-{
-    uint32_t v;
-    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(v));
-    return v;
-}
-
 template <int SINK, bool CRC, int WARPS, int CFN>
 __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 : 1) k_stream(StreamArgs a)
 {

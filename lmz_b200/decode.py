@@ -106,6 +106,7 @@ class ArchiveDecoder:
             self.d_hist = torch.zeros(max(1, ncond * 256), **u32)
             self.d_piece_cnt = torch.zeros(max(1, p.n_pieces * 16), **u32)
             self.d_piece_wcnt = torch.zeros(max(1, p.n_pieces * 64 if ncond else 1), dtype=torch.int16, device=d)
+            self.d_piece_lcnt = torch.empty(max(1, p.cond_pieces.size * 2048), **u32)
             self.d_piece_crc = torch.zeros(max(1, p.n_pieces), **u32)
             self.d_stream_status = torch.zeros(max(1, p.stream_jobs.size), **u32)
             self.d_seg_status = torch.zeros(max(1, p.seg_jobs.size), **u32)
@@ -131,6 +132,7 @@ class ArchiveDecoder:
         c.d_cond_pieces = self.d_cond_pieces.data_ptr()
         c.d_hist, c.d_piece_cnt = self.d_hist.data_ptr(), self.d_piece_cnt.data_ptr()
         c.d_piece_wcnt = self.d_piece_wcnt.data_ptr()
+        c.d_piece_lcnt = self.d_piece_lcnt.data_ptr()
         c.d_piece_crc = self.d_piece_crc.data_ptr() if checksum else None
         c.d_crc_tables = self.d_tabs.data_ptr()
         c.d_chunk_status, c.d_chunk_crc = self.d_chunk_status.data_ptr(), self.d_chunk_crc.data_ptr()
