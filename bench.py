@@ -461,6 +461,7 @@ def main():
         # end to end: every rank uploads only the stretch of the payload its own chunks lie in,
         # from its own page-locked registration of that stretch, decodes, reads its verdicts back
         lo, hi = sd.payload_range if sd.payload_range else (0, 0)
+        unpin_host(pinned)                       # the whole-archive registration of the replica leg
         own_pin = pin_host(np.asarray(blob[lo:hi]))
         nck = sd.decoder.plan.chunks.size
         res = torch.empty(nck + 1, dtype=torch.int32).pin_memory()
@@ -491,6 +492,7 @@ def main():
                         "h2d_gbs_all_ranks": round(float(h2d_all.item()) / pe2e / 1e9, 1)},
                 "what": f"one archive, chunks partitioned over {world} GPUs by output range, each rank uploading "
                         f"and decoding only its share into its own HBM (no collective)"}
+        unpin_host(own_pin)
         del sd, own_pin
         # optional full replica on every rank: equal output slices, one in-place NCCL all-gather
         sr = multi.ShardedDecoder(dec.archive, rank, world, checksum=not a.no_crc, replica=True)
@@ -902,17 +904,32 @@ def cpu_baseline_subprocess(a):
     return json.loads(r.stdout.strip().splitlines()[-1])["cpu_baseline"]
 
 
+_REGISTERED = set()
+
+
 def pin_host(arr):
     """A pinned host tensor over `arr`: the mapped archive is page-locked in place
-    (no second copy per rank); if that is refused, a pinned copy is made."""
+    (no second copy per rank); if that is refused, a pinned copy is made.  A range must
+    not be registered twice (the runtime keeps the refusal as its last error): release
+    the earlier registration with `unpin_host` first."""
     import torch
     t = torch.from_numpy(arr)
     rc = int(torch.cuda.cudart().cudaHostRegister(t.data_ptr(), t.numel(), 0))
     if rc == 0:
+        _REGISTERED.add(t.data_ptr())
         return t
     c = torch.empty(t.numel(), dtype=torch.uint8).pin_memory()
     c.copy_(t)
     return c
+
+
+def unpin_host(t):
+    """Undo `pin_host`'s registration of `t` (nothing to do for a pinned copy)."""
+    import torch
+    if t.data_ptr() in _REGISTERED:
+        torch.cuda.synchronize()
+        torch.cuda.cudart().cudaHostUnregister(t.data_ptr())
+        _REGISTERED.discard(t.data_ptr())
 
 
 def verify_sample(dec, blob, nsample: int = 24):
