@@ -62,10 +62,7 @@ __host__ __device__ constexpr uint32_t stream_stage(int cfn, int warps) { return
 constexpr uint32_t F_LOGS = 3;                     // eight copies of the CRC slice tables (32 KiB), one per lane of a group: see CrcQuarters
 constexpr uint32_t F_CRC_BYTES = (4096u << F_LOGS) + 4096u;   // + the row-advance tables, once
 constexpr uint32_t F_ROW = 256, F_UNIT = 32;       // bytes of BF16 one group / one lane emits per tile
-#ifndef LMZ_SMALL_CFN
-#define LMZ_SMALL_CFN 128
-#endif
-constexpr int F_SMALL_CFN = LMZ_SMALL_CFN;         // level-2 slots of the dense instance
+constexpr int F_SMALL_CFN = 128;         // level-2 slots of the dense instance
 constexpr uint32_t F_SMALL_LIVE = F_SMALL_CFN - 24; // largest alphabet it takes (the warp's streams sit 0, 8, 16, 24 entries in)
 
 struct FusedJob {
@@ -129,11 +126,7 @@ __host__ __device__ constexpr uint32_t stream_crc_slice(uint32_t top)
 }
 // The BF16 sink's checksum needs no row-advance tables (see k_stream), so the 4 KiB they
 // would take, above the slice tables, hold the level-1 tables of the CTA's last warp.
-#ifdef LMZ_X_NO_TOPL1
-__host__ __device__ constexpr bool stream_top_l1(int, bool, int) { return false; }
-#else
 __host__ __device__ constexpr bool stream_top_l1(int sink, bool crc, int cfn) { return sink == SINK_BF16 && crc && cfn > 0; }
-#endif
 __host__ __device__ constexpr int stream_warps(int cfn, bool crc, int sink = SINK_BYTES)
 {
     constexpr uint32_t top = F_SMEM_BASE + F_SMEM_DYN;

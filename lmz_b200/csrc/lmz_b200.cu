@@ -150,9 +150,6 @@ static int launch_stream(const StreamArgs &a0, cudaStream_t cs)
         if (!DIRECT) per = (per + 3u) & ~3u;
         if (per > groups) per = groups;
     }
-#ifdef LMZ_EXPERIMENT
-    if (const char *e = getenv("LMZ_X_PER_CTA")) { unsigned v = (unsigned)atoi(e); if (v >= 4 && v <= groups) per = v & ~3u; }
-#endif
     a.per_cta = per;
     unsigned blocks = (a.njobs + per - 1) / per;
     k_stream<SINK, CRC, WARPS, CFN><<<blocks, WARPS * 32, shm, cs>>>(a);

@@ -95,7 +95,7 @@ def _gather(blob: np.ndarray, offs: np.ndarray, width: int) -> np.ndarray:
 # stream slots (148 x 76) is bound by each warp's own instruction stream, and there the
 # two-pass path (lean stream kernel, then the merge kernel) measured faster.
 FUSE_F32_MIN = 8192
-SMALL_LIVE = int(__import__('os').environ.get('LMZ_X_SMALL_LIVE', 104))       # largest alphabet the denser fused-kernel instance takes (csrc/fused_kernel.cuh)
+SMALL_LIVE = 104       # largest alphabet the denser fused-kernel instance takes (csrc/fused_kernel.cuh)
 
 
 def _alphabet_sizes(blob: np.ndarray, offs: np.ndarray) -> np.ndarray:
