@@ -307,11 +307,12 @@ class PipelinedDecoder:
 
 class Staging:
     """Page-locked staging between a file and the device: `depth` buffers of `block`
-    bytes and the threads that fill and send them."""
+    bytes and the threads that fill and send them.  (Six threads: on a 16-core host four
+    leave the link idle at times and eight or more slow the planning that runs beside them.)"""
 
     _shared = None
 
-    def __init__(self, block: int = 32 << 20, depth: int = 6, threads: int = 4):
+    def __init__(self, block: int = 32 << 20, depth: int = 8, threads: int = 6):
         import concurrent.futures
 
         import torch
