@@ -144,8 +144,9 @@ class ArchiveDecoder:
         for i in range(6):
             c.piece_split[i] = int(p.piece_split[i])
         self._c = c
-        # kernels launched by one run(): stream decode, 3 cond kernels + segment decode,
-        # up to four finish launches, the verdict kernel
+        # kernels launched by one run(): stream decode; histogram, bucket map, counting, running
+        # totals and the segment decode of conditioned chunks; up to four finish launches; the
+        # verdict kernel
         nbf = p.n_fused - p.n_fused_f32
         if p.device_classify:                # per group: the count kernel and both instances
             fused_launches = 3 * ((1 if nbf else 0) + (1 if p.n_fused_f32 else 0))
@@ -153,7 +154,8 @@ class ArchiveDecoder:
             fused_launches = (1 if p.n_fused_small else 0) + (1 if nbf > p.n_fused_small else 0) + \
                 (1 if p.n_fused_f32_small else 0) + (1 if p.n_fused_f32 > p.n_fused_f32_small else 0)
         fused_launches += 1 if p.n_fused_t else 0
-        self.launches_per_run = (1 if p.stream_jobs.size else 0) + (4 if ncond else 0) + fused_launches + \
+        self.launches_per_run = (1 if p.stream_jobs.size else 0) + \
+            ((4 + (1 if p.seg_jobs.size else 0)) if ncond else 0) + fused_launches + \
             int(sum(p.piece_split[i + 1] > p.piece_split[i] for i in (0, 1, 3, 4))) + 1
 
     def upload(self, pinned=None, non_blocking: bool = False):

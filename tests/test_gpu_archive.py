@@ -143,6 +143,29 @@ def test_delta_chain_and_refs():
         assert {4, 8} <= codecs, codecs
 
 
+@pytest.mark.parametrize("name", ["t", "tt", "ttt", "tttt"])
+def test_conditioned_chunk_with_a_stored_exponent_plane(name):
+    """Exponent bytes that do not compress (uniform) under a sign/mantissa byte that depends
+    on the exponent's bucket: the encoder conditions the chunk and stores the exponent plane as
+    it is, so the histogram, the counting and the finish read it from the payload at whatever
+    byte offset it landed on (the tensor's name moves it), and the chunk ends in a ragged piece."""
+    from oracle import codec
+    rng = np.random.default_rng(3)
+    n = (1 << 20) + 12345
+    e = rng.integers(0, 256, n).astype(np.uint16)
+    noise = rng.random(n) < 0.03
+    b = np.where(noise, rng.integers(0, 256, n), (e // 32) * 17 + 3).astype(np.uint16)
+    w = (((b & 0x80) << 8) | (e << 7) | (b & 0x7F)).astype("<u2").view(np.uint8)
+    src = synth.safetensors_bytes([(name, "BF16", (n,), w)])
+    blob = oa.write_archive([("m.safetensors", src)])
+    recs = oa.Archive(blob).records
+    cond = [r for r in recs if r["codec"] == codec.CODEC_BF16C]
+    assert len(cond) == 1
+    head = codec.BF16C_HDR.unpack_from(np.frombuffer(blob, dtype=np.uint8), int(cond[0]["off"]))
+    assert head[1] == 0 and 3 in head[2:10], "exponent plane stored, some segment coded"
+    _roundtrip(blob, src)
+
+
 def test_tiny_and_odd_members():
     rng = np.random.default_rng(0)
     members = [("a.bin", rng.integers(0, 4, 100001, dtype=np.uint8)),      # one rANS-coded byte stream
