@@ -28,18 +28,18 @@ API int lmz_gpu_crc_tables(void *host_dst, size_t cap)
     return (int)sizeof(CrcTables);
 }
 
-// Plain pieces: 4 sub-blocks (1024 threads) share CRC tables replicated 16x, one CTA per SM.
+// Plain pieces: 4 sub-blocks (1024 threads) share one set of CRC tables.
 static int launch_finish(const FinishArgs &fa, int sms, cudaStream_t cs)
 {
     if (fa.piece_begin >= fa.piece_end) return LMZ_GPU_OK;
-    constexpr int LOGR = 4, SUBS = 4;
+    constexpr int SUBS = 4;
     static bool done[64];
-    constexpr uint32_t shm = finish_smem(LOGR, SUBS);
-    int rc = opt_in_smem(k_finish<LOGR, SUBS>, shm, done);
+    constexpr uint32_t shm = finish_smem(SUBS);
+    int rc = opt_in_smem(k_finish<SUBS>, shm, done);
     if (rc) return rc;
     unsigned n = (fa.piece_end - fa.piece_begin + SUBS - 1) / SUBS;
     unsigned grid = n < (unsigned)sms ? n : (unsigned)sms;
-    k_finish<LOGR, SUBS><<<grid, FINISH_THREADS * SUBS, shm, cs>>>(fa);
+    k_finish<SUBS><<<grid, FINISH_THREADS * SUBS, shm, cs>>>(fa);
     cudaError_t le = cudaGetLastError();
     if (le != cudaSuccess) return fail_cuda("launch k_finish", le);
     return LMZ_GPU_OK;

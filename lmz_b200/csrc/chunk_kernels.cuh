@@ -158,21 +158,15 @@ struct FinishArgs {
 
 constexpr uint32_t FINISH_THREADS = 256;   // threads that finish one piece together
 
-// Shared memory of k_finish:
-//   CRC tables, replicated.  A table lookup is indexed by data, so 32 lanes hit
-//   random banks; with one copy that serialises about 3.4x and made the kernel
-//   shared-memory bound.  Copy r of entry i sits at word i*R + r, which confines a
-//   copy to 32/R banks; lane l uses copy l % R, so with R = 16 two lanes share two
-//   banks.  Eight tables (4 slice + 4 advance) of 1 KiB * R each, the block aligned
-//   to one table's size so an address is (index bits) | (lane's base) in one LOP3.
-//   Then, per 256-thread sub-block, 2 KiB of reduction scratch.
-__host__ __device__ constexpr uint32_t finish_table_bytes(int logr) { return 8u * (1024u << logr); }
+// Shared memory of k_finish: the "multiply by x^(8 * 4096)" tables (one 4 KiB row of a piece
+// further on) in the bank-quartered layout of CrcQuarters, 32 KiB on a 32 KiB boundary of
+// the shared window; then, per 256-thread sub-block, 2 KiB of reduction scratch.
+constexpr uint32_t FINISH_TABLE_BYTES = 32768;
 __host__ __device__ constexpr uint32_t finish_sub_bytes() { return 2048; }
-__host__ __device__ constexpr uint32_t finish_smem(int logr, int subs)
+__host__ __device__ constexpr uint32_t finish_smem(int subs)
 {
-    return finish_table_bytes(logr) + (1024u << logr) /*alignment slack*/ + subs * finish_sub_bytes();
+    return 2 * FINISH_TABLE_BYTES /*the tables, wherever their boundary falls*/ + subs * finish_sub_bytes();
 }
-
 
 // Replicated-table CRC steps.  `tl` = shared address of this lane's copy of table 0;
 // table j lives j table-sizes further on.
@@ -208,32 +202,47 @@ __device__ __forceinline__ uint32_t crc_advance(uint32_t tl, uint32_t s)
            lds_u32(crc_index<LOGR, 2>(tl, s) + 6 * TS) ^ lds_u32(crc_index<LOGR, 3>(tl, s) + 7 * TS);
 }
 
-// LOGR = log2 of the CRC table replication, SUBS = 256-thread sub-blocks per CTA
-// sharing one table set.  Exponent-conditioned chunks go to k_cond_finish instead.
-template <int LOGR, int SUBS>
+// SUBS = 256-thread sub-blocks per CTA sharing one table set.  Exponent-conditioned chunks
+// go to k_cond_finish instead.
+//
+// Checksum: a thread writes the same 16 bytes of every 4 KiB row of a piece.  It keeps one
+// running value per word of them, ra[i] = sum over the rows so far of word i * x^(32768 *
+// rows since): a row costs each of the four one multiplication by x^32768 -- four table
+// lookups with no chain between the four values and no separate advance step -- and at the
+// piece's end the four are joined as if they were a 16-byte message of their own.
+template <int SUBS>
 __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
 {
     extern __shared__ __align__(16) uint8_t fsm[];
-    constexpr uint32_t TS = 1024u << LOGR;
     const uint32_t sub = threadIdx.x / FINISH_THREADS, t = threadIdx.x % FINISH_THREADS;
     const uint32_t lane = t & 31, warp = t >> 5;
-    const uint32_t tab0 = (smem_addr(fsm) + TS - 1) & ~(TS - 1);      // shared address, TS-aligned
-    uint8_t *after = fsm + (tab0 - smem_addr(fsm)) + finish_table_bytes(LOGR);
+    const uint32_t tab0 = (smem_addr(fsm) + FINISH_TABLE_BYTES - 1) & ~(FINISH_TABLE_BYTES - 1);
+    uint8_t *after = fsm + (tab0 - smem_addr(fsm)) + FINISH_TABLE_BYTES;
     uint8_t *sb = after + sub * finish_sub_bytes();
     uint32_t *s_red = reinterpret_cast<uint32_t *>(sb);               // 512 words of scratch
     const bool do_crc = a.piece_crc != nullptr;
-    const uint32_t tl = tab0 + 4 * (lane & ((1u << LOGR) - 1));
-    // slice tables are tables 0..3 (slice[0..3]), advance tables 4..7 (adv[0..3])
+    // byte m of a running value goes through table m, which crc_feed4q looks for in slot 3 - m
+    CrcQuarters cq;
+    {
+        const uint32_t k = lane & 7u, g = lane >> 3;
+#pragma unroll
+        for (uint32_t i = 0; i < 4; i++) cq.b[i] = tab0 + 32u * (3u - ((i + g) & 3u)) + 4u * k;
+        cq.rot = 8u * g;
+    }
     auto sub_sync = [&]() {
         if (SUBS == 1) __syncthreads();
         else asm volatile("bar.sync %0, %1;" ::"r"(sub + 1), "n"(FINISH_THREADS) : "memory");
     };
+    // one row into the running values
+    auto crc_row = [&](uint32_t (&ra)[4], const uint32_t (&w)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) ra[i] = crc_feed4q(cq, ra[i]) ^ w[i];
+    };
 
     if (do_crc) {
         uint32_t *tw = reinterpret_cast<uint32_t *>(fsm + (tab0 - smem_addr(fsm)));
-        const uint32_t *src = &a.tabs->slice[0][0];                   // slice then adv, contiguous
-        for (uint32_t i = threadIdx.x; i < 8u * 256u << LOGR; i += FINISH_THREADS * SUBS)
-            tw[i] = src[i >> LOGR];
+        for (uint32_t i = threadIdx.x; i < FINISH_TABLE_BYTES / 4; i += FINISH_THREADS * SUBS)
+            tw[i] = a.tabs->mul_row4096[3u - ((i >> 3) & 3u)][i >> 5];
     }
     __syncthreads();
 
@@ -254,7 +263,7 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
         if (kind == K_COPY && c.src_is_out) pl[0] = a.out + c.plane_off[0];
 
         // ---- rows: every thread produces 16 output bytes per row ----------------
-        uint32_t acc = 0;
+        uint32_t ra[4] = {0, 0, 0, 0};
         // Fast path for the overwhelmingly common piece: full, 16-byte aligned, no delta
         // base, copy or BF16 merge.  No per-row dispatch, loads on the read-only path and
         // four rows unrolled so the loads of later rows overlap the CRC chain of earlier ones.
@@ -276,11 +285,7 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
                         bf16_merge8(pa, pb, w);
                     }
                     *reinterpret_cast<uint4 *>(dst + r) = make_uint4(w[0], w[1], w[2], w[3]);
-                    if (do_crc) {
-                        acc = crc_advance<LOGR>(tl, acc);
-#pragma unroll
-                        for (int i = 0; i < 4; i++) acc = crc_feed4<LOGR>(tl, acc ^ w[i]);
-                    }
+                    if (do_crc) crc_row(ra, w);
                 }
             };
             if (kind == K_COPY) rows(std::integral_constant<int, K_COPY>{});
@@ -356,13 +361,13 @@ __global__ void __launch_bounds__(FINISH_THREADS * SUBS) k_finish(FinishArgs a)
                     }
                 }
             }
-            if (do_crc) {
-                acc = crc_advance<LOGR>(tl, acc);
-#pragma unroll
-                for (int i = 0; i < 4; i++) acc = crc_feed4<LOGR>(tl, acc ^ w[i]);
-            }
+            if (do_crc) crc_row(ra, w);
         }
         if (do_crc) {
+            // the four running values as one 16-byte message (tables in global memory: once per piece)
+            uint32_t acc = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc = crc_word(a.tabs->slice, acc, ra[i]);
             uint32_t v = crc_mulmod(a.tabs->lane_mul[t], acc);
 #pragma unroll
             for (int d = 16; d; d >>= 1) v ^= __shfl_xor_sync(0xffffffffu, v, d);
