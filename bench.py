@@ -540,7 +540,8 @@ def main():
     finish_bytes = int(coded - f_coded - f_stored - p.stream_jobs["src_len"].sum()
                        + p.stream_jobs["n"].sum() + fin_plain + p.base_bytes)
     kbytes = {"stream_decode": stream_bytes, "finish": finish_bytes, "fused": fused_bytes}
-    kname = {"stream_decode": "k_rans / k_stream<bytes>", "finish": "k_finish",
+    kname = {"stream_decode": "k_rans / k_stream<bytes>",
+             "finish": "k_stream<delta> + k_finish" if p.delta_jobs.size else "k_finish",
              "fused": "k_stream<f32>" if p.n_fused_f32 * 2 > fj.size + tj.size else
                       "k_stream<bf16, shared tables>" if tj.size > fj.size else "k_stream<bf16>"}
     dom = max(kbytes, key=lambda k: phase_ms[k])

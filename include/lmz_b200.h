@@ -195,6 +195,8 @@ int lmz_gpu_shared_group(void);
 /* Output bytes one thread block finishes at a time (65536); chunks are cut into
  * pieces of this size and checksummed piecewise. */
 int lmz_gpu_piece_bytes(void);
+/* sizeof the delta job of lmz_decode_plan.d_delta_jobs (48). */
+int lmz_gpu_delta_job_bytes(void);
 
 /* Fill host_dst with the CRC-32 tables the finish kernel reads (upload them once
  * per device).  Returns the size in bytes; if cap is too small nothing is written. */
@@ -224,6 +226,11 @@ typedef struct lmz_decode_plan {
                                  * n_fused_f32 chunks of 4-byte elements (coded top byte plane, three
                                  * stored planes), the first n_fused_f32_small of them small likewise */
     void *d_fused_status;       /* uint32 per fused job */
+    const void *d_delta_jobs;   /* delta chunks whose difference is a BF16 chunk with both planes coded: decoded,
+                                 * merged, XOR-ed with their base and checksummed by one kernel once the chunks they
+                                 * are differences against have been written (csrc/fused_kernel.cuh, DeltaJob) */
+    void *d_delta_status;       /* uint32 per stream: two per delta job */
+    void *d_delta_order;        /* n_delta + 2 uint32 of work space (the jobs sorted by alphabet size on the device) */
     const void *d_chunks;       /* chunk jobs, ordered: pass 1 cond, pass 1 plain, fused, pass 2 cond, pass 2 plain */
     const void *d_piece_chunk;  /* uint32 per piece: its chunk */
     const void *d_cond_jobs;
@@ -252,6 +259,7 @@ typedef struct lmz_decode_plan {
                                  * d_fused_status), `flags` = table number in d_tables, listed table by table
                                  * and each table's run padded with empty jobs (n = 0) to a multiple of
                                  * lmz_gpu_shared_group() */
+    uint32_t n_delta;           /* jobs in d_delta_jobs */
     uint32_t piece_split[6];    /* piece-id boundaries of the five chunk groups */
     uint32_t phases;            /* 0 = everything; else bit 0 stream decode, bit 1 conditioned-chunk
                                  * kernels, bit 2 finish, bit 3 verdicts, bit 4 fused chunks

@@ -17,6 +17,7 @@ API int lmz_gpu_struct_sizes(unsigned *out5)
 
 API int lmz_gpu_piece_bytes(void) { return (int)PIECE_BYTES; }
 API int lmz_gpu_shared_group(void) { return F_SHARED_SINK_WARPS * 4; }
+API int lmz_gpu_delta_job_bytes(void) { return (int)sizeof(DeltaJob); }
 
 API int lmz_gpu_crc_tables(void *host_dst, size_t cap)
 {
@@ -350,6 +351,38 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         if (part == 2) {
             // pass 2 (and the verdicts) read what the fused kernel wrote
             CK("join the side stream", scope.join());
+            if (p->n_delta) {
+                // delta chunks with both planes coded, now that the chunks they are differences against are in place
+                if (!p->d_delta_jobs || !p->d_delta_status) return fail_msg(LMZ_GPU_EUNSUPPORTED, "delta jobs without their arrays");
+                StreamArgs da{};
+                da.src = (const uint8_t *)p->d_payload;
+                da.djobs = (const DeltaJob *)p->d_delta_jobs;
+                da.njobs = 2 * p->n_delta;
+                da.dst = (uint8_t *)p->d_out;
+                da.status = (uint32_t *)p->d_delta_status;
+                da.any_bad = (uint32_t *)p->d_any_bad;
+                da.piece_crc = (uint32_t *)p->d_piece_crc;
+                da.tabs = (const CrcTables *)p->d_crc_tables;
+                // alphabets counted on the device: chunks whose two planes both have small ones to the denser instance
+                uint32_t *order = (uint32_t *)p->d_delta_order;
+                if (!order) return fail_msg(LMZ_GPU_EUNSUPPORTED, "delta jobs without d_delta_order");
+                uint32_t *counts = order + p->n_delta;
+                CK("memset delta counts", cudaMemsetAsync(counts, 0, 8, cs));
+                StreamArgs ca = da;
+                ca.njobs = p->n_delta;
+                k_classify<<<(p->n_delta + 7) / 8, 256, 0, cs>>>(ca, F_SMALL_LIVE, order, counts);
+                cudaError_t le = cudaGetLastError();
+                if (le != cudaSuccess) return fail_cuda("launch k_classify", le);
+                da.order = order;
+                const bool crc = p->d_piece_crc != nullptr;
+                for (int big = 0; big < 2 && !rc; big++) {
+                    da.count = counts + big;
+                    da.order_from_back = big;
+                    rc = big ? (crc ? launch_stream<SINK_DELTA, true, 256>(da, cs) : launch_stream<SINK_DELTA, false, 256>(da, cs))
+                             : (crc ? launch_stream<SINK_DELTA, true, F_SMALL_CFN>(da, cs) : launch_stream<SINK_DELTA, false, F_SMALL_CFN>(da, cs));
+                }
+                if (rc) return rc;
+            }
             continue;
         }
         f.piece_begin = p->piece_split[part];

@@ -46,6 +46,7 @@ struct CrcTables {
     uint32_t mul_row512[4][256];  // multiply a state by x^(8 * 512): one 512-byte warp row (k_cond_finish)
     uint32_t word_mul512[32][4];  // x^(32 * (128 - 4l - i)): word i of lane l's 16-byte unit to that row's end
     uint32_t warp_mul8k[8];       // x^(8 * 8192 * (7 - w)): warp w's 8 KiB run to the piece's end
+    uint32_t word_mul16[16][4];   // x^(32 * (64 - 4j - i)): word i of the j-th 16-byte unit of a 256-byte row to the row's end (delta sink)
     uint32_t mul_row4096[4][256]; // multiply a state by x^(8 * 4096): one row of a piece (k_finish)
     uint32_t mul_gap1984[4][256]; // multiply a state by x^(8 * 1984): from the end of a lane's 64 bytes of one
                                   // 2 KiB warp block to the start of its 64 bytes of the next (k_cond_finish)
@@ -117,6 +118,8 @@ inline void crc_build_tables(CrcTables &t)
     for (uint32_t l = 0; l < 32; l++)
         for (uint32_t i = 0; i < 4; i++) t.word_mul512[l][i] = crc_xpow(t.x2, 32ull * (128 - 4 * l - i));
     for (uint32_t w = 0; w < 8; w++) t.warp_mul8k[w] = crc_xpow(t.x2, 8ull * 8192 * (7 - w));
+    for (uint32_t j = 0; j < 16; j++)
+        for (uint32_t i = 0; i < 4; i++) t.word_mul16[j][i] = crc_xpow(t.x2, 32ull * (64 - 4 * j - i));
     uint32_t row4096 = crc_xpow(t.x2, 8ull * ROW_BYTES);
     for (int j = 0; j < 4; j++)
         for (uint32_t i = 0; i < 256; i++) t.mul_row4096[j][i] = crc_mulmod(row4096, i << (8 * j));

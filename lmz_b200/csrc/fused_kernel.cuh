@@ -36,7 +36,7 @@
 
 namespace lmz {
 
-enum : int { SINK_BYTES = 0, SINK_BF16 = 1, SINK_F32 = 2 };
+enum : int { SINK_BYTES = 0, SINK_BF16 = 1, SINK_F32 = 2, SINK_DELTA = 3 };
 constexpr uint32_t F_SLOT = 128, F_NSLOT = 4, F_RING = F_SLOT * F_NSLOT;
 constexpr uint32_t F_MIRROR = 272;                 // a tile reads at most 256 + 2 bytes ahead
 constexpr uint32_t F_RING_BYTES = F_RING + F_MIRROR;        // 784
@@ -77,10 +77,25 @@ struct FusedJob {
 };
 static_assert(sizeof(FusedJob) == 40, "FusedJob layout is shared with the host");
 
+// SINK_DELTA: a delta chunk (lmz/codec.py:1012-1057) whose difference is a CODEC_BF16 chunk
+// with both planes rANS-coded.  Two neighbouring stream groups of a warp decode the two
+// planes in step; the merged difference is XOR-ed with the base bytes, which are already in
+// the output space, and written once.
+struct DeltaJob {
+    uint64_t src_a, src_b;   // the exponent plane's and the sign/mantissa plane's streams
+    uint64_t dst_off;        // first output byte
+    uint64_t base_off;       // the chunk this one is a difference against, in the output space
+    uint32_t len_a, len_b;
+    uint32_t n;              // elements
+    uint32_t piece0;
+};
+static_assert(sizeof(DeltaJob) == 48, "DeltaJob layout is shared with the host");
+
 struct StreamArgs {
     const uint8_t *src;
     const FusedJob *jobs;       // SINK_BF16 jobs, or NULL
     const StreamJob *sjobs;     // plain stream jobs, or NULL
+    const DeltaJob *djobs;      // SINK_DELTA: njobs counts streams, two per job
     const uint64_t *offs;       // neither: reference layout, (offset, length) pairs + plane
     uint32_t plane;
     uint32_t njobs;
@@ -126,7 +141,7 @@ __host__ __device__ constexpr uint32_t stream_crc_slice(uint32_t top)
 }
 // The BF16 sink's checksum needs no row-advance tables (see k_stream), so the 4 KiB they
 // would take, above the slice tables, hold the level-1 tables of the CTA's last warp.
-__host__ __device__ constexpr bool stream_top_l1(int sink, bool crc, int cfn) { return sink == SINK_BF16 && crc && cfn > 0; }
+__host__ __device__ constexpr bool stream_top_l1(int sink, bool crc, int cfn) { return (sink == SINK_BF16 || sink == SINK_DELTA) && crc && cfn > 0; }
 __host__ __device__ constexpr int stream_warps(int cfn, bool crc, int sink = SINK_BYTES)
 {
     constexpr uint32_t top = F_SMEM_BASE + F_SMEM_DYN;
@@ -270,7 +285,8 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
     // costs each of them one multiplication by x^2048 (the same four lookups as feeding a
     // word) with no chain between the eight and no per-row advance; the constants
     // word_mul[k][i] carry them to the piece's end.
-    constexpr bool ROWMUL = SINK == SINK_BF16 && CRC;
+    constexpr bool ROWMUL = (SINK == SINK_BF16 || SINK == SINK_DELTA) && CRC;
+    constexpr int NRA = SINK == SINK_DELTA ? 4 : 8;        // running values per lane: words of its unit of a row
     constexpr bool TOPL1 = stream_top_l1(SINK, CRC, CFN);
     extern __shared__ __align__(16) uint8_t ssm[];
     constexpr bool WIDE = CFN <= 0, SHARED = CFN < 0;
@@ -326,15 +342,23 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
     const uint32_t idx = blockIdx.x * per_cta + gi;
     uint32_t limit = a.njobs;
     if (a.count) {
-        limit = *a.count;
+        limit = SINK == SINK_DELTA ? 2u * *a.count : *a.count;     // (delta: the count is of chunks, two streams each)
         if (blockIdx.x * per_cta >= limit) return;    // the whole CTA: nothing of this class is left
     }
     const bool have = gi < per_cta && idx < limit;
-    const uint32_t job = (have && a.order) ? a.order[a.order_from_back ? a.njobs - 1 - idx : idx] : idx;
+    // (SINK_DELTA: `order` lists chunks; stream 2c + p is plane p of chunk c)
+    const uint32_t job = !(have && a.order) ? idx
+                       : SINK == SINK_DELTA ? 2u * a.order[a.order_from_back ? a.njobs / 2 - 1 - (idx >> 1) : idx >> 1] + (idx & 1u)
+                                            : a.order[a.order_from_back ? a.njobs - 1 - idx : idx];
     uint64_t soff = 0, doff = 0, moff = 0;
     uint32_t slen = 0, n = 0, piece0 = 0;
     if (have) {
-        if (a.jobs) {
+        if (SINK == SINK_DELTA) {
+            // groups 2c and 2c + 1 of the CTA take the two planes of its chunk c
+            const DeltaJob j = a.djobs[job >> 1];
+            soff = (job & 1u) ? j.src_b : j.src_a; slen = (job & 1u) ? j.len_b : j.len_a;
+            doff = j.dst_off; moff = j.base_off; n = j.n; piece0 = j.piece0;
+        } else if (a.jobs) {
             FusedJob j = a.jobs[job];
             soff = j.src_off; doff = j.dst_off; moff = j.mant_off;
             slen = j.src_len; n = j.n; piece0 = j.piece0;
@@ -448,13 +472,17 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
     uint8_t *out = a.dst + doff;
     const uint32_t al = (uint32_t)(reinterpret_cast<uintptr_t>(out) & 15u);
 
-    // SINK_BF16: the stored plane, read as aligned words and funnel-shifted
-    const uint8_t *mant = a.src + moff + 16 * k;
+    // SINK_BF16: the stored plane, read as aligned words and funnel-shifted.
+    // SINK_DELTA: the base bytes in the output space, likewise; a tile of a chunk is 256 bytes
+    // of output, of which lane k of the chunk's first group takes the 16 from 16 k and lane k
+    // of its second group the 16 from 128 + 16 k.
+    const uint32_t j16 = 8u * (g & 1u) + k;
+    const uint8_t *mant = SINK == SINK_DELTA ? a.dst + moff + 16 * j16 : a.src + moff + 16 * k;
     const uint32_t msh = (uint32_t)(reinterpret_cast<uintptr_t>(mant) & 3u) * 8u;
     const uint32_t *mq = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(mant) & ~uintptr_t(3));
     uint32_t m[5] = {0, 0, 0, 0, 0};
     const uint32_t my_tiles = (n + TS - 1) / TS;
-    if (SINK == SINK_BF16 && my_tiles) {
+    if ((SINK == SINK_BF16 && my_tiles) || (SINK == SINK_DELTA && n > 8 * j16)) {
 #pragma unroll
         for (int i = 0; i < 5; i++) m[i] = __ldg(mq + i);
     }
@@ -505,18 +533,18 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
                 put(s4, e);
                 e = stream_step4<CFN, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4 + 1, e);
-                if (ROWMUL) ra[s4 >> 1] = crc_feed4q(cq, ra[s4 >> 1]);
+                if (ROWMUL && (s4 >> 1) < NRA) ra[s4 >> 1] = crc_feed4q(cq, ra[s4 >> 1]);
                 e = stream_step4<CFN, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4 + 2, e);
                 e = stream_step4<CFN, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4 + 3, e);
-                if (ROWMUL) ra[(s4 >> 1) + 1] = crc_feed4q(cq, ra[(s4 >> 1) + 1]);
+                if (ROWMUL && (s4 >> 1) < NRA) ra[(s4 >> 1) + 1] = crc_feed4q(cq, ra[(s4 >> 1) + 1]);
                 caddr += 2 * __popc(hist);
             }
         } else {
             if (ROWMUL) {
 #pragma unroll
-                for (int i = 0; i < 8; i++) ra[i] = crc_feed4q(cq, ra[i]);
+                for (int i = 0; i < NRA; i++) ra[i] = crc_feed4q(cq, ra[i]);
             }
 #pragma unroll 1
             for (uint32_t s = 0; s < TS / NLANES; s++) {
@@ -528,6 +556,67 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
         cursor += caddr - caddr0;
         __syncwarp();
         if (!rem || DIRECT) continue;
+        if (SINK == SINK_DELTA) {
+            // ---- both planes' symbols of this lane's eight elements, merge, XOR the base, write, checksum
+            const uint32_t pair_sa = stage_0 + (gi & ~1u) * STG + 8u * j16;
+            const uint2 ea = lds_u64(pair_sa), eb = lds_u64(pair_sa + STG);
+            uint32_t w[4];
+            bf16_merge4(ea.x, eb.x, w[0], w[1]);
+            bf16_merge4(ea.y, eb.y, w[2], w[3]);
+#pragma unroll
+            for (int h = 0; h < 4; h++) w[h] ^= __funnelshift_r(m[h], m[h + 1], msh);
+            if (n > (t + 1) * TS + 8u * j16) {                     // next tile's base bytes, if this lane has any
+#pragma unroll
+                for (int i = 0; i < 5; i++) m[i] = __ldg(mq + (size_t)(t + 1) * (2 * TS / 4) + i);
+            }
+            uint8_t *d = out + (size_t)done * 2 + 16u * j16;
+            const uint32_t ve = rem > 8u * j16 ? min(rem - 8u * j16, 8u) : 0u;   // valid elements of this lane
+            if (ve == 8) {
+                if (al == 0) *reinterpret_cast<uint4 *>(d) = make_uint4(w[0], w[1], w[2], w[3]);
+                else if ((al & 3) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) reinterpret_cast<uint32_t *>(d)[i] = w[i];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) d[i] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+                }
+            } else {
+                const uint32_t vb = 2 * ve;
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    if ((uint32_t)i < vb) d[i] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t keep = vb > 4u * i ? min(vb - 4u * i, 4u) : 0u;
+                    w[i] = keep >= 4 ? w[i] : (keep ? w[i] & ((1u << (8 * keep)) - 1u) : 0u);
+                }
+            }
+            if (CRC) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) ra[i] ^= w[i];
+                if ((t & 255u) == 255u || t + 1 == my_tiles) {
+                    // close the 64 KiB piece: every running value to the row's end, XOR over the chunk's 16 lanes
+                    uint32_t v = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        v ^= crc_mulmod(a.tabs->word_mul16[j16][i], ra[i]);
+                        ra[i] = 0;
+                    }
+                    const uint32_t pair_mask = 0xffffu << (16u * (g >> 1));
+                    v ^= __shfl_xor_sync(pair_mask, v, 1);
+                    v ^= __shfl_xor_sync(pair_mask, v, 2);
+                    v ^= __shfl_xor_sync(pair_mask, v, 4);
+                    v ^= __shfl_xor_sync(pair_mask, v, 8);
+                    if (j16 == 0) {
+                        const uint32_t p = t >> 8, rows = (t & 255u) + 1;
+                        const uint32_t plen = min(PIECE_BYTES, 2 * n - p * PIECE_BYTES);
+                        if (rows * F_ROW != plen) v = crc_unshift(a.tabs->x2, v, rows * F_ROW - plen);
+                        a.piece_crc[piece0 + p] = v;
+                    }
+                }
+            }
+            continue;
+        }
         constexpr uint32_t PER = TS / NLANES;                  // this lane's symbols of the tile: 16 or 32
         uint4 evs[PER / 16];
 #pragma unroll
@@ -704,19 +793,25 @@ __global__ void k_classify(StreamArgs a, uint32_t small_live, uint32_t *order, u
 {
     const uint32_t job = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
     if (job >= a.njobs) return;
-    uint64_t soff;
-    uint32_t slen;
-    if (a.jobs) { soff = a.jobs[job].src_off; slen = a.jobs[job].src_len; }
-    else if (a.sjobs) { soff = a.sjobs[job].src_off; slen = a.sjobs[job].src_len; }
-    else { soff = a.offs[2 * job]; slen = (uint32_t)a.offs[2 * job + 1]; }
+    // (delta jobs: njobs counts chunks here; a chunk is as large as the larger of its two planes' alphabets)
     uint32_t live = 0;
-    if (slen >= HDR_BYTES + STATE_BYTES) {
-        const uint8_t *h = a.src + soff + 4 + 16 * lane;
+    for (uint32_t plane = 0; plane < (a.djobs ? 2u : 1u); plane++) {
+        uint64_t soff;
+        uint32_t slen;
+        if (a.djobs) { soff = plane ? a.djobs[job].src_b : a.djobs[job].src_a; slen = plane ? a.djobs[job].len_b : a.djobs[job].len_a; }
+        else if (a.jobs) { soff = a.jobs[job].src_off; slen = a.jobs[job].src_len; }
+        else if (a.sjobs) { soff = a.sjobs[job].src_off; slen = a.sjobs[job].src_len; }
+        else { soff = a.offs[2 * job]; slen = (uint32_t)a.offs[2 * job + 1]; }
+        uint32_t mine = 0;
+        if (slen >= HDR_BYTES + STATE_BYTES) {
+            const uint8_t *h = a.src + soff + 4 + 16 * lane;
 #pragma unroll
-        for (int i = 0; i < 8; i++) live += (h[2 * i] | h[2 * i + 1]) != 0;
-        live = __reduce_add_sync(0xffffffffu, live);
-    } else {
-        live = 257;                                    // too short: the large instance reports it
+            for (int i = 0; i < 8; i++) mine += (h[2 * i] | h[2 * i + 1]) != 0;
+            mine = __reduce_add_sync(0xffffffffu, mine);
+        } else {
+            mine = 257;                                // too short: the large instance reports it
+        }
+        live = max(live, mine);
     }
     if (lane == 0) {
         const bool small = live <= small_live;

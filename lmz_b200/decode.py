@@ -66,7 +66,8 @@ class ArchiveDecoder:
         want = (planner.STREAM_JOB.itemsize, planner.CHUNK_JOB.itemsize,
                 planner.COND_JOB.itemsize, planner.COND_STATE_BYTES, planner.FUSED_JOB.itemsize)
         if tuple(sizes) != want or lib.lmz_gpu_piece_bytes() != planner.PIECE or \
-                lib.lmz_gpu_shared_group() != planner.T_GROUP:
+                lib.lmz_gpu_shared_group() != planner.T_GROUP or \
+                lib.lmz_gpu_delta_job_bytes() != planner.DELTA_JOB.itemsize:
             raise RuntimeError("the CUDA library and the planner disagree on job layouts")
         self.archive = ar if isinstance(ar, fmt.Archive) else fmt.Archive(ar)
         self.plan = p = plan if plan is not None else planner.build_plan(self.archive, fuse=fuse)
@@ -95,6 +96,7 @@ class ArchiveDecoder:
             self.d_stream_jobs = _dev(p.stream_jobs, d)
             self.d_seg_jobs = _dev(p.seg_jobs, d)
             self.d_fused_jobs = _dev(p.fused_jobs, d)
+            self.d_delta_jobs = _dev(p.delta_jobs, d)
             self.d_chunks = _dev(p.chunks, d)
             self.d_piece_chunk = _dev(p.piece_chunk, d)
             self.d_cond_jobs = _dev(p.cond_jobs, d)
@@ -111,6 +113,8 @@ class ArchiveDecoder:
             self.d_stream_status = torch.zeros(max(1, p.stream_jobs.size), **u32)
             self.d_seg_status = torch.zeros(max(1, p.seg_jobs.size), **u32)
             self.d_fused_status = torch.zeros(max(1, p.fused_jobs.size), **u32)
+            self.d_delta_status = torch.zeros(max(1, 2 * p.delta_jobs.size), **u32)
+            self.d_delta_order = torch.zeros(p.delta_jobs.size + 2, **u32)
             self.d_chunk_status = torch.zeros(max(1, p.chunks.size), **u32)
             self.d_chunk_crc = torch.zeros(max(1, p.chunks.size), **u32)
             self.d_any_bad = torch.zeros(1, **u32)
@@ -124,6 +128,9 @@ class ArchiveDecoder:
         c.d_stream_status, c.d_seg_status = self.d_stream_status.data_ptr(), self.d_seg_status.data_ptr()
         c.d_fused_jobs, c.d_fused_status = self.d_fused_jobs.data_ptr(), self.d_fused_status.data_ptr()
         c.n_fused, c.n_fused_t = p.n_fused, p.n_fused_t
+        c.d_delta_jobs, c.d_delta_status = self.d_delta_jobs.data_ptr(), self.d_delta_status.data_ptr()
+        c.n_delta = p.delta_jobs.size
+        c.d_delta_order = self.d_delta_order.data_ptr()
         c.d_tables = self.d_tables.data_ptr() if self.d_tables is not None else None
         c.n_fused_small = p.n_fused_small
         c.n_fused_f32, c.n_fused_f32_small = p.n_fused_f32, p.n_fused_f32_small
@@ -153,7 +160,7 @@ class ArchiveDecoder:
         else:
             fused_launches = (1 if p.n_fused_small else 0) + (1 if nbf > p.n_fused_small else 0) + \
                 (1 if p.n_fused_f32_small else 0) + (1 if p.n_fused_f32 > p.n_fused_f32_small else 0)
-        fused_launches += 1 if p.n_fused_t else 0
+        fused_launches += (1 if p.n_fused_t else 0) + (3 if p.delta_jobs.size else 0)
         self.launches_per_run = (1 if p.stream_jobs.size else 0) + \
             ((4 + (1 if p.seg_jobs.size else 0)) if ncond else 0) + fused_launches + \
             int(sum(p.piece_split[i + 1] > p.piece_split[i] for i in (0, 1, 3, 4))) + 1
@@ -212,6 +219,10 @@ class ArchiveDecoder:
         if hard.size:
             raise CorruptArchive(f"the exponent plane of a bf16 chunk: "
                                  f"{_ST_NAMES.get(int(fs[hard[0]]), '?')}")
+        ds = self.d_delta_status.cpu().numpy()[:2 * p.delta_jobs.size]
+        hard = np.nonzero((ds != 0) & (ds != 0x100))[0]
+        if hard.size:
+            raise CorruptArchive(f"a plane of a delta chunk's difference: {_ST_NAMES.get(int(ds[hard[0]]), '?')}")
         raise CorruptArchive("a bucket segment of a conditioned chunk failed to decode")
 
     def chunk_crcs(self) -> np.ndarray:

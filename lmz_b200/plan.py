@@ -51,6 +51,9 @@ BF16C_HDR = np.dtype([("k", "u1"), ("exp_m", "u1"), ("sm_m", "u1", 8), ("exp_len
 assert (STREAM_JOB.itemsize, CHUNK_JOB.itemsize, COND_JOB.itemsize, BF16C_HDR.itemsize) == \
     (32, 104, 144, 46)
 assert FUSED_JOB.itemsize == 40
+DELTA_JOB = np.dtype([("src_a", "<u8"), ("src_b", "<u8"), ("dst_off", "<u8"), ("base_off", "<u8"),
+                      ("len_a", "<u4"), ("len_b", "<u4"), ("n", "<u4"), ("piece0", "<u4")])
+assert DELTA_JOB.itemsize == 48
 
 
 @dataclass
@@ -74,6 +77,7 @@ class Plan:
     coded_bytes: int = 0           # sum of clen: algorithmic bytes read
     device_classify: bool = False  # the fused jobs are not sorted by alphabet: the library counts on the device
     n_fused_t: int = 0             # trailing fused jobs of shared-table chunks (padded per table to T_GROUP)
+    delta_jobs: np.ndarray = field(default=None)   # delta chunks decoded, undone and checksummed by one kernel
     tables: np.ndarray = field(default=None)   # the shared tables, TABLE_STRIDE bytes apart
 
     @property
@@ -122,9 +126,11 @@ def _align16(x):
 def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
                out_range=None, classify: str = "device") -> Plan:
     """`fuse` routes BF16 chunks whose exponent plane is rANS and whose sign/mantissa
-    plane is stored to the fused decode+merge+checksum kernel (no scratch plane), and
+    plane is stored to the fused decode+merge+checksum kernel (no scratch plane),
     4-byte-element chunks whose top byte plane alone is coded likewise when there are
-    at least FUSE_F32_MIN of them (`fuse="all"`: however few).
+    at least FUSE_F32_MIN of them (`fuse="all"`: however few), and delta chunks whose
+    difference is a BF16 chunk with both planes coded to the kernel instance that decodes
+    both planes, undoes the delta against the base in the output space and checksums.
     `select` (record indices) plans only those chunks -- one rank's share of a
     partitioned decode, sources of its refs and deltas included by the caller.
     `payload_range` = (lo, hi) uploads only those archive bytes (every selected chunk's
@@ -204,6 +210,8 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
     f_src = np.zeros(N, dtype=np.int64)
     f_len = np.zeros(N, dtype=np.int64)
     f_mant = np.zeros(N, dtype=np.int64)
+    fused_d = np.zeros(N, dtype=bool)               # delta chunks for the two-plane instance
+    f_len_b = np.zeros(N, dtype=np.int64)
 
     # stored, and refs (a copy out of the output space)
     i = np.nonzero((ecodec == fmt.CODEC_STORED) & ~is_ref)[0]
@@ -273,6 +281,13 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
                 fused[fi] = True
                 f_src[fi], f_len[fi], f_mant[fi] = starts[fz, 0], lens[fz, 0], starts[fz, 1]
                 stored = stored | fz[:, None]          # no scratch stream for these
+                # a delta whose difference has both planes coded (mostly zero bytes, so both pay)
+                dz = is_delta[i] & ~stored[:, 0] & ~stored[:, 1] & (nelem > 0)
+                di2 = i[dz]
+                fused_d[di2] = True
+                f_src[di2], f_len[di2] = starts[dz, 0], lens[dz, 0]
+                f_mant[di2], f_len_b[di2] = starts[dz, 1], lens[dz, 1]
+                stored = stored | dz[:, None]
             if fuse and cid == fmt.CODEC_SPLIT and npl == 4:
                 # top byte plane coded, the three lower planes stored (and then back to back)
                 fz = ~pass2[i] & ~stored[:, 3] & stored[:, :3].all(axis=1) & (nelem > 0)
@@ -401,6 +416,7 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
 
     # ---- chunk jobs in launch order ----------------------------------------------
     group = np.where(pass2, 3, 0) + (kind != K_COND) + (fused & ~pass2)
+    group[fused_d] = 2                              # written by their own kernel, like the fused chunks
     corder = np.argsort(group, kind="stable")
     chunks = np.zeros(N, dtype=CHUNK_JOB)
     chunks["dst_off"] = dst[corder]
@@ -425,7 +441,8 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
     cond_pieces = np.nonzero(chunks["kind"][piece_chunk] == K_COND)[0].astype(np.uint32)
     fall = np.nonzero(g == 2)[0]
     tpos = fall[is_t[corder[fall]]]                 # shared-table chunks: jobs of their own, below
-    fpos = fall[~is_t[corder[fall]]]                # fused chunks, in launch order ...
+    dpos = fall[fused_d[corder[fall]]]              # two-plane delta chunks: jobs of their own, too
+    fpos = fall[~is_t[corder[fall]] & ~fused_d[corder[fall]]]      # fused chunks, in launch order ...
     whole = f_len[corder[fpos]] >= 548              # table + states present (else the kernel rejects it)
     small = np.zeros(fpos.size, dtype=bool)
     if classify == "host":
@@ -457,6 +474,13 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
         tj["n"][slot], tj["piece0"][slot] = rlen[trec] // 2, piece0[tpos]
         fused_jobs = np.concatenate((fused_jobs, tj))
 
+    delta_jobs = np.zeros(dpos.size, dtype=DELTA_JOB)
+    drec = corder[dpos]
+    delta_jobs["src_a"], delta_jobs["len_a"] = f_src[drec], f_len[drec]
+    delta_jobs["src_b"], delta_jobs["len_b"] = f_mant[drec], f_len_b[drec]
+    delta_jobs["dst_off"], delta_jobs["base_off"] = dst[drec], base[drec]
+    delta_jobs["n"], delta_jobs["piece0"] = rlen[drec] // 2, piece0[dpos]
+
     payload = blob[:hi - lo]
     extra = np.concatenate(extras) if extras else np.zeros(0, dtype=np.uint8)
     return Plan(payload=payload, extras=extra, total=out_hi - out_lo, scratch_bytes=scratch_pos + 64,
@@ -466,7 +490,8 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
                 n_fused_small=int((~wide4 & small).sum()), n_fused_f32=int(wide4.sum()),
                 n_fused_f32_small=int((wide4 & small).sum()),
                 coded_bytes=int(clen.sum()), base_bytes=int(rlen[is_delta].sum()),
-                device_classify=classify != "host", n_fused_t=n_fused_t, tables=tables)
+                device_classify=classify != "host", n_fused_t=n_fused_t, tables=tables,
+                delta_jobs=delta_jobs)
 
 
 def _inflate(raw: bytes) -> bytes:

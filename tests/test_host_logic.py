@@ -165,6 +165,32 @@ def test_planner_lists_fp32_chunks_after_bf16_in_the_fused_jobs(shard):
     assert plan.build_plan(ar, fuse=False).fused_jobs.size == 0
 
 
+def test_planner_gives_two_plane_deltas_jobs_of_their_own(shard):
+    """A delta chunk whose difference is a BF16 chunk with both planes coded gets a job for
+    the kernel that decodes both planes and undoes the delta in one pass: no scratch streams,
+    its pieces in the group the finish kernels skip, base and planes as the chunk says."""
+    from lmz_b200 import archive, plan
+    nxt = shard.copy()
+    s, e = list(oa.parse_safetensors(shard)[1].values())[0]["offsets"]
+    nxt[s:e] = synth.perturbed_bf16(shard[s:e], 77)
+    blob = oa.write_archive([("a.safetensors", shard), ("b.safetensors", nxt)], mapped=True)
+    ar = archive.Archive(blob)
+    p = plan.build_plan(ar)
+    ndelta = int((ar.records["codec"] == 8).sum())
+    assert ndelta and 0 < p.delta_jobs.size <= ndelta
+    chunk_at = {int(c["piece0"]): c for c in p.chunks}
+    for j in p.delta_jobs:
+        c = chunk_at[int(j["piece0"])]
+        rec = ar.records[int(c["record"])]
+        assert int(rec["codec"]) == 8 and int(c["base_off"]) == int(j["base_off"]) and int(j["n"]) * 2 == int(rec["rlen"])
+        assert int(c["scratch_mask"]) == 0
+        assert p.piece_split[2] <= int(j["piece0"]) < p.piece_split[3]
+        lo, hi = int(rec["off"]), int(rec["off"]) + int(rec["clen"])
+        assert lo < int(j["src_a"]) < int(j["src_b"]) < hi and int(j["src_a"]) + int(j["len_a"]) == int(j["src_b"])
+        assert int(j["src_b"]) + int(j["len_b"]) == hi
+    assert plan.build_plan(ar, fuse=False).delta_jobs.size == 0
+
+
 def test_reader_rejects_damage(shard):
     from lmz_b200 import archive
     blob = oa.write_archive([("m.safetensors", shard)], mapped=True)
