@@ -363,7 +363,8 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
                 da.any_bad = (uint32_t *)p->d_any_bad;
                 da.piece_crc = (uint32_t *)p->d_piece_crc;
                 da.tabs = (const CrcTables *)p->d_crc_tables;
-                // alphabets counted on the device: chunks whose two planes both have small ones to the denser instance
+                // alphabets counted on the device: chunks whose exponent differences have a small one (the rule) go to
+                // the instance with mixed table sizes, 72 streams per SM instead of 64
                 uint32_t *order = (uint32_t *)p->d_delta_order;
                 if (!order) return fail_msg(LMZ_GPU_EUNSUPPORTED, "delta jobs without d_delta_order");
                 uint32_t *counts = order + p->n_delta;
@@ -379,7 +380,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
                     da.count = counts + big;
                     da.order_from_back = big;
                     rc = big ? (crc ? launch_stream<SINK_DELTA, true, 256>(da, cs) : launch_stream<SINK_DELTA, false, 256>(da, cs))
-                             : (crc ? launch_stream<SINK_DELTA, true, F_SMALL_CFN>(da, cs) : launch_stream<SINK_DELTA, false, F_SMALL_CFN>(da, cs));
+                             : (crc ? launch_stream<SINK_DELTA, true, F_HYBRID_CFN>(da, cs) : launch_stream<SINK_DELTA, false, F_HYBRID_CFN>(da, cs));
                 }
                 if (rc) return rc;
             }

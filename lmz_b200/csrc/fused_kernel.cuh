@@ -62,7 +62,8 @@ __host__ __device__ constexpr uint32_t stream_stage(int cfn, int warps) { return
 constexpr uint32_t F_LOGS = 3;                     // eight copies of the CRC slice tables (32 KiB), one per lane of a group: see CrcQuarters
 constexpr uint32_t F_CRC_BYTES = (4096u << F_LOGS) + 4096u;   // + the row-advance tables, once
 constexpr uint32_t F_ROW = 256, F_UNIT = 32;       // bytes of BF16 one group / one lane emits per tile
-constexpr int F_SMALL_CFN = 128;         // level-2 slots of the dense instance
+constexpr int F_SMALL_CFN = 128;                   // level-2 slots of the dense instance
+constexpr int F_HYBRID_CFN = 192;                  // delta sink: 128-entry tables for first planes, 256-entry for second planes
 constexpr uint32_t F_SMALL_LIVE = F_SMALL_CFN - 24; // largest alphabet it takes (the warp's streams sit 0, 8, 16, 24 entries in)
 
 struct FusedJob {
@@ -292,7 +293,14 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
     constexpr bool WIDE = CFN <= 0, SHARED = CFN < 0;
     constexpr bool DIRECT = stream_direct(CFN, WARPS);
     static_assert(!DIRECT || SINK == SINK_BYTES, "the 13-stream instance writes bytes only");
+    // SINK_DELTA with CFN = 192: the two planes of a chunk have level-2 tables of different sizes, 128
+    // entries for the exponent differences (a handful of symbols) and 256 for the sign/mantissa
+    // differences, 768 bytes a stream on average; the decode steps are those of the 256-entry instance.
+    constexpr bool HYB = SINK == SINK_DELTA && CFN == F_HYBRID_CFN;
+    constexpr int CFN_STEP = HYB ? 256 : CFN;
     constexpr uint32_t G = DIRECT ? F_DIRECT_GROUPS : stream_groups(CFN, WARPS), CFB = WIDE ? 16u : 4u * CFN;
+    constexpr uint32_t CF_ALIGN = HYB ? 1024u : CFB;
+    static_assert(CFN != F_HYBRID_CFN || SINK == SINK_DELTA, "mixed table sizes are the delta sink's");
     constexpr uint32_t LEAD = (SHARED ? 0u : HDR_BYTES) + STATE_BYTES;
     constexpr uint32_t MAX_LIVE = CFN > 0 && CFN < 256 ? (uint32_t)CFN - 24u : 256u;
     constexpr uint32_t TS = stream_tile(CFN, WARPS), NSL = stream_nslot(CFN, WARPS), RB = stream_ring_bytes(CFN, WARPS);
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
     const uint32_t bars_0 = (s0 + 15u) & ~15u;
     const uint32_t stage_0 = bars_0 + G * 8 * NSL;
     const uint32_t ring_0 = stage_0 + G * STG;
-    const uint32_t cf_0 = (ring_0 + G * RB + CFB - 1) & ~(CFB - 1);
+    const uint32_t cf_0 = (ring_0 + G * RB + CF_ALIGN - 1) & ~(CF_ALIGN - 1);
     // compact: level 1 at the top; wide: 16 KiB tables from the first 16 KiB boundary up
     const uint32_t l1_0 = DIRECT ? cf_0 : WIDE ? (cf_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1)
                                : ((CRC ? tab0 : top) & ~4095u) - (WARPS - (TOPL1 ? 1 : 0)) * 4096u;
@@ -324,7 +332,10 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
     const bool fits = WIDE ? l1_0 + (SHARED ? 1u : G) * F_WIDE_BYTES <= (CRC ? tab0 : top) : cf_0 + G * CFB <= l1_0 && (!TOPL1 || (adv0 & 4095u) == 0);
     auto gen = [&](uint32_t sa) { return ssm + (sa - s0); };
     const uint32_t l1_sa = SHARED ? l1_0 : WIDE ? l1_0 + gi * F_WIDE_BYTES : l1_of(warp) + g * 4;
-    const uint32_t cf_sa = cf_0 + gi * CFB;
+    // (mixed sizes: the 1 KiB tables of the second planes first, then the half-KiB tables of the first planes)
+    auto cf_of = [&](uint32_t grp) { return HYB ? ((grp & 1u) ? cf_0 + (grp >> 1) * 1024u : cf_0 + (G / 2) * 1024u + (grp >> 1) * 512u)
+                                               : cf_0 + grp * CFB; };
+    const uint32_t cf_sa = cf_of(gi);
     const uint32_t stage_sa = stage_0 + gi * STG;
     // byte (i + g) & 3 of a state word goes through slice table 3 - ((i + g) & 3)
     CrcQuarters cq;
@@ -450,19 +461,20 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
         auto rd = [&](uint32_t o) { return lds_u8(rsa + o); };     // header sits in the first 548+15 bytes
         Tables tb{};
         auto freq_of = [&](uint32_t s) { return rd(sk + 4 + 2 * s) | (rd(sk + 5 + 2 * s) << 8); };
-        uint32_t nlive = 0;
+        uint32_t nlive = 0, max_live = MAX_LIVE;
         bool ok;
         if (WIDE) {
             tb.wide = reinterpret_cast<uint32_t *>(gen(l1_0 + (warp * 4 + gg) * F_WIDE_BYTES));
             ok = build_table<T_WIDE1>(freq_of, tb, lane);
         } else {
             tb.l1 = reinterpret_cast<uint32_t *>(gen(l1_of(warp) + gg * 4));
-            tb.cf = reinterpret_cast<uint32_t *>(gen(cf_0 + (warp * 4 + gg) * CFB));
-            ok = build_table<T_COMPACT, 4>(freq_of, tb, lane, CFN < 256 ? 8u * gg : 0u, &nlive, MAX_LIVE);
+            tb.cf = reinterpret_cast<uint32_t *>(gen(cf_of(warp * 4 + gg)));
+            max_live = HYB ? ((gg & 1u) ? 256u : F_SMALL_LIVE) : MAX_LIVE;
+            ok = build_table<T_COMPACT, 4>(freq_of, tb, lane, (HYB ? !(gg & 1u) : CFN < 256) ? 8u * gg : 0u, &nlive, max_live);
         }
         ok = ok && rd(sk) == 'R' && rd(sk + 1) == '1';
         // an alphabet too large for this instance is the caller's mistake, not the stream's
-        if (!ok && gi == warp * 4 + gg) { st = nlive > MAX_LIVE ? ST_BAD_SHAPE : ST_BAD_HEADER; n = 0; }
+        if (!ok && gi == warp * 4 + gg) { st = nlive > max_live ? ST_BAD_SHAPE : ST_BAD_HEADER; n = 0; }
     }
     __syncwarp();
 
@@ -529,14 +541,14 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
 #pragma unroll
             for (uint32_t s4 = 0; s4 < TS / NLANES; s4 += 4) {
                 uint32_t hist = 0, e;
-                e = stream_step4<CFN, true, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN_STEP, true, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4, e);
-                e = stream_step4<CFN, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN_STEP, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4 + 1, e);
                 if (ROWMUL && (s4 >> 1) < NRA) ra[s4 >> 1] = crc_feed4q(cq, ra[s4 >> 1]);
-                e = stream_step4<CFN, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN_STEP, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4 + 2, e);
-                e = stream_step4<CFN, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN_STEP, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4 + 3, e);
                 if (ROWMUL && (s4 >> 1) < NRA) ra[(s4 >> 1) + 1] = crc_feed4q(cq, ra[(s4 >> 1) + 1]);
                 caddr += 2 * __popc(hist);
@@ -549,7 +561,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
 #pragma unroll 1
             for (uint32_t s = 0; s < TS / NLANES; s++) {
                 bool active = s * NLANES + k < rem;
-                uint32_t e = stream_step<CFN, !DIRECT>(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
+                uint32_t e = stream_step<CFN_STEP, !DIRECT>(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
                 if (active) put(s, e);
             }
         }
@@ -793,9 +805,10 @@ __global__ void k_classify(StreamArgs a, uint32_t small_live, uint32_t *order, u
 {
     const uint32_t job = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
     if (job >= a.njobs) return;
-    // (delta jobs: njobs counts chunks here; a chunk is as large as the larger of its two planes' alphabets)
+    // (delta jobs: njobs counts chunks here, and the first plane's alphabet decides: the instance for
+    // small ones gives the second plane a full-size table)
     uint32_t live = 0;
-    for (uint32_t plane = 0; plane < (a.djobs ? 2u : 1u); plane++) {
+    for (uint32_t plane = 0; plane < 1u; plane++) {
         uint64_t soff;
         uint32_t slen;
         if (a.djobs) { soff = plane ? a.djobs[job].src_b : a.djobs[job].src_a; slen = plane ? a.djobs[job].len_b : a.djobs[job].len_a; }

@@ -166,6 +166,30 @@ def test_conditioned_chunk_with_a_stored_exponent_plane(name):
     _roundtrip(blob, src)
 
 
+def test_delta_whose_exponent_differences_have_a_wide_alphabet():
+    """Deltas go to one kernel that decodes both planes of the difference: chunks whose
+    exponent differences take a handful of values to its instance with mixed table sizes,
+    the others -- here ~150 distinct differences -- to the one with full-size tables for both
+    planes.  The sign/mantissa difference is all zeros: a one-symbol stream."""
+    from lmz_b200 import archive, plan
+    rng = np.random.default_rng(21)
+    n = 700_000
+    base = rng.integers(0, 65536, n).astype("<u2")
+    d = np.minimum(rng.geometric(0.04, n) - 1, 180).astype(np.uint16)
+    d[rng.random(n) < 0.5] = 0
+    nxt = (base ^ (d << 7)).astype("<u2")
+    small = synth.normal_bf16(200_000, 4)
+    near = synth.perturbed_bf16(small, 9)
+    a = synth.safetensors_bytes([("w", "BF16", (n,), base.view(np.uint8)), ("v", "BF16", (200_000,), small)])
+    b = synth.safetensors_bytes([("w", "BF16", (n,), nxt.view(np.uint8)), ("v", "BF16", (200_000,), near)])
+    for kw in (dict(mapped=True), dict(chunk_size=(1 << 17) + 6)):
+        blob = oa.write_archive([("a.safetensors", a), ("b.safetensors", b)], **kw)
+        p = plan.build_plan(archive.Archive(blob))
+        assert p.delta_jobs.size >= 2 and p.stream_jobs.size == 0
+        _roundtrip(blob, np.concatenate([a, b]))
+        _roundtrip(blob, np.concatenate([a, b]), checksum=False)
+
+
 def test_tiny_and_odd_members():
     rng = np.random.default_rng(0)
     members = [("a.bin", rng.integers(0, 4, 100001, dtype=np.uint8)),      # one rANS-coded byte stream
