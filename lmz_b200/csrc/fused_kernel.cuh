@@ -477,6 +477,13 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
         if (!ok && gi == warp * 4 + gg) { st = nlive > max_live ? ST_BAD_SHAPE : ST_BAD_HEADER; n = 0; }
     }
     __syncwarp();
+    if (SINK == SINK_DELTA) {
+        // The two groups of a chunk walk its tiles together (they share the merge, and the
+        // checksum is folded over both with shuffles): when one plane has been refused, the
+        // other is not decoded either.  The refused plane's status reports the chunk.
+        const uint32_t partner_n = __shfl_xor_sync(0xffffffffu, n, 8);
+        if (partner_n == 0) n = 0;
+    }
 
     const uint32_t xo = ring.sa + skew + (SHARED ? 0u : HDR_BYTES) + 4 * k;
     uint32_t x = lds_u8(xo) | (lds_u8(xo + 1) << 8) | (lds_u8(xo + 2) << 16) | (lds_u8(xo + 3) << 24);

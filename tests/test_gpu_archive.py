@@ -228,6 +228,31 @@ def test_corruption_is_reported(shard):
         decode.ArchiveDecoder(bytes(blob[:-1]))
 
 
+def test_corrupt_delta_chunks_are_reported():
+    """Damage inside either plane's stream of a delta chunk, in a stream's magic and in a
+    frequency table: the one-pass delta kernel (or the checksum behind it) reports each."""
+    from lmz_b200 import archive, decode, plan
+    from lmz_b200.archive import CorruptArchive
+    base = synth.safetensors_bytes([("w", "BF16", (300_000,), synth.normal_bf16(300_000, 2))])
+    nxt = base.copy()
+    s, e = list(oa.parse_safetensors(base)[1].values())[0]["offsets"]
+    nxt[s:e] = synth.perturbed_bf16(base[s:e], 5)
+    blob = oa.write_archive([("a.safetensors", base), ("b.safetensors", nxt)], mapped=True)
+    p = plan.build_plan(archive.Archive(blob))
+    assert p.delta_jobs.size
+    j = p.delta_jobs[p.delta_jobs.size // 2]
+    for where in (int(j["src_a"]) + 548 + 40, int(j["src_b"]) + 548 + 1000, int(j["src_b"]), int(j["src_a"]) + 4 + 2 * 7):
+        hit = bytearray(blob)
+        hit[where] ^= 0x41
+        dec = decode.ArchiveDecoder(bytes(hit))
+        dec.run()
+        with pytest.raises(CorruptArchive):
+            dec.check()
+    dec = decode.ArchiveDecoder(blob)
+    dec.run()
+    dec.check()
+
+
 def test_corrupt_conditioned_chunks_are_reported(shard):
     """Default chunking: damage to the exponent stream of a conditioned chunk changes its
     histogram, so its bucket sizes no longer match the stored segments - the chunk is
