@@ -188,16 +188,60 @@ def archive_pin(a, rank: int = 0) -> str:
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+    """SM clock and throttle reasons of one GPU while a region runs: read through NVML
+    (read-only queries) every 10 ms by a thread of this process, so that even a timed region
+    of a few tens of milliseconds gets samples; nvidia-smi in a loop where NVML cannot be
+    loaded."""
 
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, index: int):
         self.rows, self.proc, self.index = [], None, index
+        self.nvml = self.handle = self.t = None
+        self.stop = threading.Event()
+
+    def _open_nvml(self):
+        import pynvml
+        pynvml.nvmlInit()
+        handle = None
+        try:                                   # the CUDA device's own NVML handle, whatever the visible-device order
+            import torch
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        except Exception:
+            handle = None
+        if handle is None:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        self.nvml, self.handle = pynvml, handle
+        self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+
+    def _sample(self):
+        n, h = self.nvml, self.handle
+        mhz = float(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM))
+        bits = int(n.nvmlDeviceGetCurrentClocksEventReasons(h))
+        flags = [bool(bits & m) for m in (n.nvmlClocksEventReasonHwSlowdown, n.nvmlClocksEventReasonHwThermalSlowdown,
+                                          n.nvmlClocksEventReasonSwThermalSlowdown, n.nvmlClocksEventReasonSwPowerCap)]
+        self.rows.append([mhz, self.max_mhz, 0.0] + ["Active" if f else "Not Active" for f in flags])
+
+    def _poll(self):
+        while not self.stop.is_set():
+            try:
+                self._sample()
+            except Exception:
+                return
+            self.stop.wait(0.01)
 
     def __enter__(self):
+        try:
+            self._open_nvml()
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return self
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
@@ -214,6 +258,10 @@ class ClockSampler:
             self.rows.append([x.strip() for x in line.split(",")])
 
     def __exit__(self, *exc):
+        if self.nvml is not None:
+            self.stop.set()
+            self.t.join(timeout=2)
+            return
         if self.proc is not None:
             time.sleep(0.15)
             self.proc.terminate()
@@ -221,15 +269,14 @@ class ClockSampler:
 
     def summary(self) -> dict:
         sm, mx, reasons = [], 0, set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for r in self.rows:
             try:
                 sm.append(float(r[0]))
                 mx = max(mx, float(r[1]))
             except (ValueError, IndexError):
                 continue
-            for n, v in zip(names, r[3:7]):
-                if v.lower().startswith("active"):
+            for n, v in zip(self.NAMES, r[3:7]):
+                if str(v).lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None,
                 "reasons": sorted(reasons), "samples": len(sm)}
