@@ -824,9 +824,11 @@ __global__ void k_classify(StreamArgs a, uint32_t small_live, uint32_t *order, u
         else { soff = a.offs[2 * job]; slen = (uint32_t)a.offs[2 * job + 1]; }
         uint32_t mine = 0;
         if (slen >= HDR_BYTES + STATE_BYTES) {
-            const uint8_t *h = a.src + soff + 4 + 16 * lane;
+            // this lane's eight frequencies: 16 bytes at any alignment, as aligned words
+            uint32_t w[4];
+            load_words_nc<4>(a.src + soff + 4 + 16 * lane, w);
 #pragma unroll
-            for (int i = 0; i < 8; i++) mine += (h[2 * i] | h[2 * i + 1]) != 0;
+            for (int i = 0; i < 4; i++) mine += ((w[i] & 0xffffu) != 0) + ((w[i] >> 16) != 0);
             mine = __reduce_add_sync(0xffffffffu, mine);
         } else {
             mine = 257;                                // too short: the large instance reports it
