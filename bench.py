@@ -609,9 +609,10 @@ def main():
     if world == 1:
         cpu_base = cpu_baseline_subprocess(a)
         batch = batch_decode_compare(dec, p)
+        saved = save_side(dec, a) if a.layout == "mapped" and not a.shared_tables else None
         other = default_layout_side(a, barrier) if a.layout == "mapped" and a.model == "llama-3.1-8b" else None
     else:
-        cpu_base = batch = other = None        # timed at N=1 only
+        cpu_base = batch = other = saved = None        # timed at N=1 only
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": round(ms / a.steps, 3),
@@ -638,6 +639,7 @@ def main():
                                       "bytes": coded + plain + p.base_bytes}},
         "phase_ms": {k: round(v, 3) for k, v in phase_ms.items()},
         "cpu_baseline": cpu_base,
+        "save": saved,
         "batch_decode": batch,
         "default_layout": other,
         "partitioned": part,
@@ -813,6 +815,46 @@ def _stress_decode(i):
     from oracle import native
     s = _STRESS["streams"][i % len(_STRESS["streams"])]
     return int(native.best().rans_decode(s, 1 << 20).size)
+
+
+def save_side(dec, a):
+    """The way back: the first BF16 member of the decoded model, as it sits in HBM, written as an
+    lmz archive by `lmz_b200.save.save_archive` (plane split, rANS coding, framing and crc32 on the
+    device; the container and the record list on the host), then decoded again and compared.
+    `device_gbs` counts the device work alone, `value` the whole call including the host's
+    Python loop over the chunk records and the write to a RAM-backed file."""
+    import tempfile
+
+    import torch
+
+    from lmz_b200 import decode, save
+    ar = dec.archive
+    pick = next((m for m in ar.members if m.get("kind") == "safetensors" and
+                 all(t["dtype"] == "BF16" for t in m.get("tensors", {}).values())), None)
+    if pick is None:
+        return None
+    lo, size = int(pick["dst"]), int(pick["size"])
+    member = dec.output[lo:lo + size]
+    tmpdir = "/dev/shm" if os.path.isdir("/dev/shm") else None
+    with tempfile.NamedTemporaryFile(suffix=".lmz", dir=tmpdir) as f:
+        best = None
+        for _ in range(2):
+            st = {}
+            t0 = time.perf_counter()
+            nbytes = save.save_archive(f.name, [(pick["path"], member)], chunk_size=64 << 10, mapped=True, stats=st)
+            dt = time.perf_counter() - t0
+            if best is None or dt < best[0]:
+                best = (dt, st, nbytes)
+        back = decode.ArchiveDecoder(f.name)
+        back.run()
+        back.check()
+        if not torch.equal(back.output, member):
+            raise SystemExit("the archive written on the device does not decode to the member it was written from")
+        del back
+    return {"value": round(size / best[0] / 1e9, 2), "unit": "GB/s", "seconds": round(best[0], 3),
+            "device_gbs": round(size / best[1]["device_s"] / 1e9, 1), "plaintext_bytes": size,
+            "archive_bytes": int(best[2]),
+            "api": "lmz_b200.save.save_archive: one BF16 safetensors member resident in HBM -> .lmz file, 64 KiB chunks"}
 
 
 def batch_decode_compare(dec, p):

@@ -65,16 +65,28 @@ def _header_chunk(raw: bytes, level: int = 1):
 def save_archive(path, members, chunk_size: int = 64 << 10, mapped: bool = True, stats=None):
     """Write `members` = [(member path, CUDA uint8 tensor holding a BF16 safetensors file)] as
     an lmz archive.  Every tensor must be BF16.  Returns the number of bytes written.
-    `stats`, a dict, receives `device_s` (split + encode + frame + checksum on the GPU) and
-    `payload_bytes`."""
-    import time
-
-    import torch
-    lib = gpu.library()
+    `stats`, a dict, receives `device_s` (the kernels: split + encode + frame + checksum, timed
+    with CUDA events) and `payload_bytes`.  The framed payload comes back through a page-locked
+    buffer that the module keeps between calls and goes to the file batch by batch."""
     if chunk_size < (64 << 10) or chunk_size >= COND_MIN_BYTES or chunk_size % 2:
         raise ValueError("chunk_size must be even, at least 64 KiB and below 2 MiB")
-    records, metas, pieces, base = [], [], [], 0
+    with open(path, "wb") as f:
+        return _write_archive(f, members, chunk_size, mapped, stats)
+
+
+def _write_archive(f, members, chunk_size, mapped, stats):
+    import torch
+    lib = gpu.library()
+    recs_parts, metas, base = [], [], 0                      # record arrays, in file order
     device_s = 0.0
+    f.write(bytes(fmt.HEADER.size))                          # the header goes in last: it holds the total size
+
+    def add_records(dst, rlen, crc, codec, esize, flags, clen):
+        part = np.zeros(len(dst), dtype=fmt.RECORD)
+        part["dst"], part["rlen"], part["crc"], part["codec"] = dst, rlen, crc, codec
+        part["esize"], part["flags"], part["clen"] = esize, flags, clen
+        recs_parts.append(part)
+
     for mpath, data in members:
         if not (type(data).__module__.startswith("torch") and data.is_cuda and data.dtype == torch.uint8):
             raise ValueError("a member must be a CUDA uint8 tensor")
@@ -92,53 +104,59 @@ def save_archive(path, members, chunk_size: int = 64 << 10, mapped: bool = True,
         for s in range(0, start, chunk_size):
             raw = head[s:min(s + chunk_size, start)]
             payload, codec, flags = _header_chunk(raw)
-            records.append((base + s, len(raw), zlib.crc32(raw) & 0xFFFFFFFF, codec, 1, flags, len(pieces)))
-            pieces.append(np.frombuffer(payload, dtype=np.uint8))
+            add_records([base + s], [len(raw)], [zlib.crc32(raw) & 0xFFFFFFFF], [codec], [1], [flags], [len(payload)])
+            f.write(payload)
         # the data area: BF16 chunks, framed on the device
-        t0 = time.perf_counter()
         body = flat[start:]
         nbytes = int(body.numel())
         # (in batches: the coder's slots take a little over twice the bytes they code)
         batch = max(1, BATCH_BYTES // chunk_size) * chunk_size
         for b0 in range(0, nbytes, batch):
             part = body[b0:min(b0 + batch, nbytes)]
-            payload, clen, codec, flags, crc = _frame_bf16(lib, part, chunk_size)
-            pos = np.cumsum(clen) - clen
-            rlens = np.minimum(chunk_size, int(part.numel()) - np.arange(clen.size, dtype=np.int64) * chunk_size)
-            for i in range(clen.size):
-                records.append((base + start + b0 + i * chunk_size, int(rlens[i]), int(crc[i]), int(codec[i]), 2,
-                                int(flags[i]), len(pieces)))
-                pieces.append(payload[int(pos[i]):int(pos[i]) + int(clen[i])])
-        torch.cuda.synchronize(body.device)
-        device_s += time.perf_counter() - t0
+            payload, clen, codec, flags, crc, kernel_s = _frame_bf16(lib, part, chunk_size)
+            device_s += kernel_s
+            at = np.arange(clen.size, dtype=np.int64) * chunk_size
+            add_records(base + start + b0 + at, np.minimum(chunk_size, int(part.numel()) - at), crc, codec,
+                        np.full(clen.size, 2), flags, clen)
+            f.write(memoryview(payload))                      # the chunks' payloads back to back, in record order
         metas.append({"path": mpath, "size": size, "dst": base, "kind": "safetensors", "mode": 0o644, "crc": 0,
                       "tensors": {k: dict(v) for k, v in tensors.items()}})
         base += size
-    recs = np.zeros(len(records), dtype=fmt.RECORD)
-    off = fmt.HEADER.size
-    for i, (dst, rlen, crc, codec, esize, flags, pi) in enumerate(records):
-        recs[i] = (off, dst, pieces[pi].size, rlen, crc, codec, esize, flags)
-        off += int(pieces[pi].size)
+    recs = np.concatenate(recs_parts) if recs_parts else np.zeros(0, dtype=fmt.RECORD)
+    clens = recs["clen"].astype(np.int64)
+    recs["off"] = fmt.HEADER.size + np.cumsum(clens) - clens
+    off = fmt.HEADER.size + int(clens.sum())
     manifest = {"version": 1, "tool": "lmz-b200 device writer", "level": 1, "chunk_size": chunk_size,
                 "mapped": bool(mapped), "aligned": False, "entropy": "deflate", "checksum": "crc32",
-                "total_size": base, "members": metas, "chunks": len(records), "table_raw_len": int(recs.nbytes)}
+                "total_size": base, "members": metas, "chunks": int(recs.size), "table_raw_len": int(recs.nbytes)}
     table_c = zlib.compress(recs.tobytes(), 3)
     man_c = zlib.compress(json.dumps(manifest, separators=(",", ":")).encode(), 3)
-    with open(path, "wb") as f:
-        f.write(fmt.HEADER.pack(fmt.MAGIC, 6, fmt.FLAG_PAGE_MAPPED if mapped else 0, base, 0, 0))
-        for p in pieces:
-            f.write(memoryview(np.ascontiguousarray(p)))
-        f.write(table_c)
-        f.write(man_c)
-        f.write(fmt.FOOTER.pack(off, len(table_c), off + len(table_c), len(man_c), fmt.TAIL))
+    f.write(table_c)
+    f.write(man_c)
+    f.write(fmt.FOOTER.pack(off, len(table_c), off + len(table_c), len(man_c), fmt.TAIL))
+    f.seek(0)
+    f.write(fmt.HEADER.pack(fmt.MAGIC, 6, fmt.FLAG_PAGE_MAPPED if mapped else 0, base, 0, 0))
     if stats is not None:
         stats.update(device_s=device_s, payload_bytes=off - fmt.HEADER.size)
     return off + len(table_c) + len(man_c) + fmt.FOOTER.size
 
 
+_host = {}
+
+
+def _host_buffer(nbytes: int):
+    """A page-locked host buffer of at least `nbytes`, kept between calls (allocating one is slow)."""
+    import torch
+    buf = _host.get("buf")
+    if buf is None or buf.numel() < nbytes:
+        _host["buf"] = buf = torch.empty(max(nbytes, 64 << 20), dtype=torch.uint8).pin_memory()
+    return buf
+
+
 def _frame_bf16(lib, body, chunk_size: int):
     """Chunk payloads of one BF16 data area, on the device.  Returns host arrays: the payload
-    bytes of all chunks back to back, and per chunk its length, codec id, flags and crc32."""
+    bytes of all chunks back to back (a view of the module's page-locked buffer: use it before
+    the next call), per chunk its length, codec id, flags and crc32, and the kernels' seconds."""
     import torch
     dev = body.device
     nbytes = int(body.numel())
@@ -146,6 +164,8 @@ def _frame_bf16(lib, body, chunk_size: int):
     nchunks = nfull + (1 if tail else 0)
     with torch.cuda.device(dev):
         cs = torch.cuda.current_stream(dev).cuda_stream
+        e0, e1, e2, e3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        e0.record()
         planes = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         lens = torch.zeros(2 * nchunks, dtype=torch.int32, device=dev)
         rc = lib.lmz_gpu_split_bf16_dev(body.data_ptr(), nbytes, chunk_size, planes.data_ptr(), cs)
@@ -171,8 +191,10 @@ def _frame_bf16(lib, body, chunk_size: int):
             raise RuntimeError(f"chunk framing failed ({rc}): {gpu.last_error()}")
         clen = meta[:, 0].to(torch.int64)
         offs = (torch.cumsum(clen, 0) - clen).contiguous()
-        total = int(clen.sum())
+        e1.record()
+        total = int(clen.sum())                                                  # (the host needs the size: a sync)
         out = torch.empty(total + 16, dtype=torch.uint8, device=dev)
+        e2.record()
         rc = lib.lmz_gpu_frame_bf16_dev(body.data_ptr(), nbytes, chunk_size, lens.data_ptr(), meta.data_ptr(),
                                         planes.data_ptr(), ctypes.c_void_p(sbase), offs.data_ptr(),
                                         out.data_ptr(), cs)                      # pass 2: the bytes
@@ -184,7 +206,11 @@ def _frame_bf16(lib, body, chunk_size: int):
                                           meta.data_ptr(), cs)
         if rc != gpu.OK:
             raise RuntimeError(f"chunk checksum failed ({rc}): {gpu.last_error()}")
+        e3.record()
+        host = _host_buffer(total)[:total]
+        host.copy_(out[:total], non_blocking=True)
         torch.cuda.current_stream(dev).synchronize()
         m = meta.cpu().numpy()
-        return (out[:total].cpu().numpy(), m[:, 0].astype(np.int64), m[:, 1], m[:, 2],
-                m[:, 3].astype(np.int64) & 0xFFFFFFFF)
+        kernel_s = (e0.elapsed_time(e1) + e2.elapsed_time(e3)) / 1e3
+        return (host.numpy(), m[:, 0].astype(np.int64), m[:, 1], m[:, 2],
+                m[:, 3].astype(np.int64) & 0xFFFFFFFF, kernel_s)
