@@ -11,6 +11,11 @@
 //               and whose three lower planes are stored back to back: each tile is
 //               interleaved with 3 x 128 stored bytes (lmz/native/lmzcore.c:289-347),
 //               written once as 512 bytes and folded into the chunk's CRC-32
+//   SINK_DELTA  a delta chunk (lmz/codec.py:1012-1057) whose difference is a CODEC_BF16
+//               chunk with both planes rANS: two neighbouring groups of a warp decode the two
+//               planes in step, the merged difference is XOR-ed with the base bytes already
+//               in the output space, written once and checksummed (CFN = 192: a 128-entry
+//               level 2 for the first plane, a 256-entry one for the second)
 //
 // Differences from k_rans that buy instructions and occupancy:
 //   * shared memory is laid out by kind (all level-1 tables, all level-2 tables,
@@ -28,8 +33,11 @@
 //   * CFN = 0: no levels, a 16 KiB slot -> entry table per stream and 12 streams per
 //     CTA, 256-symbol tiles: for launches so small that only the length of a symbol's
 //     dependent chain counts (one lookup instead of two and a popcount)
+//   * CFN = 0 with a fourth warp: 13 streams per CTA, unaligned tables, a shorter ring and
+//     every symbol stored straight to its output byte (no staging row)
 //   * CFN = -1: the same wide table once per CTA, for batches whose streams share one
-//     516-byte table (lmz_gpu_decode_batch's d_hdr); a stream is then states + words
+//     516-byte table (lmz_gpu_decode_batch's d_hdr) or for the chunks of a shared-table
+//     archive (StreamArgs.tables); a stream is then states + words
 #pragma once
 #include "chunk_kernels.cuh"
 #include "rans.cuh"
