@@ -609,7 +609,12 @@ def main():
     if world == 1:
         cpu_base = cpu_baseline_subprocess(a)
         batch = batch_decode_compare(dec, p)
-        saved = save_side(dec, a) if a.layout == "mapped" and not a.shared_tables else None
+        saved = None
+        if a.layout == "mapped" and not a.shared_tables:
+            try:
+                saved = save_side(dec, a)
+            except (OSError, RuntimeError, ValueError) as exc:     # a side measurement: the line is printed without it
+                saved = {"error": f"{type(exc).__name__}: {exc}"[:200]}
         other = default_layout_side(a, barrier) if a.layout == "mapped" and a.model == "llama-3.1-8b" else None
     else:
         cpu_base = batch = other = saved = None        # timed at N=1 only
