@@ -226,11 +226,12 @@ typedef struct lmz_decode_plan {
                                  * n_fused_f32 chunks of 4-byte elements (coded top byte plane, three
                                  * stored planes), the first n_fused_f32_small of them small likewise */
     void *d_fused_status;       /* uint32 per fused job */
-    const void *d_delta_jobs;   /* delta chunks whose difference is a BF16 chunk with both planes coded: decoded,
-                                 * merged, XOR-ed with their base and checksummed by one kernel once the chunks they
-                                 * are differences against have been written (csrc/fused_kernel.cuh, DeltaJob) */
-    void *d_delta_status;       /* uint32 per stream: two per delta job */
-    void *d_delta_order;        /* n_delta + 2 uint32 of work space (the jobs sorted by alphabet size on the device) */
+    const void *d_delta_jobs;   /* BF16 chunks with both planes coded (csrc/fused_kernel.cuh, DeltaJob): decoded, merged
+                                 * and checksummed by one kernel -- the first n_delta_plain of them plain chunks
+                                 * (base_off all ones), in the first pass; the others delta chunks, XOR-ed with their
+                                 * base once the chunks they are differences against have been written */
+    void *d_delta_status;       /* uint32 per stream: two per job */
+    void *d_delta_order;        /* n_delta + 4 uint32 of work space (the jobs sorted by alphabet size on the device) */
     const void *d_chunks;       /* chunk jobs, ordered: pass 1 cond, pass 1 plain, fused, pass 2 cond, pass 2 plain */
     const void *d_piece_chunk;  /* uint32 per piece: its chunk */
     const void *d_cond_jobs;
@@ -260,6 +261,7 @@ typedef struct lmz_decode_plan {
                                  * and each table's run padded with empty jobs (n = 0) to a multiple of
                                  * lmz_gpu_shared_group() */
     uint32_t n_delta;           /* jobs in d_delta_jobs */
+    uint32_t n_delta_plain;     /* the first of them, which have no base */
     uint32_t piece_split[6];    /* piece-id boundaries of the five chunk groups */
     uint32_t phases;            /* 0 = everything; else bit 0 stream decode, bit 1 conditioned-chunk
                                  * kernels, bit 2 finish, bit 3 verdicts, bit 4 fused chunks

@@ -14,7 +14,7 @@ class DecodePlan(ctypes.Structure):
         "d_cond_pieces", "d_hist", "d_piece_cnt", "d_piece_wcnt", "d_piece_lcnt", "d_piece_crc", "d_crc_tables",
         "d_chunk_status", "d_chunk_crc", "d_any_bad", "d_tables", "d_fused_order")] + [(n, _u32) for n in (
             "n_stream_jobs", "n_seg_jobs", "n_chunks", "n_pieces", "n_cond", "n_cond_pieces",
-            "n_fused", "n_fused_small", "n_fused_f32", "n_fused_f32_small", "n_fused_t", "n_delta")] + [("piece_split", _u32 * 6), ("phases", _u32)]
+            "n_fused", "n_fused_small", "n_fused_f32", "n_fused_f32_small", "n_fused_t", "n_delta", "n_delta_plain")] + [("piece_split", _u32 * 6), ("phases", _u32)]
 
 
 def bind(lib) -> None:

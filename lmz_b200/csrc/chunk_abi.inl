@@ -145,6 +145,44 @@ API int lmz_host_alphabet_sizes(const void *base, const uint64_t *offs, size_t n
     return LMZ_GPU_OK;
 }
 
+// Chunks whose two BF16 planes are both coded, jobs [first, first + count) of the plan's list: alphabets
+// counted on the device, then chunks whose first plane has a small one (the rule) to the instance with
+// mixed table sizes (72 streams per SM), the others to the one with full-size tables for both planes (64).
+static int launch_two_plane(const lmz_decode_plan *p, uint32_t first, uint32_t count, cudaStream_t cs)
+{
+    if (count == 0) return LMZ_GPU_OK;
+    if (!p->d_delta_jobs || !p->d_delta_status || !p->d_delta_order)
+        return fail_msg(LMZ_GPU_EUNSUPPORTED, "two-plane jobs without their arrays");
+    StreamArgs da{};
+    da.src = (const uint8_t *)p->d_payload;
+    da.djobs = (const DeltaJob *)p->d_delta_jobs + first;
+    da.njobs = 2 * count;
+    da.dst = (uint8_t *)p->d_out;
+    da.status = (uint32_t *)p->d_delta_status + 2 * (size_t)first;
+    da.any_bad = (uint32_t *)p->d_any_bad;
+    da.piece_crc = (uint32_t *)p->d_piece_crc;
+    da.tabs = (const CrcTables *)p->d_crc_tables;
+    // work space: `count` indices and two counters, at 2 * first + ... so the two passes never share it
+    uint32_t *order = (uint32_t *)p->d_delta_order + (first ? first + 2 : 0);
+    uint32_t *counts = order + count;
+    CK("memset two-plane counts", cudaMemsetAsync(counts, 0, 8, cs));
+    StreamArgs ca = da;
+    ca.njobs = count;
+    k_classify<<<(count + 7) / 8, 256, 0, cs>>>(ca, F_SMALL_LIVE, order, counts);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) return fail_cuda("launch k_classify", le);
+    da.order = order;
+    const bool crc = p->d_piece_crc != nullptr;
+    int rc = LMZ_GPU_OK;
+    for (int big = 0; big < 2 && !rc; big++) {
+        da.count = counts + big;
+        da.order_from_back = big;
+        rc = big ? (crc ? launch_stream<SINK_DELTA, true, 256>(da, cs) : launch_stream<SINK_DELTA, false, 256>(da, cs))
+                 : (crc ? launch_stream<SINK_DELTA, true, F_HYBRID_CFN>(da, cs) : launch_stream<SINK_DELTA, false, F_HYBRID_CFN>(da, cs));
+    }
+    return rc;
+}
+
 API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
 {
     if (!p) return fail_msg(LMZ_GPU_EUNSUPPORTED, "no plan");
@@ -169,6 +207,7 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         return fail_msg(LMZ_GPU_EUNSUPPORTED, "n_fused_t is not a multiple of lmz_gpu_shared_group()");
     const bool other_work = p->n_stream_jobs || p->n_cond || p->piece_split[2] > p->piece_split[0] ||
                             p->piece_split[5] > p->piece_split[3];
+    if (p->n_delta_plain > p->n_delta) return fail_msg(LMZ_GPU_EUNSUPPORTED, "n_delta_plain exceeds n_delta");
     if ((p->n_fused || p->n_fused_t) && (ph & 16u)) {
         cudaStream_t fs = cs;
         if (ph == 0x1fu && other_work) {        // whole decode: run the fused kernel beside the rest
@@ -267,7 +306,14 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         }
     }
 
-    // 1. every rANS stream whose length is known up front, into scratch
+    // 1. plain chunks with both planes coded: the two-plane kernel without a base (few chunks are of this
+    //    shape: a short launch, beside the fused kernel when that one has a stream of its own)
+    if (p->n_delta_plain && (ph & 1u)) {
+        rc = launch_two_plane(p, 0, p->n_delta_plain, cs);
+        if (rc) return rc;
+    }
+
+    //    and every rANS stream whose length is known up front, into scratch
     if (p->n_stream_jobs && (ph & 1u)) {
         RansArgs a{};
         a.src = (const uint8_t *)p->d_payload;
@@ -351,39 +397,9 @@ API int lmz_gpu_decode_chunks_dev(const lmz_decode_plan *p, void *cuda_stream)
         if (part == 2) {
             // pass 2 (and the verdicts) read what the fused kernel wrote
             CK("join the side stream", scope.join());
-            if (p->n_delta) {
-                // delta chunks with both planes coded, now that the chunks they are differences against are in place
-                if (!p->d_delta_jobs || !p->d_delta_status) return fail_msg(LMZ_GPU_EUNSUPPORTED, "delta jobs without their arrays");
-                StreamArgs da{};
-                da.src = (const uint8_t *)p->d_payload;
-                da.djobs = (const DeltaJob *)p->d_delta_jobs;
-                da.njobs = 2 * p->n_delta;
-                da.dst = (uint8_t *)p->d_out;
-                da.status = (uint32_t *)p->d_delta_status;
-                da.any_bad = (uint32_t *)p->d_any_bad;
-                da.piece_crc = (uint32_t *)p->d_piece_crc;
-                da.tabs = (const CrcTables *)p->d_crc_tables;
-                // alphabets counted on the device: chunks whose exponent differences have a small one (the rule) go to
-                // the instance with mixed table sizes, 72 streams per SM instead of 64
-                uint32_t *order = (uint32_t *)p->d_delta_order;
-                if (!order) return fail_msg(LMZ_GPU_EUNSUPPORTED, "delta jobs without d_delta_order");
-                uint32_t *counts = order + p->n_delta;
-                CK("memset delta counts", cudaMemsetAsync(counts, 0, 8, cs));
-                StreamArgs ca = da;
-                ca.njobs = p->n_delta;
-                k_classify<<<(p->n_delta + 7) / 8, 256, 0, cs>>>(ca, F_SMALL_LIVE, order, counts);
-                cudaError_t le = cudaGetLastError();
-                if (le != cudaSuccess) return fail_cuda("launch k_classify", le);
-                da.order = order;
-                const bool crc = p->d_piece_crc != nullptr;
-                for (int big = 0; big < 2 && !rc; big++) {
-                    da.count = counts + big;
-                    da.order_from_back = big;
-                    rc = big ? (crc ? launch_stream<SINK_DELTA, true, 256>(da, cs) : launch_stream<SINK_DELTA, false, 256>(da, cs))
-                             : (crc ? launch_stream<SINK_DELTA, true, F_HYBRID_CFN>(da, cs) : launch_stream<SINK_DELTA, false, F_HYBRID_CFN>(da, cs));
-                }
-                if (rc) return rc;
-            }
+            // delta chunks with both planes coded, now that the chunks they are differences against are in place
+            rc = launch_two_plane(p, p->n_delta_plain, p->n_delta - p->n_delta_plain, cs);
+            if (rc) return rc;
             continue;
         }
         f.piece_begin = p->piece_split[part];

@@ -509,7 +509,8 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
     const uint32_t *mq = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(mant) & ~uintptr_t(3));
     uint32_t m[5] = {0, 0, 0, 0, 0};
     const uint32_t my_tiles = (n + TS - 1) / TS;
-    if ((SINK == SINK_BF16 && my_tiles) || (SINK == SINK_DELTA && n > 8 * j16)) {
+    const bool has_base = SINK == SINK_DELTA && moff != NONE64;      // (a plain two-plane chunk has none: m stays zero)
+    if ((SINK == SINK_BF16 && my_tiles) || (has_base && n > 8 * j16)) {
 #pragma unroll
         for (int i = 0; i < 5; i++) m[i] = __ldg(mq + i);
     }
@@ -592,7 +593,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
             bf16_merge4(ea.y, eb.y, w[2], w[3]);
 #pragma unroll
             for (int h = 0; h < 4; h++) w[h] ^= __funnelshift_r(m[h], m[h + 1], msh);
-            if (n > (t + 1) * TS + 8u * j16) {                     // next tile's base bytes, if this lane has any
+            if (has_base && n > (t + 1) * TS + 8u * j16) {         // next tile's base bytes, if this lane has any
 #pragma unroll
                 for (int i = 0; i < 5; i++) m[i] = __ldg(mq + (size_t)(t + 1) * (2 * TS / 4) + i);
             }

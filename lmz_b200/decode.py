@@ -114,7 +114,7 @@ class ArchiveDecoder:
             self.d_seg_status = torch.zeros(max(1, p.seg_jobs.size), **u32)
             self.d_fused_status = torch.zeros(max(1, p.fused_jobs.size), **u32)
             self.d_delta_status = torch.zeros(max(1, 2 * p.delta_jobs.size), **u32)
-            self.d_delta_order = torch.zeros(p.delta_jobs.size + 2, **u32)
+            self.d_delta_order = torch.zeros(p.delta_jobs.size + 4, **u32)
             self.d_chunk_status = torch.zeros(max(1, p.chunks.size), **u32)
             self.d_chunk_crc = torch.zeros(max(1, p.chunks.size), **u32)
             self.d_any_bad = torch.zeros(1, **u32)
@@ -129,7 +129,7 @@ class ArchiveDecoder:
         c.d_fused_jobs, c.d_fused_status = self.d_fused_jobs.data_ptr(), self.d_fused_status.data_ptr()
         c.n_fused, c.n_fused_t = p.n_fused, p.n_fused_t
         c.d_delta_jobs, c.d_delta_status = self.d_delta_jobs.data_ptr(), self.d_delta_status.data_ptr()
-        c.n_delta = p.delta_jobs.size
+        c.n_delta, c.n_delta_plain = p.delta_jobs.size, p.n_delta_plain
         c.d_delta_order = self.d_delta_order.data_ptr()
         c.d_tables = self.d_tables.data_ptr() if self.d_tables is not None else None
         c.n_fused_small = p.n_fused_small
@@ -160,7 +160,8 @@ class ArchiveDecoder:
         else:
             fused_launches = (1 if p.n_fused_small else 0) + (1 if nbf > p.n_fused_small else 0) + \
                 (1 if p.n_fused_f32_small else 0) + (1 if p.n_fused_f32 > p.n_fused_f32_small else 0)
-        fused_launches += (1 if p.n_fused_t else 0) + (3 if p.delta_jobs.size else 0)
+        fused_launches += (1 if p.n_fused_t else 0) + (3 if p.n_delta_plain else 0) + \
+            (3 if p.delta_jobs.size > p.n_delta_plain else 0)
         self.launches_per_run = (1 if p.stream_jobs.size else 0) + \
             ((4 + (1 if p.seg_jobs.size else 0)) if ncond else 0) + fused_launches + \
             int(sum(p.piece_split[i + 1] > p.piece_split[i] for i in (0, 1, 3, 4))) + 1

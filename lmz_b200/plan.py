@@ -77,7 +77,9 @@ class Plan:
     coded_bytes: int = 0           # sum of clen: algorithmic bytes read
     device_classify: bool = False  # the fused jobs are not sorted by alphabet: the library counts on the device
     n_fused_t: int = 0             # trailing fused jobs of shared-table chunks (padded per table to T_GROUP)
-    delta_jobs: np.ndarray = field(default=None)   # delta chunks decoded, undone and checksummed by one kernel
+    delta_jobs: np.ndarray = field(default=None)   # chunks with both BF16 planes coded: decoded, merged, a delta undone
+                                                   # and checksummed by one kernel; the first n_delta_plain have no base
+    n_delta_plain: int = 0
     tables: np.ndarray = field(default=None)   # the shared tables, TABLE_STRIDE bytes apart
 
     @property
@@ -281,8 +283,9 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
                 fused[fi] = True
                 f_src[fi], f_len[fi], f_mant[fi] = starts[fz, 0], lens[fz, 0], starts[fz, 1]
                 stored = stored | fz[:, None]          # no scratch stream for these
-                # a delta whose difference has both planes coded (mostly zero bytes, so both pay)
-                dz = is_delta[i] & ~stored[:, 0] & ~stored[:, 1] & (nelem > 0)
+                # both planes coded: a delta's difference (mostly zero bytes, so both pay), or a plain
+                # chunk whose sign/mantissa bytes compress; the same kernel, with or without a base
+                dz = ~is_ref[i] & ~stored[:, 0] & ~stored[:, 1] & (nelem > 0)
                 di2 = i[dz]
                 fused_d[di2] = True
                 f_src[di2], f_len[di2] = starts[dz, 0], lens[dz, 0]
@@ -474,11 +477,14 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
         tj["n"][slot], tj["piece0"][slot] = rlen[trec] // 2, piece0[tpos]
         fused_jobs = np.concatenate((fused_jobs, tj))
 
+    dpos = np.concatenate([dpos[~pass2[corder[dpos]]], dpos[pass2[corder[dpos]]]])   # plain chunks first: the first pass
+    n_delta_plain = int((~pass2[corder[dpos]]).sum())
     delta_jobs = np.zeros(dpos.size, dtype=DELTA_JOB)
     drec = corder[dpos]
     delta_jobs["src_a"], delta_jobs["len_a"] = f_src[drec], f_len[drec]
     delta_jobs["src_b"], delta_jobs["len_b"] = f_mant[drec], f_len_b[drec]
-    delta_jobs["dst_off"], delta_jobs["base_off"] = dst[drec], base[drec]
+    delta_jobs["dst_off"] = dst[drec]
+    delta_jobs["base_off"] = np.where(base[drec] >= 0, base[drec].astype(np.uint64), NONE64)
     delta_jobs["n"], delta_jobs["piece0"] = rlen[drec] // 2, piece0[dpos]
 
     payload = blob[:hi - lo]
@@ -491,7 +497,7 @@ def build_plan(ar: fmt.Archive, fuse=True, select=None, payload_range=None,
                 n_fused_f32_small=int((wide4 & small).sum()),
                 coded_bytes=int(clen.sum()), base_bytes=int(rlen[is_delta].sum()),
                 device_classify=classify != "host", n_fused_t=n_fused_t, tables=tables,
-                delta_jobs=delta_jobs)
+                delta_jobs=delta_jobs, n_delta_plain=n_delta_plain)
 
 
 def _inflate(raw: bytes) -> bytes:

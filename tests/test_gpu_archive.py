@@ -228,6 +228,30 @@ def test_corruption_is_reported(shard):
         decode.ArchiveDecoder(bytes(blob[:-1]))
 
 
+def test_plain_chunks_with_both_planes_coded():
+    """BF16 whose sign/mantissa bytes compress too (a few distinct values): both planes of a
+    chunk are rANS streams, and the two-plane kernel decodes, merges and checksums them in the
+    first pass without a base; a later member that is a delta against such chunks reads them."""
+    from lmz_b200 import archive, plan
+    rng = np.random.default_rng(17)
+    n = 500_003
+    vals = synth.normal_bf16(64, 3).view("<u2")
+    w = vals[rng.integers(0, 64, n)].astype("<u2")
+    a = synth.safetensors_bytes([("w", "BF16", (n,), w.view(np.uint8))])
+    w2 = w.copy()
+    hit = rng.random(n) < 0.2
+    w2[hit] ^= rng.integers(1, 4, int(hit.sum())).astype("<u2")
+    b = synth.safetensors_bytes([("w", "BF16", (n,), w2.view(np.uint8))])
+    for kw in (dict(mapped=True), dict(chunk_size=1 << 20)):
+        blob = oa.write_archive([("a.safetensors", a), ("b.safetensors", b)], **kw)
+        p = plan.build_plan(archive.Archive(blob))
+        assert 0 < p.n_delta_plain < p.delta_jobs.size, (p.n_delta_plain, p.delta_jobs.size)
+        assert (p.delta_jobs["base_off"][:p.n_delta_plain] == plan.NONE64).all()
+        assert (p.delta_jobs["base_off"][p.n_delta_plain:] != plan.NONE64).all()
+        _roundtrip(blob, np.concatenate([a, b]))
+        _roundtrip(blob, np.concatenate([a, b]), checksum=False)
+
+
 def test_corrupt_delta_chunks_are_reported():
     """Damage inside either plane's stream of a delta chunk, in a stream's magic and in a
     frequency table: the one-pass delta kernel (or the checksum behind it) reports each."""
