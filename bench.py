@@ -625,7 +625,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": workload_name(a), "plaintext_bytes": plain, "coded_bytes": coded,
                    "chunks": int(p.chunks.size),
-                   "rans_streams": int(p.fused_jobs.size + p.stream_jobs.size + p.seg_jobs.size),
+                   "rans_streams": int(p.fused_jobs.size + 2 * p.delta_jobs.size + p.stream_jobs.size + p.seg_jobs.size),
                    "crc32": not a.no_crc, "archive": archive_pin(a, rank),
                    "parity": "device crc32 of every chunk equals its record; 24 spread chunks byte-compared with the CPU oracle",
                    "per_gpu": "its own tensor-parallel slice" if per_rank_archives(a) else "full replica",
@@ -971,7 +971,7 @@ def default_layout_side(a, barrier):
     peak, _ = measured_peak()
     moved = p.coded_bytes + p.total
     return {"workload": workload_name(b), "plaintext_bytes": int(p.total), "chunks": int(p.chunks.size),
-            "rans_streams": int(p.fused_jobs.size + p.stream_jobs.size + p.seg_jobs.size),
+            "rans_streams": int(p.fused_jobs.size + 2 * p.delta_jobs.size + p.stream_jobs.size + p.seg_jobs.size),
             "value": round(p.total / (ms / 1e3) / 1e9, 2), "unit": "GB/s", "ms_per_step": round(ms, 3),
             "roofline_frac": round(moved / (ms / 1e3) / 1e9 / peak, 4), "archive": archive_pin(b),
             "phase_ms": phase}
@@ -1074,7 +1074,7 @@ def run_reference(a, rank: int):
         "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": {"workload": workload_name(a), "plaintext_bytes": int(p.total), "coded_bytes": int(p.coded_bytes),
                    "chunks": int(p.chunks.size),
-                   "rans_streams": int(p.fused_jobs.size + p.stream_jobs.size + p.seg_jobs.size),
+                   "rans_streams": int(p.fused_jobs.size + 2 * p.delta_jobs.size + p.stream_jobs.size + p.seg_jobs.size),
                    "crc32": not a.no_crc, "archive": archive_pin(a, 0),
                    "parity": "device crc32 of every chunk equals its record; 24 spread chunks byte-compared with the CPU oracle",
                    "per_gpu": "its own tensor-parallel slice" if per_rank_archives(a) else "full replica",
