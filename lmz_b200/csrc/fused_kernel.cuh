@@ -33,8 +33,9 @@
 //   * CFN = 0: no levels, a 16 KiB slot -> entry table per stream and 12 streams per
 //     CTA, 256-symbol tiles: for launches so small that only the length of a symbol's
 //     dependent chain counts (one lookup instead of two and a popcount)
-//   * CFN = 0 with a fourth warp: 13 streams per CTA, unaligned tables, a shorter ring and
-//     every symbol stored straight to its output byte (no staging row)
+//   * CFN = 0 with a fourth warp: 13 streams per CTA -- the tables on 16 KiB boundaries, the rings
+//     (shorter) in what is left below the first and above the last -- and every symbol stored
+//     straight to its output byte (no staging row)
 //   * CFN = -1: the same wide table once per CTA, for batches whose streams share one
 //     516-byte table (lmz_gpu_decode_batch's d_hdr) or for the chunks of a shared-table
 //     archive (StreamArgs.tables); a stream is then states + words
@@ -53,9 +54,9 @@ constexpr uint32_t F_STAGE = 144;                  // 128 + 16: groups land 4 ba
 // instruction of tile bookkeeping is paid in full, and has shared memory to spare beside
 // its 12 tables: its tiles are twice as long (256 symbols) and its ring twice as deep.
 __host__ __device__ constexpr bool stream_long_tiles(int cfn, int warps) { return cfn == 0 && (warps == 3 || warps == 4); }
-// The same with a thirteenth stream (a fourth warp that carries one): its table fits only when the
-// tables need no 16 KiB alignment, the ring has six slots instead of eight and nothing is staged --
-// every symbol goes straight to its byte of the output.  For launches of 12 x SMs + 1 ... 13 x SMs
+// The same with a thirteenth stream (a fourth warp that carries one): thirteen tables on 16 KiB
+// boundaries leave 19 KiB in two pieces, under the first and above the last, enough for rings of six
+// slots instead of eight and for no staging rows -- every symbol goes straight to its byte of the output.  For launches of 12 x SMs + 1 ... 13 x SMs
 // streams (the 1915 long streams of an 8B model at the reference's default chunking, on 148 SMs).
 __host__ __device__ constexpr bool stream_direct(int cfn, int warps) { return cfn == 0 && warps == 4; }
 constexpr uint32_t F_DIRECT_GROUPS = 13;
@@ -222,14 +223,14 @@ struct MRingT {
 
 // Table lookups and the state update of one decode step, before the refill.
 // Returns the level-2 entry (its low byte is the symbol); x2 is the new state.
-template <int CFN, bool ALIGNED = true>
+template <int CFN>
 __device__ __forceinline__ uint32_t stream_advance(uint32_t x, uint32_t l1_sa, uint32_t cf_sa, uint32_t &x2)
 {
     uint32_t e;
     if (CFN <= 0) {
-        // wide table at l1_sa (the stream's own, or the CTA's shared one): one lookup.  A 16 KiB
-        // aligned table is indexed by OR, any other by a shift-add.
-        e = lds_u32(ALIGNED ? ((x << 2) & 0x3ffcu) | l1_sa : l1_sa + ((x & 0xfffu) << 2));
+        // wide table at l1_sa (the stream's own, or the CTA's shared one), 16 KiB aligned: one
+        // lookup, the index OR-ed onto the base
+        e = lds_u32(((x << 2) & 0x3ffcu) | l1_sa);
     } else {
         // level 1: the warp's four tables are interleaved word by word, so bucket b of
         // this group sits 16 * b bytes in -- the slot's bits 4-11, unshifted
@@ -246,13 +247,13 @@ __device__ __forceinline__ uint32_t stream_advance(uint32_t x, uint32_t l1_sa, u
 
 // One decode step, any lane mix.  `caddr` is the shared address of the cursor
 // (linear within a tile thanks to the mirror).
-template <int CFN, bool ALIGNED = true>
+template <int CFN>
 __device__ __forceinline__ uint32_t stream_step(uint32_t &x, uint32_t &caddr, uint32_t l1_sa,
                                                 uint32_t cf_sa, uint32_t lt_mask, uint32_t grp_mask,
                                                 bool active)
 {
     uint32_t x2;
-    const uint32_t e = stream_advance<CFN, ALIGNED>(x, l1_sa, cf_sa, x2);
+    const uint32_t e = stream_advance<CFN>(x, l1_sa, cf_sa, x2);
     const bool need = active && x2 < RANS_LOW;
     const uint32_t vote = __ballot_sync(0xffffffffu, need);
     const uint32_t addr = caddr + 2 * __popc(vote & lt_mask);
@@ -269,13 +270,13 @@ __device__ __forceinline__ uint32_t stream_step(uint32_t &x, uint32_t &caddr, ui
 // lane's = bits of the older bytes plus the lanes below it in the newest, so one
 // popcount of hist & below (= 0xffffff00 | lanes below) gives the offset from
 // the block's cursor.  The caller adds 2 * popc(hist) to `cbase` after step 3.
-template <int CFN, bool FIRST, bool ALIGNED = true>
+template <int CFN, bool FIRST>
 __device__ __forceinline__ uint32_t stream_step4(uint32_t &x, uint32_t &hist, uint32_t cbase,
                                                  uint32_t l1_sa, uint32_t cf_sa, uint32_t below,
                                                  uint32_t vsel)
 {
     uint32_t x2;
-    const uint32_t e = stream_advance<CFN, ALIGNED>(x, l1_sa, cf_sa, x2);
+    const uint32_t e = stream_advance<CFN>(x, l1_sa, cf_sa, x2);
     const bool need = x2 < RANS_LOW;
     const uint32_t vote = __ballot_sync(0xffffffffu, need);
     hist = __byte_perm(vote, FIRST ? 0u : hist, vsel);
@@ -331,13 +332,23 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
     const uint32_t bars_0 = (s0 + 15u) & ~15u;
     const uint32_t stage_0 = bars_0 + G * 8 * NSL;
     const uint32_t ring_0 = stage_0 + G * STG;
+    // DIRECT: thirteen 16 KiB tables leave 19 KiB of the window, some of it below the first 16 KiB
+    // boundary and some above the last table: the tables sit on boundaries (an index is OR-ed onto the
+    // base, which is what makes the step as short as the 12-stream instance's) and the rings fill both
+    // remainders, `ring_below` of them under the tables.
+    const uint32_t dl1_0 = (ring_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1);
+    const uint32_t ring_below = DIRECT ? min(G, (dl1_0 - ring_0) / RB) : G;
+    const uint32_t ring_above_0 = dl1_0 + G * F_WIDE_BYTES;
+    auto ring_of = [&](uint32_t grp) { return DIRECT && grp >= ring_below ? ring_above_0 + (grp - ring_below) * RB : ring_0 + grp * RB; };
     const uint32_t cf_0 = (ring_0 + G * RB + CF_ALIGN - 1) & ~(CF_ALIGN - 1);
     // compact: level 1 at the top; wide: 16 KiB tables from the first 16 KiB boundary up
-    const uint32_t l1_0 = DIRECT ? cf_0 : WIDE ? (cf_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1)
+    const uint32_t l1_0 = DIRECT ? dl1_0 : WIDE ? (cf_0 + F_WIDE_BYTES - 1) & ~(F_WIDE_BYTES - 1)
                                : ((CRC ? tab0 : top) & ~4095u) - (WARPS - (TOPL1 ? 1 : 0)) * 4096u;
     // compact: this warp's 4 KiB of level 1 (the last warp's sits where the row-advance tables would)
     auto l1_of = [&](uint32_t w) { return TOPL1 && w == WARPS - 1 ? adv0 : l1_0 + w * 4096u; };
-    const bool fits = WIDE ? l1_0 + (SHARED ? 1u : G) * F_WIDE_BYTES <= (CRC ? tab0 : top) : cf_0 + G * CFB <= l1_0 && (!TOPL1 || (adv0 & 4095u) == 0);
+    const bool fits = DIRECT ? ring_above_0 + (G - ring_below) * RB <= top
+                    : WIDE ? l1_0 + (SHARED ? 1u : G) * F_WIDE_BYTES <= (CRC ? tab0 : top)
+                           : cf_0 + G * CFB <= l1_0 && (!TOPL1 || (adv0 & 4095u) == 0);
     auto gen = [&](uint32_t sa) { return ssm + (sa - s0); };
     const uint32_t l1_sa = SHARED ? l1_0 : WIDE ? l1_0 + gi * F_WIDE_BYTES : l1_of(warp) + g * 4;
     // (mixed sizes: the 1 KiB tables of the second planes first, then the half-KiB tables of the first planes)
@@ -353,7 +364,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
     const uint32_t tla = adv0 - 4096u;                              // crc_advance<0> adds 4 .. 7 KiB
 
     MRingT<NSL, stream_mirror(CFN, WARPS)> ring;
-    ring.sa = ring_0 + gi * RB;
+    ring.sa = ring_of(gi);
     ring.bars = reinterpret_cast<uint64_t *>(gen(bars_0)) + gi * NSL;
 
     // ---- this group's stream ------------------------------------------------------
@@ -465,7 +476,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
         uint32_t on = __shfl_sync(0xffffffffu, n, gg * 8);
         if (!on || (DIRECT && warp * 4 + gg >= G)) continue;
         uint32_t sk = __shfl_sync(0xffffffffu, skew, gg * 8);
-        const uint32_t rsa = ring_0 + (warp * 4 + gg) * RB;
+        const uint32_t rsa = ring_of(warp * 4 + gg);
         auto rd = [&](uint32_t o) { return lds_u8(rsa + o); };     // header sits in the first 548+15 bytes
         Tables tb{};
         auto freq_of = [&](uint32_t s) { return rd(sk + 4 + 2 * s) | (rd(sk + 5 + 2 * s) << 8); };
@@ -557,14 +568,14 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
 #pragma unroll
             for (uint32_t s4 = 0; s4 < TS / NLANES; s4 += 4) {
                 uint32_t hist = 0, e;
-                e = stream_step4<CFN_STEP, true, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN_STEP, true>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4, e);
-                e = stream_step4<CFN_STEP, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN_STEP, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4 + 1, e);
                 if (ROWMUL && (s4 >> 1) < NRA) ra[s4 >> 1] = crc_feed4q(cq, ra[s4 >> 1]);
-                e = stream_step4<CFN_STEP, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN_STEP, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4 + 2, e);
-                e = stream_step4<CFN_STEP, false, !DIRECT>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
+                e = stream_step4<CFN_STEP, false>(x, hist, caddr, l1_sa, cf_sa, below, vsel);
                 put(s4 + 3, e);
                 if (ROWMUL && (s4 >> 1) < NRA) ra[(s4 >> 1) + 1] = crc_feed4q(cq, ra[(s4 >> 1) + 1]);
                 caddr += 2 * __popc(hist);
@@ -577,7 +588,7 @@ __global__ void __launch_bounds__(WARPS * 32, CFN < 0 && SINK == SINK_BYTES ? 2 
 #pragma unroll 1
             for (uint32_t s = 0; s < TS / NLANES; s++) {
                 bool active = s * NLANES + k < rem;
-                uint32_t e = stream_step<CFN_STEP, !DIRECT>(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
+                uint32_t e = stream_step<CFN_STEP>(x, caddr, l1_sa, cf_sa, lt_mask, grp_mask, active);
                 if (active) put(s, e);
             }
         }
